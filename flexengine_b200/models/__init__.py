@@ -1,0 +1,1 @@
+from . import qwen2  # noqa: F401  (registers Qwen2ForCausalLM)

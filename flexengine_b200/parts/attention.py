@@ -1,0 +1,80 @@
+"""Causal grouped-query attention over the paged cache.
+
+q = h Wq^T + bq, k, v likewise; rotary encoding of q and k; k, v written to the
+request's pages before the scores are taken, so that a portion sees itself; key t is
+visible to the query at absolute position p iff t <= p (and t > p - window for a
+window group); softmax in float32; query head h reads key/value head h // (nq/nkv);
+output projection (src/flexengine/inference/models/qwen2.py:98-129,
+src/flexengine/inference/attention/paged.py:18-70).
+"""
+from __future__ import annotations
+
+import math
+
+from .base import Mixer, build_part, register_mixer
+from .spec import PartSpec
+
+
+class AttentionMixer(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: PartSpec | dict | None = None, qkv_bias: bool = True, out_bias: bool = False,
+                 window: int = 0, scale: float | None = None):
+        if num_heads % num_kv_heads:
+            raise ValueError("Invalid GQA head ratio")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = \
+            int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        if position is None:
+            position = PartSpec("none")
+        if isinstance(position, dict):
+            position = PartSpec(position["kind"], position.get("params", {}))
+        self.position = build_part("position", position)
+        self.qkv_weight = self.qkv_bias_ = self.out_weight = self.out_bias_ = None
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+
+    def parameter_shapes(self) -> dict:
+        shapes = {"qkv.weight": ((self.qkv_width, self.hidden_size), "matrix"),
+                  "out.weight": ((self.hidden_size, self.num_heads * self.head_dim), "matrix")}
+        if self.qkv_bias:
+            shapes["qkv.bias"] = ((self.qkv_width,), "vector")
+        if self.out_bias:
+            shapes["out.bias"] = ((self.hidden_size,), "vector")
+        return shapes
+
+    def bind(self, tensors: dict) -> None:
+        super().bind(tensors)
+        self.qkv_bias_ = tensors.get("qkv.bias")
+        self.out_bias_ = tensors.get("out.bias")
+
+    def cache_need(self):
+        return {"kind": "window" if self.window > 0 else "full", "kv_heads": self.num_kv_heads,
+                "head_dim": self.head_dim, "window": self.window}
+
+    def forward(self, ctx, h, entry):
+        ops = ctx.ops
+        group = ctx.groups[entry.cache_group]
+        k_cache, v_cache = group.kv_slot(entry.cache_slot)
+        qkv = ops.linear(h, self.qkv_weight)
+        rotary = self.position.rotary_table(h.device)
+        if rotary is None:
+            inv_freq, rot = None, 0
+        else:
+            inv_freq, rot = rotary
+        # bias, rotation and the cache write are one kernel; a run entry that only reads
+        # another entry's cache passes no slot mapping, so nothing is written.
+        ops.qkv_bias_rope_cache(qkv, self.qkv_bias_, ctx.positions, inv_freq, rot,
+                                group.slot_mapping if entry.write_cache else None,
+                                k_cache, v_cache, self.num_heads, self.num_kv_heads, self.head_dim,
+                                group.page_size)
+        if rotary is None:
+            self.position.apply(ctx, qkv, None)
+        out = ops.paged_attention(qkv, k_cache, v_cache, group.block_table, ctx, self.num_heads,
+                                  self.num_kv_heads, self.head_dim, group.page_size, self.scale, self.window)
+        return ops.linear(out, self.out_weight, self.out_bias_)
+
+
+register_mixer("attention", AttentionMixer)

@@ -1,0 +1,113 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part knows its own sizes and constants (constructor parameters) and nothing about
+the model it sits in.  Kinds are looked up by name, so that a test or another
+architecture can add a mixer, feed-forward, norm, position encoding or block
+arrangement with ``register_*`` and no change to this package.
+
+Interfaces
+----------
+Every part:      ``parameter_shapes() -> {local name: (shape, kind)}`` with kind in
+                 {"matrix", "vector", "int"}; ``bind({local name: tensor})``.
+Mixer:           ``cache_need() -> dict | None`` (what cache group it needs) and
+                 ``forward(ctx, h, entry) -> delta [T, hidden]``.
+FeedForward:     ``forward(ctx, h) -> delta [T, hidden]``.
+Norm:            ``forward(ctx, residual, delta, rows=None) -> h``: adds ``delta`` (may be None)
+                 to the float32 residual stream in place and returns the normalised rows
+                 in the compute dtype; with ``rows`` it reads only those rows and leaves the
+                 residual untouched.
+PositionEncoding: ``rotary_table()`` -> (inv_freq float32 [rot/2], rot) to be fused into the
+                 mixer's kernel, or None; then ``apply(ctx, q, k)`` is called instead.
+Block:           ``forward(ctx, residual, pending, entry) -> pending``: the arrangement of
+                 norms, mixer and feed-forward around the residual stream.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+_REGISTRIES: dict[str, dict[str, Callable]] = {
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+}
+
+
+def _register(family: str, kind: str, factory: Callable) -> None:
+    _REGISTRIES[family][kind] = factory
+
+
+def register_mixer(kind: str, factory: Callable) -> None:
+    _register("mixer", kind, factory)
+
+
+def register_feed_forward(kind: str, factory: Callable) -> None:
+    _register("feed_forward", kind, factory)
+
+
+def register_norm(kind: str, factory: Callable) -> None:
+    _register("norm", kind, factory)
+
+
+def register_position(kind: str, factory: Callable) -> None:
+    _register("position", kind, factory)
+
+
+def register_block(kind: str, factory: Callable) -> None:
+    _register("block", kind, factory)
+
+
+def build_part(family: str, spec):
+    """Instantiate ``spec`` (a PartSpec) from the registry of ``family``."""
+    table = _REGISTRIES[family]
+    if spec.kind not in table:
+        raise KeyError(f"unknown {family} kind {spec.kind!r}; known: {sorted(table)}")
+    return table[spec.kind](**dict(spec.params))
+
+
+def block_factory(kind: str) -> Callable:
+    table = _REGISTRIES["block"]
+    if kind not in table:
+        raise KeyError(f"unknown block kind {kind!r}; known: {sorted(table)}")
+    return table[kind]
+
+
+class Part:
+    """Common behaviour: declared parameters are bound by local name with a shape check."""
+
+    def parameter_shapes(self) -> dict:
+        return {}
+
+    def bind(self, tensors: dict) -> None:
+        want = self.parameter_shapes()
+        missing = sorted(set(want) - set(tensors))
+        extra = sorted(set(tensors) - set(want))
+        if missing or extra:
+            raise ValueError(f"{type(self).__name__}: missing {missing}, unexpected {extra}")
+        for name, (shape, _kind) in want.items():
+            if tuple(tensors[name].shape) != tuple(shape):
+                raise ValueError(f"{type(self).__name__}.{name}: shape {tuple(tensors[name].shape)}, want {tuple(shape)}")
+            setattr(self, name.replace(".", "_"), tensors[name])
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, ctx, h, entry):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, h):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, ctx, residual, delta, rows=None):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary_table(self, device):
+        return None
+
+    def apply(self, ctx, q, k):
+        return None
