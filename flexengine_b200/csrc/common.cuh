@@ -1,0 +1,91 @@
+// Shared helpers of the kernels: element conversion, warp and block reductions, error
+// reporting.  Every kernel is templated on the element type (float for the true 32-bit
+// path, __nv_bfloat16 for serving) and does its arithmetic in float.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// dtype codes of the C interface
+#define FE_F32 0
+#define FE_BF16 1
+
+// bits a kernel may set in the device status word (it then skips the access)
+#define FE_STATUS_BAD_TOKEN 1
+#define FE_STATUS_BAD_PAGE 2
+#define FE_STATUS_BAD_SLOT 4
+#define FE_STATUS_WAIT_EXPIRED 8
+
+namespace fe {
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_float(T v);
+template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  ``scratch`` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                 // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float w = lane < warps ? scratch[lane] : 0.f;
+        w = warp_sum(w);
+        if (lane == 0) scratch[32] = w;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Load 8 consecutive elements (16-byte aligned for bf16, 32-byte span for float) as floats.
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* out);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* out) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* out) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i] = __uint_as_float(w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+}  // namespace fe
+
+// Host side: the last error message of this thread, and a checked launch epilogue.
+void fe_set_error(const char* fmt, ...);
+int fe_check_launch(const char* what);
+
+#define FE_REQUIRE(cond, ...)            \
+    do {                                 \
+        if (!(cond)) {                   \
+            fe_set_error(__VA_ARGS__);   \
+            return 1;                    \
+        }                                \
+    } while (0)

@@ -1,0 +1,206 @@
+"""The kernels as Python functions over CUDA tensors.
+
+Every function here launches hand-written CUDA from ``csrc/`` on the current stream;
+the only library calls are bfloat16 matrix products (cuBLAS through ``torch.mm``), where
+the reference uses a library too (src/flexengine/inference/models/qwen2.py:99-101,129-135).
+There is no CPU path: tensors must be on a CUDA device, and a missing or unbuildable
+kernel library raises.
+
+Conventions: activations are float32 (true 32-bit path) or bfloat16; the residual stream,
+norm weights, biases and logits are float32; index tensors are int32.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import library
+
+_c_void_p, _c_int, _c_float, _c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+_status: dict = {}
+launches = 0          # kernels of this package launched so far (library matrix products not counted)
+
+
+def _core():
+    return library.load("core")
+
+
+def _ptr(t):
+    return _c_void_p(t.data_ptr()) if t is not None else _c_void_p(0)
+
+
+def _stream():
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _code(dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise TypeError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("flexengine_b200.ops runs on CUDA tensors only; there is no CPU path")
+
+
+def _run(lib, name: str, *args) -> None:
+    global launches
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed: {lib.fe_last_error().decode()}")
+    launches += 1
+
+
+def status_word(device) -> torch.Tensor:
+    """The device word in which kernels record a guarded fault (bad token, page or slot)."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Synchronises; raises if a kernel met an index it had to skip since the last check."""
+    word = status_word(device)
+    value = int(word.item())
+    if value:
+        word.zero_()
+        names = [n for bit, n in ((1, "token id out of range"), (2, "page id out of range"),
+                                  (4, "cache slot out of range"), (8, "a bounded wait ran out")) if value & bit]
+        raise RuntimeError("kernel status: " + ", ".join(names))
+
+
+# ------------------------------------------------------------------------------------------------
+def embedding(token_ids, table):
+    """float32 residual rows [T, H] = table[token_ids]."""
+    _need_cuda(token_ids, table)
+    T, (V, H) = token_ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _run(_core(), "fe_embedding", _ptr(token_ids), _ptr(table), _ptr(out), _c_int(T), _c_int(H), _c_int(V),
+         _c_int(_code(table.dtype)), _ptr(status_word(table.device)), _stream())
+    return out
+
+
+def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None):
+    """Fused residual add + RMSNorm.  rows=None: residual += delta in place (all rows) and every row
+    is normalised; rows given: only those rows are read (residual[rows] + delta[rows]), nothing is
+    written back."""
+    _need_cuda(residual, delta, weight, rows)
+    T, H = residual.shape
+    if residual.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise TypeError("the residual stream and norm weights are float32")
+    if delta is not None and (delta.dtype != out_dtype or delta.shape != residual.shape or not delta.is_contiguous()):
+        raise ValueError("add_rmsnorm: delta must be contiguous, shaped like the residual, in the compute dtype")
+    n_out = T if rows is None else rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=residual.device)
+    _run(_core(), "fe_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(weight), _c_float(eps), _ptr(out), _ptr(rows),
+         _c_int(n_out), _c_int(H), _c_int(T), _c_int(_code(out_dtype)), _stream())
+    return out
+
+
+def gemm_fp32(x, w, bias=None):
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _run(_core(), "fe_gemm_fp32", _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _stream())
+    return out
+
+
+def linear(x, w, bias=None, out_float32=False):
+    """y = x w^T (+ bias); x [M, K], w [N, K].  A float32 weight runs the true 32-bit product
+    (CUDA cores, no reduced-precision mode) whatever the activation dtype; a bfloat16 weight
+    runs on tensor cores with float32 accumulation."""
+    _need_cuda(x, w, bias)
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise ValueError(f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    if w.dtype == torch.float32:
+        y = gemm_fp32(x if x.dtype == torch.float32 else x.float(), w, bias)
+        return y if (out_float32 or x.dtype == torch.float32) else y.to(x.dtype)
+    if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+        raise TypeError(f"linear: weight {w.dtype} with activations {x.dtype}")
+    y = torch.mm(x, w.t(), out_dtype=torch.float32) if out_float32 else torch.mm(x, w.t())
+    if bias is not None:
+        y += bias.to(y.dtype)
+    return y
+
+
+def swiglu(gate_up, intermediate):
+    _need_cuda(gate_up)
+    T = gate_up.shape[0]
+    if gate_up.shape[1] != 2 * intermediate or not gate_up.is_contiguous():
+        raise ValueError("swiglu: input must be contiguous [T, 2 * intermediate]")
+    out = torch.empty((T, intermediate), dtype=gate_up.dtype, device=gate_up.device)
+    _run(_core(), "fe_swiglu", _ptr(gate_up), _ptr(out), _c_int(T), _c_int(intermediate),
+         _c_int(_code(gate_up.dtype)), _stream())
+    return out
+
+
+def linear_swiglu(x, w, intermediate):
+    """silu(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K])."""
+    return swiglu(linear(x, w), intermediate)
+
+
+def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache,
+                        nq, nkv, d, page_size):
+    """In place on qkv [T, (nq + 2 nkv) d]: + bias, rotary encoding of the query and key heads;
+    key and value heads are also written to their cache slots (slot_mapping None: no write)."""
+    _need_cuda(qkv, bias, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    T, width = qkv.shape
+    if width != (nq + 2 * nkv) * d or not qkv.is_contiguous():
+        raise ValueError("qkv_bias_rope_cache: qkv must be contiguous [T, (nq + 2 nkv) d]")
+    if k_cache.dtype != qkv.dtype or tuple(k_cache.shape[1:]) != (nkv, page_size, d) or not k_cache.is_contiguous() \
+            or not v_cache.is_contiguous():
+        raise ValueError("qkv_bias_rope_cache: cache must be contiguous [pages, nkv, page_size, d] in the compute dtype")
+    if bias is not None and bias.dtype != torch.float32:
+        raise TypeError("biases are float32")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2):
+        raise ValueError("inv_freq must be float32 [rot / 2]")
+    num_slots = k_cache.shape[0] * page_size
+    _run(_core(), "fe_qkv_bias_rope_cache", _ptr(qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq), _c_int(rot),
+         _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d),
+         _c_int(page_size), _c_ll(num_slots), _c_int(_code(qkv.dtype)), _ptr(status_word(qkv.device)), _stream())
+
+
+def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, token_request, T, nq, nkv, d,
+                         page_size, scale, window):
+    out = torch.empty((T, nq * d), dtype=k_cache.dtype, device=k_cache.device)
+    _run(_core(), "fe_paged_attention_simt", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
+         _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
+         _ptr(token_request), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size),
+         _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window), _c_int(_code(k_cache.dtype)),
+         _ptr(status_word(k_cache.device)), _stream())
+    return out
+
+
+def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window):
+    """Causal grouped-query attention of the step's tokens over their requests' pages.
+    qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d]."""
+    _need_cuda(qkv, k_cache, v_cache, block_table)
+    T = qkv.shape[0]
+    if qkv.dtype != k_cache.dtype:
+        raise TypeError("queries and cache differ in dtype")
+    return paged_attention_simt(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start,
+                                ctx.token_request, T, nq, nkv, d, page_size, scale, window)
+
+
+def sample(logits, temperature, top_k, seed, draw):
+    """int32 [R]: one token per row of float32 logits [R, V]; see csrc/sampling.cu."""
+    _need_cuda(logits, temperature, top_k, seed, draw)
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise TypeError("sample: logits must be float32 with unit column stride")
+    if temperature.dtype != torch.float32 or top_k.dtype != torch.int32 or seed.dtype != torch.int64 \
+            or draw.dtype != torch.int64:
+        raise TypeError("sample: temperature float32, top_k int32, seed and draw int64")
+    out = torch.empty(R, dtype=torch.int32, device=logits.device)
+    _run(_core(), "fe_sample", _ptr(logits), _c_ll(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
+         _ptr(top_k), _ptr(seed), _ptr(draw), _ptr(out), _stream())
+    return out

@@ -1,0 +1,280 @@
+"""Each CUDA kernel alone against its plain PyTorch reference, at sizes other than the engine's:
+widths and vocabularies that are no powers of two, head sizes in steps of 16, ragged tails,
+reversed and scattered block tables, windows, and inputs made so that a far key matters."""
+import math
+import random
+import types
+
+import pytest
+import torch
+
+import kernel_refs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from flexengine_b200 import ops as cuda_ops
+    return cuda_ops
+
+
+def bar(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def rand(shape, dtype, gen, scale=1.0):
+    return (torch.randn(shape, generator=gen, device=DEV, dtype=torch.float32) * scale).to(dtype)
+
+
+@pytest.fixture()
+def gen():
+    g = torch.Generator(device=DEV)
+    g.manual_seed(1234)
+    return g
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H", [(301, 80), (1000, 3584), (17, 24)])
+def test_embedding(dtype, V, H, gen):
+    table = rand((V, H), dtype, gen)
+    ids = torch.randint(0, V, (37,), device=DEV, dtype=torch.int32, generator=gen)
+    got = ops().embedding(ids, table)
+    assert got.dtype == torch.float32
+    torch.testing.assert_close(got, kernel_refs.embedding(ids, table), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H", [(1, 64), (5, 80), (7, 3584), (3, 5000), (2, 24)])
+def test_add_rmsnorm(dtype, T, H, gen):
+    weight = 1 + 0.1 * torch.randn(H, device=DEV, generator=gen)
+    for eps in (1e-6, 1e-2):
+        residual = torch.randn(T, H, device=DEV, generator=gen)
+        delta = rand((T, H), dtype, gen)
+        r1, r2 = residual.clone(), residual.clone()
+        got = ops().add_rmsnorm(r1, delta, weight, eps, dtype)
+        want = kernel_refs.add_rmsnorm(r2, delta, weight, eps, dtype)
+        torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
+        torch.testing.assert_close(r1, r2, atol=1e-6, rtol=1e-6)          # residual updated in place
+        got0 = ops().add_rmsnorm(r1, None, weight, eps, dtype)
+        torch.testing.assert_close(got0.float(), kernel_refs.add_rmsnorm(r2, None, weight, eps, dtype).float(), **bar(dtype))
+        rows = torch.tensor([T - 1, 0, T // 2], device=DEV, dtype=torch.int32)
+        keep = r1.clone()
+        got_rows = ops().add_rmsnorm(r1, delta, weight, eps, dtype, rows)
+        want_rows = kernel_refs.add_rmsnorm(r2, delta, weight, eps, dtype, rows)
+        torch.testing.assert_close(got_rows.float(), want_rows.float(), **bar(dtype))
+        torch.testing.assert_close(r1, keep, atol=0, rtol=0)             # rows mode leaves the residual alone
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (33, 130, 70), (64, 64, 16), (100, 301, 257), (3, 1000, 3584)])
+def test_gemm_fp32_is_true_fp32(M, N, K, gen):
+    x = torch.randn(M, K, device=DEV, generator=gen)
+    w = torch.randn(N, K, device=DEV, generator=gen)
+    b = torch.randn(N, device=DEV, generator=gen)
+    want = (x.double() @ w.double().T + b.double())
+    got = ops().linear(x, w, b)
+    assert got.dtype == torch.float32
+    # float32 accumulation over K terms of unit variance: error ~ sqrt(K) * 2^-24 * |terms|
+    torch.testing.assert_close(got.double(), want, atol=2e-6 * math.sqrt(K) * 4, rtol=1e-5)
+    # a row's result does not depend on how many rows are in the batch
+    alone = ops().linear(x[:1].contiguous(), w, b)
+    assert torch.equal(alone[0], got[0])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 301 * 8, 80), (130, 384, 192)])
+def test_linear_bf16(M, N, K, gen):
+    x, w = rand((M, K), torch.bfloat16, gen), rand((N, K), torch.bfloat16, gen, 0.05)
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(ops().linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
+    got32 = ops().linear(x, w, None, out_float32=True)
+    assert got32.dtype == torch.float32
+    torch.testing.assert_close(got32, want, atol=1e-3, rtol=1e-3)
+    # a weight stored in 32-bit stays so: the product is the true float32 one
+    got = ops().linear(x, w.float())
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 160), (9, 112), (33, 18944)])
+def test_swiglu(dtype, T, I, gen):
+    x = rand((T, 2 * I), dtype, gen, 2.0)
+    torch.testing.assert_close(ops().swiglu(x, I).float(), kernel_refs.swiglu(x, I).float(), **bar(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot,ps", [(4, 2, 16, 16, 16), (6, 1, 32, 32, 32), (5, 5, 48, 32, 16),
+                                             (28, 4, 128, 128, 16), (3, 3, 64, 0, 8)])
+def test_qkv_bias_rope_cache(dtype, nq, nkv, d, rot, ps, gen):
+    T, pages = 19, 12
+    qkv = rand((T, (nq + 2 * nkv) * d), dtype, gen)
+    bias = torch.randn((nq + 2 * nkv) * d, device=DEV, generator=gen) * 0.1
+    # large positions too: the angle is position * inv_freq in float32
+    positions = torch.tensor([0, 1, 2, 15, 16, 17, 255, 4095, 32767, 100000, 131071] + list(range(40, 48)),
+                             device=DEV, dtype=torch.int32)
+    inv_freq = None
+    if rot:
+        inv_freq = (1.0 / 1e6 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot)).to(DEV)
+    slots = torch.randperm(pages * ps, device=DEV, generator=gen)[:T].to(torch.int32)
+    slots[3] = -1                                       # a padded token writes nothing
+    caches = [torch.zeros(2, pages, nkv, ps, d, device=DEV, dtype=dtype) for _ in range(2)]
+    a, b = qkv.clone(), qkv.clone()
+    ops().qkv_bias_rope_cache(a, bias, positions, inv_freq, rot, slots, caches[0][0], caches[0][1], nq, nkv, d, ps)
+    kernel_refs.qkv_bias_rope_cache(b, bias, positions, inv_freq, rot, slots, caches[1][0], caches[1][1], nq, nkv, d, ps)
+    # sin/cos of a large float32 angle: both sides take the same float32 angle, so they agree to rounding
+    torch.testing.assert_close(a.float(), b.float(), **bar(dtype))
+    torch.testing.assert_close(caches[0].float(), caches[1].float(), **bar(dtype))
+    # without a slot mapping nothing is written
+    c = qkv.clone()
+    untouched = torch.zeros_like(caches[0])
+    ops().qkv_bias_rope_cache(c, bias, positions, inv_freq, rot, None, untouched[0], untouched[1], nq, nkv, d, ps)
+    assert float(untouched.abs().max()) == 0.0
+    torch.testing.assert_close(c.float(), b.float(), **bar(dtype))
+    ops().check_status(DEV)
+
+
+def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None):
+    """chunks: [(start, n)] per request.  Fills the cache for positions < start + n."""
+    R = len(chunks)
+    lens = [s + n for s, n in chunks]
+    pages_per = [-(-l // ps) for l in lens]
+    total_pages = sum(pages_per) + 3
+    perm = list(range(total_pages))
+    if order == "scattered":
+        random.Random(0).shuffle(perm)
+    elif order == "reversed":
+        perm = perm[::-1]
+    kc = rand((total_pages, nkv, ps, d), dtype, gen)
+    vc = rand((total_pages, nkv, ps, d), dtype, gen)
+    bt = torch.full((R, max(pages_per)), -1, dtype=torch.int32)
+    k = 0
+    for r, n in enumerate(pages_per):
+        bt[r, :n] = torch.tensor(perm[k:k + n], dtype=torch.int32)
+        k += n
+    T = sum(n for _, n in chunks)
+    qkv = rand((T, (nq + 2 * nkv) * d), dtype, gen)
+    if boost is not None:
+        # make one far key decisive for the last query of request 0: align the key with the query
+        r0_len = lens[0]
+        t_far = boost
+        page, off = int(bt[0, t_far // ps]), t_far % ps
+        last_row = chunks[0][1] - 1
+        ratio = nq // nkv
+        for g in range(nkv):
+            qvec = qkv[last_row, g * ratio * d:(g * ratio + 1) * d].clone()
+            for h in range(g * ratio, (g + 1) * ratio):          # the heads of a group share the query
+                qkv[last_row, h * d:(h + 1) * d] = qvec
+            kc[page, g, off] = (qvec.float() * 4.0).to(dtype)
+        vc[page, :, off] = 10.0
+        assert t_far < r0_len
+    cu = [0]
+    for _, n in chunks:
+        cu.append(cu[-1] + n)
+    ctx = types.SimpleNamespace(
+        cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+        q_start=torch.tensor([s for s, _ in chunks], dtype=torch.int32, device=DEV),
+        token_request=torch.tensor([r for r, (_, n) in enumerate(chunks) for _ in range(n)], dtype=torch.int32, device=DEV))
+    bt = bt.to(DEV)
+    scale = 1.0 / math.sqrt(d)
+    got = ops().paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
+    want = kernel_refs.paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
+    return got, want, chunks
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,ps", [(4, 2, 16, 16), (6, 1, 32, 32), (6, 3, 48, 16), (28, 4, 128, 16),
+                                         (2, 2, 256, 8), (5, 1, 80, 16)])
+def test_paged_attention_shapes(dtype, nq, nkv, d, ps, gen):
+    # lengths around page and 32-key block edges; decode tokens beside portions
+    chunks = [(0, 1), (0, 17), (15, 2), (31, 1), (32, 1), (33, 5), (0, 64), (129, 1), (100, 30)]
+    got, want, _ = _attention_case(dtype, nq, nkv, d, ps, chunks, 0, gen)
+    torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
+    ops().check_status(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("order", ["reversed", "scattered", "ordered"])
+def test_paged_attention_block_tables(dtype, order, gen):
+    got, want, _ = _attention_case(dtype, 6, 2, 32, 16, [(512, 1), (0, 129), (250, 7)], 0, gen, order=order)
+    torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 33, 100])
+def test_paged_attention_window(dtype, window, gen):
+    got, want, _ = _attention_case(dtype, 4, 2, 32, 16, [(200, 1), (0, 70), (90, 12)], window, gen)
+    torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 15, 16, 17, 333, 700])
+def test_paged_attention_finds_a_far_key(dtype, far, gen):
+    # one key among 800 is made decisive; the output of the last query must be its value (10)
+    got, want, chunks = _attention_case(dtype, 4, 2, 64, 16, [(799, 1), (3, 2)], 0, gen, boost=far)
+    torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
+    assert float((got[0].float() - 10.0).abs().max()) < 0.5
+
+
+def test_sample_greedy_and_ties():
+    logits = torch.randn(5, 301, device=DEV)
+    logits[1, 7] = logits[1, 200] = 50.0            # a tie goes to the lowest index
+    logits[2, 300] = 60.0
+    zeros_f, zeros_i = torch.zeros(5, device=DEV), torch.zeros(5, dtype=torch.int32, device=DEV)
+    z64 = torch.zeros(5, dtype=torch.int64, device=DEV)
+    got = ops().sample(logits, zeros_f, zeros_i, z64, z64)
+    assert got.tolist() == kernel_refs.sample(logits, zeros_f, zeros_i, z64, z64).tolist()
+    assert got[1] == 7 and got[2] == 300
+
+
+@pytest.mark.parametrize("V", [301, 152064])
+def test_sample_temperature_top_k(V):
+    torch.manual_seed(0)
+    R = 24
+    logits = torch.randn(R, V, device=DEV) * 3
+    logits[5, 10] = logits[5, 20] = logits[5, 30] = 9.0     # ties at the top-k edge
+    temperature = torch.tensor([0.8, 1.0, 5.0, 0.3] * 6, device=DEV)
+    top_k = torch.tensor([0, 1, 2, 40, 0, 2, 300, V, V + 5, 7, 0, 3] * 2, dtype=torch.int32, device=DEV)
+    seed = torch.arange(100, 100 + R, dtype=torch.int64, device=DEV)
+    for draw_no in range(6):
+        draw = torch.full((R,), draw_no, dtype=torch.int64, device=DEV)
+        got = ops().sample(logits, temperature, top_k, seed, draw).cpu()
+        again = ops().sample(logits, temperature, top_k, seed, draw).cpu()
+        assert torch.equal(got, again)
+        for r in range(R):
+            x = (logits[r].cpu().double() / float(temperature[r]))
+            k = int(top_k[r])
+            keep = torch.ones(V, dtype=torch.bool)
+            if 0 < k < V:
+                keep[:] = False
+                keep[torch.sort(x, descending=True, stable=True).indices[:k]] = True
+            assert keep[got[r]], f"row {r}: sampled a token outside the top {k}"
+            e = torch.where(keep, torch.exp(x - x.max()), torch.zeros_like(x))
+            cum = torch.cumsum(e, 0)
+            target = kernel_refs.uniform_from(int(seed[r]), draw_no) * float(cum[-1])
+            lo = float(cum[got[r] - 1]) if got[r] > 0 else 0.0
+            hi = float(cum[got[r]])
+            slack = 1e-5 * float(cum[-1])
+            assert lo - slack <= target <= hi + slack, f"row {r}: draw outside the token's interval"
+    # a row's draw does not depend on its place in the batch
+    perm = torch.randperm(R)
+    draw = torch.full((R,), 3, dtype=torch.int64, device=DEV)
+    base = ops().sample(logits, temperature, top_k, seed, draw).cpu()
+    shuffled = ops().sample(logits[perm.to(DEV)].contiguous(), temperature[perm.to(DEV)], top_k[perm.to(DEV)],
+                            seed[perm.to(DEV)], draw).cpu()
+    assert torch.equal(shuffled, base[perm])
+
+
+def test_sample_follows_the_distribution():
+    V = 11
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5, 3.0, -2.0, 1.5, 0.2, 2.5, -0.5]], device=DEV)
+    n = 20000
+    rows = logits.expand(n, V).contiguous()
+    t = torch.full((n,), 0.7, device=DEV)
+    k = torch.full((n,), 5, dtype=torch.int32, device=DEV)
+    seed = torch.full((n,), 77, dtype=torch.int64, device=DEV)
+    draw = torch.arange(n, dtype=torch.int64, device=DEV)
+    got = ops().sample(rows, t, k, seed, draw).cpu()
+    import plain_model
+    want = plain_model.sampling_distribution(logits[0], 0.7, 5)
+    freq = torch.bincount(got.long(), minlength=V).double() / n
+    assert float((freq - want.double()).abs().max()) < 0.015

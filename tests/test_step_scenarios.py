@@ -1,0 +1,76 @@
+"""The step function against the plain implementation, under every way of cutting the work.
+
+The same scenarios run twice: on the CPU with the PyTorch kernel references handed to the
+engine (host logic: metadata, cache, block tables), and, marked ``gpu``, with the CUDA
+kernels in float32 and in bfloat16.
+"""
+import random
+
+import pytest
+import torch
+
+import helpers
+import kernel_refs
+
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 40, 77, 130], "C": [3, 50, 64]}
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    return {name: helpers.make_model_dir(tmp_path_factory, name, seed=11 + i)
+            for i, name in enumerate(helpers.CONFIGS)}
+
+
+def _requests(name: str, seed: int = 3) -> dict:
+    rng = random.Random(seed)
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    return {f"r{i}": helpers.random_prompt(rng, n, vocab) for i, n in enumerate(LENGTHS[name])}
+
+
+def _scenario(kind: str, requests: dict, rng: random.Random) -> list:
+    if kind == "whole":
+        return helpers.steps_whole(requests)
+    if kind == "last_decoded":
+        return helpers.steps_last_decoded(requests, tail=32)
+    if kind == "portions":
+        return helpers.steps_portions(requests, rng)
+    if kind == "mixed":
+        # twice the requests, so that later ones run in pages that earlier ones gave back
+        doubled = dict(requests)
+        doubled.update({rid + "x": ids[::-1] for rid, ids in requests.items()})
+        return helpers.steps_mixed(doubled, rng, live=4)
+    raise ValueError(kind)
+
+
+def _run(model_dir, name, kind, dtype, device, ops):
+    rng = random.Random(5)
+    requests = _requests(name)
+    steps = _scenario(kind, requests, rng)
+    page = helpers.PAGE_SIZE[name]
+    # just enough pages for the live requests: pages are used again
+    pages = helpers.peak_pages(steps, page) + (0 if kind == "mixed" else 1)
+    runner = helpers.make_runner(model_dir, dtype, device, pages, page, max_requests=4, ops=ops)
+    results = helpers.run_steps(runner, steps)
+    assert runner.cache.used_pages == 0
+    all_requests = {}
+    for entries, _ in steps:
+        for rid, toks, _w in entries:
+            all_requests.setdefault(rid, []).extend(toks)
+    helpers.compare_with_plain(model_dir, results, all_requests, dtype, f"{name}/{kind}/{dtype}")
+    if device != "cpu":
+        from flexengine_b200 import ops as cuda_ops
+        cuda_ops.check_status(device)
+
+
+@pytest.mark.parametrize("kind", ["whole", "last_decoded", "portions", "mixed"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_step_on_cpu_with_reference_kernels(model_dirs, name, kind):
+    _run(model_dirs[name], name, kind, "float32", "cpu", kernel_refs)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["whole", "last_decoded", "portions", "mixed"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_step_on_gpu(model_dirs, name, kind, dtype):
+    _run(model_dirs[name], name, kind, dtype, "cuda:0", None)
