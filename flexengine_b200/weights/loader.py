@@ -69,7 +69,7 @@ def check_against_plan(plan, entries: dict) -> None:
 
 
 def _natural(name: str):
-    return [int(p) if p.isdigit() else p for p in name.replace(".", " . ").split()]
+    return [(0, int(p), "") if p.isdigit() else (1, 0, p) for p in name.split(".")]
 
 
 def _held_dtype(kind: str, stored: list, compute: torch.dtype) -> torch.dtype:

@@ -1,0 +1,104 @@
+"""On the GPU: greedy generation through the Python entry point, long decoding, the first tokens
+of a sequence, and sampling through the engine, in float32 and bfloat16."""
+import random
+
+import pytest
+import torch
+
+import helpers
+import plain_model
+from flexengine_b200.config import EngineConfig
+from flexengine_b200.engine import StepEntry
+from flexengine_b200.engine.runtime import Engine
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def model_dirs(tmp_path_factory):
+    return {name: helpers.make_model_dir(tmp_path_factory, name, seed=41) for name in ("A", "B")}
+
+
+def engine_for(model_dir, name, dtype, **kw):
+    cfg = EngineConfig(model=model_dir, device=DEV, dtype=dtype, max_model_len=kw.pop("max_model_len", 256),
+                       max_num_seqs=kw.pop("max_num_seqs", 4), max_num_batched_tokens=kw.pop("budget", 24),
+                       kv_block_size=helpers.PAGE_SIZE[name], kv_num_blocks=kw.pop("pages", 32), max_output_tokens=64, **kw)
+    return Engine.from_model_dir(model_dir, cfg)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(model_dirs, name):
+    config, weights = plain_model.read_model_folder(model_dirs[name], DEV)
+    rng = random.Random(1)
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    prompts = [helpers.random_prompt(rng, n, vocab) for n in (5, 17, 33, 1, 40)]
+    engine = engine_for(model_dirs[name], name, "float32", scheduler_policy="decode_first", prefill_chunk_size=8)
+    outputs = engine.generate(prompts, max_tokens=8)
+    for prompt, out in zip(prompts, outputs):
+        assert out.token_ids == plain_model.greedy_generate(config, weights, prompt, 8)
+        assert out.finish_reason in ("length", "stop")
+    assert engine.cache.used_pages == 0
+    # bfloat16: every chosen token is a maximum of the float32 logits up to bfloat16's error
+    engine = engine_for(model_dirs[name], name, "bfloat16")
+    for prompt, out in zip(prompts, engine.generate(prompts, max_tokens=8)):
+        logits = plain_model.forward_logits(config, weights, prompt + out.token_ids[:-1])
+        for i, token in enumerate(out.token_ids):
+            row = logits[len(prompt) - 1 + i]
+            assert float(row.max() - row[token]) < 0.06
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_dirs, dtype):
+    """400 tokens decoded one by one after a short prompt, beside a second request that starts
+    later; every logits row against the whole-sequence plain implementation."""
+    name = "B"
+    rng = random.Random(2)
+    ids = helpers.random_prompt(rng, 420, 512)
+    other = helpers.random_prompt(rng, 150, 512)
+    runner = helpers.make_runner(model_dirs[name], dtype, DEV, 20, 32, max_requests=2)
+    rows = {"long": [], "other": []}
+    rows["long"].append(runner.step([StepEntry("long", ids[:20], list(range(20)))]))
+    for p in range(20, 420):
+        entries = [StepEntry("long", ids[p:p + 1], [0])]
+        q = p - 200
+        if 0 <= q < 150:
+            entries.append(StepEntry("other", other[q:q + 1], [0]))
+        out = runner.step(entries)
+        rows["long"].append(out[:1])
+        if len(entries) == 2:
+            rows["other"].append(out[1:])
+    helpers.assert_logits_close(torch.cat(rows["long"]), helpers.plain_logits(model_dirs[name], ids, DEV), dtype, "long")
+    helpers.assert_logits_close(torch.cat(rows["other"]), helpers.plain_logits(model_dirs[name], other, DEV), dtype, "other")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    vocab = helpers.CONFIGS[name]["vocab_size"]
+    ids = helpers.random_prompt(random.Random(3), 4, vocab)
+    want = helpers.plain_logits(model_dirs[name], ids)
+    runner = helpers.make_runner(model_dirs[name], dtype, DEV, 4, helpers.PAGE_SIZE[name], max_requests=4)
+    one = torch.cat([runner.step([StepEntry("a", ids[p:p + 1], [0])]) for p in range(4)])
+    helpers.assert_logits_close(one, want, dtype, "token by token from position 0")
+    two = torch.cat([runner.step([StepEntry("b", ids[:1], [0])]), runner.step([StepEntry("b", ids[1:], [0, 1, 2])])])
+    helpers.assert_logits_close(two, want, dtype, "1 + 3")
+    single = runner.step([StepEntry("c", ids[:1], [0])])
+    helpers.assert_logits_close(single, want[:1], dtype, "a sequence of one token")
+
+
+def test_temperature_sampling_through_the_engine(model_dirs):
+    prompts = [list(range(60, 72)), [7, 200] * 16 + [1], [3, 14, 15, 92, 65], [9]]
+    alone = [engine_for(model_dirs["A"], "A", "float32").generate([p], max_tokens=8, temperature=0.8, top_k=20, seed=100 + i)[0].token_ids
+             for i, p in enumerate(prompts)]
+    together = engine_for(model_dirs["A"], "A", "float32", budget=5, scheduler_policy="decode_first")
+    assert [o.token_ids for o in together.generate(prompts, max_tokens=8, temperature=0.8, top_k=20, seed=100)] == alone
+    tight = engine_for(model_dirs["A"], "A", "float32", pages=4, budget=48, max_num_seqs=2, max_model_len=64)
+    assert [o.token_ids for o in tight.generate(prompts, max_tokens=8, temperature=0.8, top_k=20, seed=100)] == alone
+    assert tight.preemption_count >= 1 and tight.cache.used_pages == 0
+    # every sampled token lies among the 20 most likely of the plain implementation's distribution
+    config, weights = plain_model.read_model_folder(model_dirs["A"], DEV)
+    for prompt, tokens in zip(prompts, alone):
+        logits = plain_model.forward_logits(config, weights, prompt + tokens[:-1])
+        for i, token in enumerate(tokens):
+            assert token in torch.topk(logits[len(prompt) - 1 + i], 21).indices.tolist()
