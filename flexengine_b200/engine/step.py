@@ -79,8 +79,10 @@ class ModelRunner:
         self.ops = ops
         self.device = cache.device
         self.vocab_size = model.plan.vocab_size
-        self._pinned = None
+        self._ring = []
+        self._ring_at = 0
         self.steps_run = 0
+        self.h2d_bytes = 0           # bytes of step metadata copied to the device so far
 
     # ------------------------------------------------------------------------------------------
     def _check(self, entries) -> None:
@@ -125,6 +127,20 @@ class ModelRunner:
                         del rc.tables[gi][keep:]
             raise
 
+    def _staging(self, count: int) -> torch.Tensor:
+        """A pinned host buffer that no copy still in flight reads from.  The host runs ahead of
+        the device, so a buffer is taken again only after the copy that last used it has finished."""
+        if not self._ring:
+            self._ring = [[torch.empty(1 << 14, dtype=torch.int32, pin_memory=True), torch.cuda.Event()]
+                          for _ in range(4)]
+            self._ring_at = 0
+        self._ring_at = (self._ring_at + 1) % len(self._ring)
+        slot = self._ring[self._ring_at]
+        slot[1].synchronize()
+        if slot[0].numel() < count:
+            slot[0] = torch.empty(max(count, 2 * slot[0].numel()), dtype=torch.int32, pin_memory=True)
+        return slot[0][:count]
+
     def _upload(self, arrays: list) -> list:
         """One host buffer, one transfer; returns device views in the order given."""
         sizes = [len(a) for a in arrays]
@@ -135,16 +151,19 @@ class ModelRunner:
             total += (s + 3) // 4 * 4
         total = max(total, 4)
         if self.device.type == "cuda":
-            if self._pinned is None or self._pinned.numel() < total:
-                self._pinned = torch.empty(max(total, 1 << 14), dtype=torch.int32, pin_memory=True)
-            host = self._pinned[:total]
+            host = self._staging(total)
         else:
             host = torch.empty(total, dtype=torch.int32)
         view = host.numpy()
         for a, o, s in zip(arrays, offsets, sizes):
             if s:
                 view[o:o + s] = a
-        dev = host.to(self.device, non_blocking=True) if self.device.type == "cuda" else host.clone()
+        self.h2d_bytes += total * 4
+        if self.device.type == "cuda":
+            dev = host.to(self.device, non_blocking=True)
+            self._ring[self._ring_at][1].record()       # the copy out of this buffer is done after this
+        else:
+            dev = host.clone()
         return [dev[o:o + s] for o, s in zip(offsets, sizes)]
 
     # ------------------------------------------------------------------------------------------

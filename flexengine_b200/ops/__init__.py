@@ -61,7 +61,8 @@ def status_word(device) -> torch.Tensor:
     """The device word in which kernels record a guarded fault (bad token, page or slot)."""
     key = str(device)
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):          # a plain tensor, writable from any mode
+            _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]
 
 

@@ -102,3 +102,23 @@ def test_temperature_sampling_through_the_engine(model_dirs):
         logits = plain_model.forward_logits(config, weights, prompt + tokens[:-1])
         for i, token in enumerate(tokens):
             assert token in torch.topk(logits[len(prompt) - 1 + i], 21).indices.tolist()
+
+
+def test_host_running_ahead_of_the_device(model_dirs):
+    """The host enqueues many steps while the device is still busy with earlier work: every step
+    must see its own metadata (staging buffers are not reused while a copy is in flight)."""
+    name = "A"
+    rng = random.Random(5)
+    ids = [helpers.random_prompt(rng, 120, 256) for _ in range(3)]
+    runner = helpers.make_runner(model_dirs[name], "float32", DEV, 24, 16, max_requests=3)
+    big = torch.randn(8192, 8192, device=DEV)
+    for _ in range(40):                                  # keeps the device busy for a while
+        big = torch.tanh(big @ big * 1e-4)
+    outs = [runner.step([StepEntry(f"r{j}", ids[j][:20], list(range(20))) for j in range(3)])]
+    for p in range(20, 120):
+        outs.append(runner.step([StepEntry(f"r{j}", ids[j][p:p + 1], [0]) for j in range(3)]))
+    from flexengine_b200 import ops
+    ops.check_status(DEV)
+    for j in range(3):
+        got = torch.cat([outs[0][20 * j:20 * (j + 1)]] + [o[j:j + 1] for o in outs[1:]])
+        helpers.assert_logits_close(got, helpers.plain_logits(model_dirs[name], ids[j], DEV), "float32", f"ahead {j}")

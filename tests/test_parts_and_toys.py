@@ -107,7 +107,8 @@ def test_attention_mixer_part(device, window):
     group_spec = CacheGroupSpec("kv", "window" if window else "full", slots=1, kv_heads=nkv, head_dim=d, window=window)
     cache = CacheManager([group_spec], 4, ps, 1, torch.float32, device)
     runner_ctx = ModelRunner.__new__(ModelRunner)                # only build_context is used
-    runner_ctx.cache, runner_ctx.ops, runner_ctx.device, runner_ctx._pinned = cache, provider(device), cache.device, None
+    runner_ctx.cache, runner_ctx.ops, runner_ctx.device = cache, provider(device), cache.device
+    runner_ctx._ring, runner_ctx._ring_at, runner_ctx.h2d_bytes = [], 0, 0
     runner_ctx.model = types.SimpleNamespace(dtype=torch.float32)
     outs, fed = [], 0
     for n in (9, 11, 1):
