@@ -1,0 +1,478 @@
+// Paged causal grouped-query attention on tensor cores (bfloat16 inputs, float accumulation,
+// float online softmax), for decode and for prefill portions.
+//
+// Math as the reference's block-wise path (inference/attention/paged.py:50-70): running maximum,
+// running sum and value accumulator in float; key t is visible to the query at position p iff
+// t <= p (and t > p - window when window > 0); query head h reads key/value head h / (nq / nkv).
+//
+// Both kernels walk the keys in tiles of 32 aligned to position 0.  A tile's keys and values are
+// gathered page by page with 16-byte asynchronous copies into a ring of shared-memory stages
+// (rows swizzled against bank conflicts), read back with ldmatrix and multiplied with
+// mma.sync.m16n8k16.  The 16 rows of an MMA tile are the query heads of one key/value group
+// (decode) or (query, head-of-group) pairs (prefill), so the group shares every key it loads.
+//
+// decode:  one warp per (split of the keys, key/value head, request); partial results of the
+//          splits go to scratch memory and are merged by a second kernel (split-KV).
+// prefill: four warps per (tile of 64 rows, key/value head, request); the warps share the
+//          key/value stages.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+using namespace fe;
+
+namespace {
+
+constexpr int TK = 32;          // keys per tile
+constexpr int STAGES = 3;       // shared-memory stages per ring
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int src_bytes) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem_src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+// D[16x8] += A[16x16] (row) * B[16x8] (col), bf16 inputs, float accumulators
+__device__ __forceinline__ void mma16816(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
+// Element offset of 16-byte chunk c of row r in a tile whose rows are PITCH elements apart:
+// chunks are XOR-swizzled with the row inside each group of eight chunks.
+template <int PITCH> __device__ __forceinline__ int tile_offset(int r, int c) {
+    return r * PITCH + (((c & ~7) | ((c ^ r) & 7)) << 3);
+}
+
+struct KvSource {
+    const bf16* kc;
+    const bf16* vc;
+    const int* table;      // this request's row of the block table
+    int nkv, kvh, d, ps, num_pages;
+};
+
+// Gather keys/values of tile ``tile`` (keys tile*TK .. +TK-1) into one stage.  Keys outside
+// [lo, hi] are filled with zeros (their scores are masked; zero values keep 0 * v finite).
+template <int DMAX, int THREADS>
+__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const KvSource& src, int tile, int lo, int hi,
+                                          int* status) {
+    const int cpr = src.d >> 3;                       // 16-byte chunks per row
+    for (int idx = threadIdx.x; idx < TK * cpr; idx += THREADS) {
+        const int r = idx / cpr, c = idx - r * cpr;
+        const int key = tile * TK + r;
+        bool valid = key >= lo && key <= hi;
+        long long off = 0;
+        if (valid) {
+            const int page = src.table[key / src.ps];
+            if (page < 0 || page >= src.num_pages) {
+                if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
+                valid = false;
+            } else {
+                off = (((long long)page * src.nkv + src.kvh) * src.ps + (key % src.ps)) * src.d + (c << 3);
+            }
+        }
+        const int o = tile_offset<DMAX>(r, c);
+        cp_async16(ks + o, src.kc + off, valid ? 16 : 0);
+        cp_async16(vs + o, src.vc + off, valid ? 16 : 0);
+    }
+}
+
+// One warp, one tile: s = Q K^T (scaled to log2 units), mask, online softmax, o += P V.
+// pos0 / pos1: positions of the queries in rows g and g + 8 (negative: the row is padding).
+template <int DMAX>
+__device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, const unsigned (*qfrag)[4],
+                                             float (*o)[4], float* m, float* l, int tile, int d, float scale_log2,
+                                             int pos0, int pos1, int window) {
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    float s[TK / 8][4];
+#pragma unroll
+    for (int j = 0; j < TK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    const int mat = lane >> 3, mrow = lane & 7;
+#pragma unroll
+    for (int ksx = 0; ksx < DMAX / 16; ++ksx) {
+        if (ksx * 16 < d) {
+#pragma unroll
+            for (int jp = 0; jp < TK / 16; ++jp) {
+                unsigned r0, r1, r2, r3;
+                const int row = jp * 16 + (mat >> 1) * 8 + mrow;
+                ldmatrix_x4(r0, r1, r2, r3, ks + tile_offset<DMAX>(row, ksx * 2 + (mat & 1)));
+                mma16816(s[jp * 2], qfrag[ksx], r0, r1);
+                mma16816(s[jp * 2 + 1], qfrag[ksx], r2, r3);
+            }
+        }
+    }
+    const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int lo1 = window > 0 ? max(0, pos1 - window + 1) : 0;
+    float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < TK / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = tile * TK + j * 8 + 2 * t + (e & 1);
+            const bool upper = e < 2;
+            const bool vis = upper ? (key <= pos0 && key >= lo0) : (key <= pos1 && key >= lo1);
+            const float v = vis ? s[j][e] * scale_log2 : -CUDART_INF_F;
+            s[j][e] = v;
+            if (upper) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    const float ms0 = mn0 == -CUDART_INF_F ? 0.f : mn0, ms1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
+    const float al0 = exp2f(m[0] - ms0), al1 = exp2f(m[1] - ms1);      // exp2(-inf) = 0 on the first visible tile
+    m[0] = mn0; m[1] = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < TK / 8; ++j) {
+        s[j][0] = exp2f(s[j][0] - ms0); s[j][1] = exp2f(s[j][1] - ms0);
+        s[j][2] = exp2f(s[j][2] - ms1); s[j][3] = exp2f(s[j][3] - ms1);
+        sum0 += s[j][0] + s[j][1]; sum1 += s[j][2] + s[j][3];
+    }
+    l[0] = l[0] * al0 + sum0; l[1] = l[1] * al1 + sum1;                 // per-thread partial sums of the row
+#pragma unroll
+    for (int n = 0; n < DMAX / 8; ++n) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
+#pragma unroll
+    for (int kk = 0; kk < TK / 16; ++kk) {
+        unsigned a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int np = 0; np < DMAX / 16; ++np) {
+            if (np * 16 < d) {
+                unsigned r0, r1, r2, r3;
+                const int row = kk * 16 + (mat & 1) * 8 + mrow;
+                ldmatrix_x4_trans(r0, r1, r2, r3, vs + tile_offset<DMAX>(row, np * 2 + (mat >> 1)));
+                mma16816(o[np * 2], a, r0, r1);
+                mma16816(o[np * 2 + 1], a, r2, r3);
+            }
+        }
+    }
+}
+
+// Query fragments of one 16-row tile: row g -> src0, row g + 8 -> src1 (nullptr: a padding row).
+template <int DMAX>
+__device__ __forceinline__ void load_q(unsigned (*qfrag)[4], const bf16* src0, const bf16* src1, int d) {
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int ksx = 0; ksx < DMAX / 16; ++ksx) {
+        qfrag[ksx][0] = qfrag[ksx][1] = qfrag[ksx][2] = qfrag[ksx][3] = 0u;
+        if (ksx * 16 < d) {
+            const int c = ksx * 16 + 2 * t;
+            if (src0) { qfrag[ksx][0] = *reinterpret_cast<const unsigned*>(src0 + c);
+                        qfrag[ksx][2] = *reinterpret_cast<const unsigned*>(src0 + c + 8); }
+            if (src1) { qfrag[ksx][1] = *reinterpret_cast<const unsigned*>(src1 + c);
+                        qfrag[ksx][3] = *reinterpret_cast<const unsigned*>(src1 + c + 8); }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// decode: grid (splits, nkv, requests), one warp.  Every request brings exactly one token.
+template <int DMAX>
+__global__ void __launch_bounds__(32)
+paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                    float* __restrict__ part_o, float* __restrict__ part_lse, const bf16* __restrict__ kc,
+                    const bf16* __restrict__ vc, const int* __restrict__ block_table, int bt_stride,
+                    const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv, int d, int ps,
+                    int num_pages, float scale_log2, int window, int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    constexpr int TILE = TK * DMAX;                  // elements per K (or V) stage
+    const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
+    const int G = nq / nkv;
+    const int tok = cu_q[b];
+    const int pos = q_start[b];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int tile_lo = lo / TK, tile_hi = pos / TK;
+    const int per = (tile_hi - tile_lo + 1 + splits - 1) / splits;
+    const int t_begin = tile_lo + split * per, t_end = min(tile_hi + 1, t_begin + per);
+
+    unsigned qfrag[DMAX / 16][4];
+    const bf16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * d;
+    load_q<DMAX>(qfrag, g < G ? qrow + (size_t)g * d : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * d : nullptr, d);
+
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int n = 0; n < DMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+
+    KvSource src{kc, vc, block_table + (size_t)b * bt_stride, nkv, kvh, d, ps, num_pages};
+    const int n_tiles = max(0, t_end - t_begin);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_tiles) load_tile<DMAX, 32>(smem + s * 2 * TILE, smem + s * 2 * TILE + TILE, src, t_begin + s, lo, pos, status);
+        cp_async_commit();
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<STAGES - 2>();
+        __syncwarp();
+        const int nxt = it + STAGES - 1;
+        if (nxt < n_tiles) {
+            const int st = nxt % STAGES;
+            load_tile<DMAX, 32>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, src, t_begin + nxt, lo, pos, status);
+        }
+        cp_async_commit();
+        const int st = it % STAGES;
+        compute_tile<DMAX>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, qfrag, o, m, l, t_begin + it, d,
+                           scale_log2, pos, pos, window);
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = g + 8 * i;
+        if (row >= G) continue;
+        const int head = kvh * G + row;
+        const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+        if (splits == 1) {
+            bf16* op = out + (size_t)tok * out_stride + (size_t)head * d;
+#pragma unroll
+            for (int n = 0; n < DMAX / 8; ++n) {
+                const int col = n * 8 + 2 * t;
+                if (col < d)
+                    *reinterpret_cast<__nv_bfloat162*>(op + col) = __floats2bfloat162_rn(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+            }
+        } else {
+            const size_t slot = ((size_t)b * nq + head) * splits + split;
+            float* po = part_o + slot * d;
+#pragma unroll
+            for (int n = 0; n < DMAX / 8; ++n) {
+                const int col = n * 8 + 2 * t;
+                if (col < d) *reinterpret_cast<float2*>(po + col) = make_float2(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+            }
+            if (t == 0) part_lse[slot] = l[i] > 0.f ? m[i] + log2f(l[i]) : -CUDART_INF_F;
+        }
+    }
+}
+
+// Merge the splits: grid (nq, requests), one thread per element of the head.
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                      bf16* __restrict__ out, long long out_stride, const int* __restrict__ cu_q,
+                                      int nq, int d, int splits) {
+    const int head = blockIdx.x, b = blockIdx.y;
+    const size_t base = ((size_t)b * nq + head) * splits;
+    float mx = -CUDART_INF_F;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_lse[base + s]);
+    bf16* op = out + (size_t)cu_q[b] * out_stride + (size_t)head * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float acc = 0.f, wsum = 0.f;
+        if (mx != -CUDART_INF_F) {
+            for (int s = 0; s < splits; ++s) {
+                const float w = exp2f(part_lse[base + s] - mx);
+                wsum += w;
+                acc += w * part_o[(base + s) * d + j];
+            }
+        }
+        op[j] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// prefill: grid (row tiles, nkv, requests), four warps.  Row m of a (request, kv head) is the pair
+// (query m / G, head m % G of the group); a block takes 64 consecutive rows.
+constexpr int PREFILL_WARPS = 4;
+constexpr int PREFILL_ROWS = PREFILL_WARPS * 16;
+
+template <int DMAX>
+__global__ void __launch_bounds__(PREFILL_WARPS * 32)
+paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                     const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
+                     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv,
+                     int d, int ps, int num_pages, float scale_log2, int window, int* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    constexpr int TILE = TK * DMAX;
+    constexpr int THREADS = PREFILL_WARPS * 32;
+    const int kvh = blockIdx.y, r = blockIdx.z;
+    const int G = nq / nkv;
+    const int tok0 = cu_q[r], n_q = cu_q[r + 1] - tok0;
+    const int rows = n_q * G;
+    const int m_block = blockIdx.x * PREFILL_ROWS;
+    if (m_block >= rows) return;
+    const int start = q_start[r];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int m0 = m_block + warp * 16 + g, m1 = m0 + 8;
+    const bool v0 = m0 < rows, v1 = m1 < rows;
+    const int qi0 = v0 ? m0 / G : 0, qi1 = v1 ? m1 / G : 0;
+    const int pos0 = v0 ? start + qi0 : -1, pos1 = v1 ? start + qi1 : -1;
+    const int head0 = kvh * G + (v0 ? m0 % G : 0), head1 = kvh * G + (v1 ? m1 % G : 0);
+
+    unsigned qfrag[DMAX / 16][4];
+    load_q<DMAX>(qfrag, v0 ? q + (size_t)(tok0 + qi0) * q_stride + (size_t)head0 * d : nullptr,
+                 v1 ? q + (size_t)(tok0 + qi1) * q_stride + (size_t)head1 * d : nullptr, d);
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int n = 0; n < DMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
+
+    // keys this block needs: from the window edge of its first query to its last query
+    const int qi_first = m_block / G, qi_last = min(n_q - 1, (m_block + PREFILL_ROWS - 1) / G);
+    const int hi = start + qi_last;
+    const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
+    const int t_begin = lo / TK, n_tiles = hi / TK - t_begin + 1;
+    // this warp's rows see no key beyond its last valid row's position
+    const int warp_last = min(rows - 1, m_block + warp * 16 + 15);
+    const int warp_hi = warp_last >= m_block + warp * 16 ? start + warp_last / G : -1;
+    const int warp_lo = window > 0 ? max(0, start + (m_block + warp * 16) / G - window + 1) : 0;
+
+    KvSource src{kc, vc, block_table + (size_t)r * bt_stride, nkv, kvh, d, ps, num_pages};
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < n_tiles) load_tile<DMAX, THREADS>(smem + s * 2 * TILE, smem + s * 2 * TILE + TILE, src, t_begin + s, lo, hi, status);
+        cp_async_commit();
+    }
+    for (int it = 0; it < n_tiles; ++it) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                 // tile ``it`` has landed; everyone is done with tile it - 1
+        const int nxt = it + STAGES - 1;
+        if (nxt < n_tiles) {
+            const int st = nxt % STAGES;
+            load_tile<DMAX, THREADS>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, src, t_begin + nxt, lo, hi, status);
+        }
+        cp_async_commit();
+        const int tile = t_begin + it;
+        if (tile * TK <= warp_hi && tile * TK + TK - 1 >= warp_lo) {
+            const int st = it % STAGES;
+            compute_tile<DMAX>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, qfrag, o, m, l, tile, d,
+                               scale_log2, pos0, pos1, window);
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (!(i == 0 ? v0 : v1)) continue;
+        const int qi = i == 0 ? qi0 : qi1, head = i == 0 ? head0 : head1;
+        const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+        bf16* op = out + (size_t)(tok0 + qi) * out_stride + (size_t)head * d;
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n) {
+            const int col = n * 8 + 2 * t;
+            if (col < d)
+                *reinterpret_cast<__nv_bfloat162*>(op + col) = __floats2bfloat162_rn(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+        }
+    }
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <int DMAX> size_t ring_bytes() { return (size_t)STAGES * 2 * TK * DMAX * sizeof(bf16); }
+
+template <typename K> int allow_smem(K kernel, size_t bytes, const char* what) {
+    if (bytes > 48 * 1024) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (err != cudaSuccess) {
+            fe_set_error("%s: %s", what, cudaGetErrorString(err));
+            return 1;
+        }
+    }
+    return 0;
+}
+
+int check_common(const char* what, int nq, int nkv, int d, int ps, int num_pages, int window, long long q_stride,
+                 long long out_stride) {
+    FE_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "%s: bad head counts %d/%d", what, nq, nkv);
+    FE_REQUIRE(d >= 16 && d <= 256 && d % 16 == 0, "%s: head size %d is not a multiple of 16 in [16, 256]", what, d);
+    FE_REQUIRE(ps > 0 && num_pages > 0 && window >= 0, "%s: bad page size, page count or window", what);
+    FE_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0, "%s: row strides must keep 16-byte alignment", what);
+    return 0;
+}
+
+}  // namespace
+
+// Number of bytes of scratch the decode kernel needs for ``splits`` > 1 (0 for one split):
+// float partial outputs [requests, nq, splits, d] followed by float log-sum-exps [requests, nq, splits].
+extern "C" long long fe_paged_decode_scratch_bytes(int requests, int nq, int d, int splits) {
+    if (splits <= 1) return 0;
+    return (long long)requests * nq * splits * (d + 1) * (long long)sizeof(float);
+}
+
+extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, void* scratch,
+                                   const void* kc, const void* vc, const int* block_table, int bt_stride,
+                                   const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
+                                   int num_pages, float scale, int window, int splits, int* status,
+                                   cudaStream_t stream) {
+    if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
+    FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
+    FE_REQUIRE(splits >= 1 && splits <= 65535 && requests >= 0, "paged_decode: bad split or request count");
+    FE_REQUIRE(splits == 1 || scratch != nullptr, "paged_decode: %d splits need scratch memory", splits);
+    if (requests == 0) return 0;
+    float* part_o = (float*)scratch;
+    float* part_lse = part_o ? part_o + (size_t)requests * nq * splits * d : nullptr;
+    const dim3 grid(splits, nkv, requests);
+    const float scale_log2 = scale * LOG2E;
+#define FE_DECODE(DMAX)                                                                                           \
+    do {                                                                                                          \
+        if (allow_smem(paged_decode_kernel<DMAX>, ring_bytes<DMAX>(), "paged_decode")) return 1;                  \
+        paged_decode_kernel<DMAX><<<grid, 32, ring_bytes<DMAX>(), stream>>>(                                      \
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, part_o, part_lse, (const bf16*)kc, (const bf16*)vc, \
+            block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);        \
+    } while (0)
+    if (d <= 64) FE_DECODE(64);
+    else if (d <= 128) FE_DECODE(128);
+    else FE_DECODE(256);
+#undef FE_DECODE
+    if (fe_check_launch("paged_decode")) return 2;
+    if (splits > 1) {
+        decode_combine_kernel<<<dim3(nq, requests), d >= 128 ? 128 : 64, 0, stream>>>(
+            part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits);
+        return fe_check_launch("paged_decode combine");
+    }
+    return 0;
+}
+
+extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride,
+                                    const void* kc, const void* vc, const int* block_table, int bt_stride,
+                                    const int* cu_q, const int* q_start, int requests, int max_q_len, int nq, int nkv,
+                                    int d, int ps, int num_pages, float scale, int window, int* status,
+                                    cudaStream_t stream) {
+    if (check_common("paged_prefill", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
+    FE_REQUIRE(requests >= 0 && max_q_len >= 0, "paged_prefill: bad request count or length");
+    if (requests == 0 || max_q_len == 0) return 0;
+    const long long rows = (long long)max_q_len * (nq / nkv);
+    const long long tiles = (rows + PREFILL_ROWS - 1) / PREFILL_ROWS;
+    FE_REQUIRE(tiles <= 2147483647LL && nkv <= 65535 && requests <= 65535, "paged_prefill: grid too large");
+    const dim3 grid((unsigned)tiles, nkv, requests);
+    const float scale_log2 = scale * LOG2E;
+#define FE_PREFILL(DMAX)                                                                                       \
+    do {                                                                                                       \
+        if (allow_smem(paged_prefill_kernel<DMAX>, ring_bytes<DMAX>(), "paged_prefill")) return 1;             \
+        paged_prefill_kernel<DMAX><<<grid, PREFILL_WARPS * 32, ring_bytes<DMAX>(), stream>>>(                  \
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table,  \
+            bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);                  \
+    } while (0)
+    if (d <= 64) FE_PREFILL(64);
+    else if (d <= 128) FE_PREFILL(128);
+    else FE_PREFILL(256);
+#undef FE_PREFILL
+    return fe_check_launch("paged_prefill");
+}

@@ -181,15 +181,78 @@ def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_sta
     return out
 
 
+_scratch: dict = {}
+SM_COUNT = 148
+
+
+def _bf16():
+    return library.load("bf16")
+
+
+def scratch(device, nbytes: int) -> torch.Tensor:
+    """Scratch memory of at least ``nbytes`` bytes on ``device`` (grown on demand, then kept)."""
+    key = str(device)
+    have = _scratch.get(key)
+    if have is None or have.numel() < nbytes:
+        with torch.inference_mode(False):
+            _scratch[key] = have = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+    return have
+
+
+def decode_splits(requests: int, nkv: int, max_ctx_len: int) -> int:
+    """How many ways the keys of a request are split in decode: enough blocks to fill the GPU,
+    but no split shorter than two tiles of 32 keys."""
+    tiles = max(1, -(-max_ctx_len // 32))
+    want = max(1, (4 * SM_COUNT) // max(1, requests * nkv))
+    return int(max(1, min(want, tiles // 2)))
+
+
+def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
+                     scale, window, splits, out=None):
+    """Tensor-core decode attention (one token per request), keys split ``splits`` ways."""
+    if out is None:
+        out = torch.empty((requests, nq * d), dtype=torch.bfloat16, device=k_cache.device)
+    lib = _bf16()
+    lib.fe_paged_decode_scratch_bytes.restype = _c_ll
+    need = lib.fe_paged_decode_scratch_bytes(_c_int(requests), _c_int(nq), _c_int(d), _c_int(splits))
+    work = scratch(k_cache.device, need) if need else None
+    _run(lib, "fe_paged_decode_mma", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(work),
+         _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
+         _c_int(requests), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
+         _c_float(scale), _c_int(window), _c_int(splits), _ptr(status_word(k_cache.device)), _stream())
+    return out
+
+
+def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
+                      page_size, scale, window):
+    """Tensor-core attention for portions of any length (decoded tokens are portions of one)."""
+    out = torch.empty((T, nq * d), dtype=torch.bfloat16, device=k_cache.device)
+    _run(_bf16(), "fe_paged_prefill_mma", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
+         _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
+         _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
+         _c_float(scale), _c_int(window), _ptr(status_word(k_cache.device)), _stream())
+    return out
+
+
 def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window):
     """Causal grouped-query attention of the step's tokens over their requests' pages.
-    qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d]."""
+    qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d].
+    float32 runs on CUDA cores (true 32-bit); bfloat16 on tensor cores: the split-KV decode
+    kernel when every request brings one token, else the prefill kernel."""
     _need_cuda(qkv, k_cache, v_cache, block_table)
     T = qkv.shape[0]
     if qkv.dtype != k_cache.dtype:
         raise TypeError("queries and cache differ in dtype")
-    return paged_attention_simt(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start,
-                                ctx.token_request, T, nq, nkv, d, page_size, scale, window)
+    if qkv.dtype == torch.float32:
+        return paged_attention_simt(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start,
+                                    ctx.token_request, T, nq, nkv, d, page_size, scale, window)
+    requests = ctx.cu_q.numel() - 1
+    if ctx.max_q_len == 1 and nq // nkv <= 16:
+        splits = decode_splits(requests, nkv, ctx.max_ctx_len)
+        return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
+                                nq, nkv, d, page_size, scale, window, splits)
+    return paged_prefill_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
+                             ctx.max_q_len, nq, nkv, d, page_size, scale, window)
 
 
 def sample(logits, temperature, top_k, seed, draw):

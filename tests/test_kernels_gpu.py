@@ -133,7 +133,8 @@ def test_qkv_bias_rope_cache(dtype, nq, nkv, d, rot, ps, gen):
     ops().check_status(DEV)
 
 
-def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None):
+def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None, splits=None,
+                    simt=False):
     """chunks: [(start, n)] per request.  Fills the cache for positions < start + n."""
     R = len(chunks)
     lens = [s + n for s, n in chunks]
@@ -171,13 +172,21 @@ def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered
     for _, n in chunks:
         cu.append(cu[-1] + n)
     ctx = types.SimpleNamespace(
+        max_q_len=max(n for _, n in chunks), max_ctx_len=max(lens),
         cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
         q_start=torch.tensor([s for s, _ in chunks], dtype=torch.int32, device=DEV),
         token_request=torch.tensor([r for r, (_, n) in enumerate(chunks) for _ in range(n)], dtype=torch.int32, device=DEV))
     bt = bt.to(DEV)
     scale = 1.0 / math.sqrt(d)
-    got = ops().paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
     want = kernel_refs.paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
+    if splits is not None:            # the split-KV decode kernel, asked for by name
+        got = ops().paged_decode_mma(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, R, nq, nkv, d, ps, scale,
+                                     window, splits)
+    elif simt:
+        got = ops().paged_attention_simt(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, ctx.token_request, T,
+                                         nq, nkv, d, ps, scale, window)
+    else:
+        got = ops().paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
     return got, want, chunks
 
 
@@ -213,6 +222,39 @@ def test_paged_attention_finds_a_far_key(dtype, far, gen):
     got, want, chunks = _attention_case(dtype, 4, 2, 64, 16, [(799, 1), (3, 2)], 0, gen, boost=far)
     torch.testing.assert_close(got.float(), want.float(), **bar(dtype))
     assert float((got[0].float() - 10.0).abs().max()) < 0.5
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 40])
+@pytest.mark.parametrize("nq,nkv,d,ps", [(4, 2, 16, 16), (6, 1, 32, 32), (6, 3, 48, 16), (28, 4, 128, 16), (16, 1, 64, 8),
+                                         (2, 2, 256, 16), (5, 5, 80, 64)])
+def test_split_kv_decode_kernel(nq, nkv, d, ps, splits, gen):
+    # one token per request at contexts around tile (32), page and split edges
+    chunks = [(p, 1) for p in (0, 1, 15, 16, 31, 32, 33, 63, 64, 100, 255, 256, 700, 1023)]
+    got, want, _ = _attention_case(torch.bfloat16, nq, nkv, d, ps, chunks, 0, gen, splits=splits)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
+
+
+@pytest.mark.parametrize("window", [1, 31, 32, 33, 200])
+def test_split_kv_decode_kernel_window_and_far_key(window, gen):
+    chunks = [(p, 1) for p in (0, 5, 40, 64, 300, 999)]
+    for splits in (1, 4):
+        got, want, _ = _attention_case(torch.bfloat16, 8, 2, 64, 16, chunks, window, gen, splits=splits)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    for far in (0, 17, 333, 798):
+        got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(799, 1), (3, 1)], 0, gen, boost=far, splits=5)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+        assert float((got[0].float() - 10.0).abs().max()) < 0.5
+
+
+def test_bfloat16_on_cuda_cores_for_shapes_the_tensor_core_kernels_refuse(gen):
+    # 24 query heads on one key/value head is beyond the decode kernel's 16: the dispatch takes another path
+    got, want, _ = _attention_case(torch.bfloat16, 24, 1, 32, 16, [(40, 1), (7, 1)], 0, gen)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    got, want, _ = _attention_case(torch.bfloat16, 6, 2, 48, 16, [(40, 1), (0, 37)], 0, gen, simt=True)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    with pytest.raises(RuntimeError, match="up to 16"):
+        _attention_case(torch.bfloat16, 24, 1, 32, 16, [(40, 1)], 0, gen, splits=2)
 
 
 def test_sample_greedy_and_ties():
