@@ -185,9 +185,10 @@ def run_ours(args):
         greedy(logits)
         runner.finish(rid)
     prompt_ids = prompt()
-    for w in range(max(args.warmup, 3)):
-        prefill_once(-1 - w)
-    prefill_ms, _ = timed(prefill_once, 3)
+    if args.profile != "decode":
+        for w in range(max(args.warmup, 3)):
+            prefill_once(-1 - w)
+    prefill_ms, _ = timed(prefill_once, 3 if not args.profile else 0) if not args.profile else (1.0, 0)
     flops = prefill_flops(cfg, PROMPT_LEN)
     prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
                "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12)}
@@ -210,6 +211,28 @@ def run_ours(args):
         return ms, launches, ctx
 
     warmup = max(args.warmup, 3)
+    if args.profile:
+        # for a profiler started with --profile-from-start off: only this region is captured
+        if args.profile == "prefill":
+            torch.cuda.profiler.start()
+            prefill_once(100)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        else:
+            rids = [f"x{i}" for i in range(args.batch)]
+            for rid in rids:
+                cache.reserve(rid, PROMPT_LEN)
+                cache.commit(rid, PROMPT_LEN)            # the cache holds zeros: timing does not depend on values
+            for i in range(3):
+                greedy(runner.step([StepEntry(rid, [i + 1], [0]) for rid in rids]))
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            greedy(runner.step([StepEntry(rid, [7], [0]) for rid in rids]))
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        sampler.stop()
+        print(json.dumps({"profiled": args.profile, "batch": args.batch}))
+        return 0
     ms, launches, ctx = decode(args.batch, args.steps, warmup)
     value = args.batch / (ms / 1e3)
     achieved = decode_bytes(cfg, args.batch, ctx) / (ms / 1e3) / 1e9
@@ -281,7 +304,9 @@ def main():
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     p.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
-    p.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=False)
+    p.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                   help="run one decode step or one prefill between cudaProfilerStart/Stop and exit")
+    p.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=True)
     args = p.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this engine has no multi-GPU path (asked for --gpus {args.gpus})")

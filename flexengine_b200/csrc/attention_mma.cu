@@ -23,8 +23,7 @@ using namespace fe;
 
 namespace {
 
-constexpr int TK = 32;          // keys per tile
-constexpr int STAGES = 3;       // shared-memory stages per ring
+constexpr int TK = 32;          // keys per compute tile (one key per lane when gathering)
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int src_bytes) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -53,6 +52,12 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const unsigned*>(&v);
 }
+// 2^x in float (the hardware's approximation, 2 ulp); 2^-inf = 0
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 
 // Element offset of 16-byte chunk c of row r in a tile whose rows are PITCH elements apart:
 // chunks are XOR-swizzled with the row inside each group of eight chunks.
@@ -67,102 +72,147 @@ struct KvSource {
     int nkv, kvh, d, ps, num_pages;
 };
 
-// Gather keys/values of tile ``tile`` (keys tile*TK .. +TK-1) into one stage.  Keys outside
-// [lo, hi] are filled with zeros (their scores are masked; zero values keep 0 * v finite).
-template <int DMAX, int THREADS>
-__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const KvSource& src, int tile, int lo, int hi,
-                                          int* status) {
-    const int cpr = src.d >> 3;                       // 16-byte chunks per row
-    for (int idx = threadIdx.x; idx < TK * cpr; idx += THREADS) {
-        const int r = idx / cpr, c = idx - r * cpr;
-        const int key = tile * TK + r;
-        bool valid = key >= lo && key <= hi;
-        long long off = 0;
-        if (valid) {
+// Gather ROWS keys/values starting at key ``first`` into one stage.  Keys outside [lo, hi] are
+// filled with zeros (their scores are masked; zero values keep 0 * v finite).  Lane r of every
+// warp looks up the pages of keys r, r + 32, ... once; the 16-byte copies then take their row's
+// offset by shuffle, so no copy waits on a table load of its own, and the (row, chunk) walk is
+// incremental (no division in the loop).
+template <int DMAX, int THREADS, int ROWS>
+__device__ __forceinline__ void load_stage(bf16* ks, bf16* vs, const KvSource& src, int first, int lo, int hi,
+                                           int* status) {
+    const int lane = threadIdx.x & 31;
+    long long row_off[ROWS / 32];
+#pragma unroll
+    for (int i = 0; i < ROWS / 32; ++i) {
+        const int key = first + i * 32 + lane;
+        row_off[i] = -1;
+        if (key >= lo && key <= hi) {
             const int page = src.table[key / src.ps];
             if (page < 0 || page >= src.num_pages) {
                 if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
-                valid = false;
             } else {
-                off = (((long long)page * src.nkv + src.kvh) * src.ps + (key % src.ps)) * src.d + (c << 3);
+                row_off[i] = (((long long)page * src.nkv + src.kvh) * src.ps + (key % src.ps)) * src.d;
             }
         }
-        const int o = tile_offset<DMAX>(r, c);
-        cp_async16(ks + o, src.kc + off, valid ? 16 : 0);
-        cp_async16(vs + o, src.vc + off, valid ? 16 : 0);
+    }
+    const int cpr = src.d >> 3;                       // 16-byte chunks per row
+    const int step_r = THREADS / cpr, step_c = THREADS - step_r * cpr;
+    int r = threadIdx.x / cpr, c = threadIdx.x - r * cpr;
+    const int total = ROWS * cpr;
+    for (int base = 0; base < total; base += THREADS) {
+        const bool active = base + (int)threadIdx.x < total;
+        const int rr = active ? r : 0;
+        long long off = __shfl_sync(0xffffffffu, row_off[0], rr & 31);
+#pragma unroll
+        for (int i = 1; i < ROWS / 32; ++i) {
+            const long long other = __shfl_sync(0xffffffffu, row_off[i], rr & 31);
+            if ((rr >> 5) == i) off = other;
+        }
+        if (active) {
+            const int o = tile_offset<DMAX>(r, c);
+            const bool valid = off >= 0;
+            const long long from = valid ? off + (c << 3) : 0;
+            cp_async16(ks + o, src.kc + from, valid ? 16 : 0);
+            cp_async16(vs + o, src.vc + from, valid ? 16 : 0);
+        }
+        r += step_r; c += step_c;
+        if (c >= cpr) { c -= cpr; ++r; }
     }
 }
 
-// One warp, one tile: s = Q K^T (scaled to log2 units), mask, online softmax, o += P V.
-// pos0 / pos1: positions of the queries in rows g and g + 8 (negative: the row is padding).
-template <int DMAX>
+// One warp, 32 keys: s = Q K^T, mask (only where ``masked``), online softmax in float with the
+// running maximum kept in log2 units, o += P V.  ``ks``/``vs`` point at the first of the 32 rows.
+// pos0/pos1 and lo0/lo1: last and first visible key of the queries in rows g and g + 8.
+// UPPER = false: rows 8..15 of the tile are padding and their softmax is skipped.
+template <int DMAX, bool UPPER>
 __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, const unsigned (*qfrag)[4],
-                                             float (*o)[4], float* m, float* l, int tile, int d, float scale_log2,
-                                             int pos0, int pos1, int window) {
+                                             float (*o)[4], float* m, float* l, int first_key, int d,
+                                             float scale_log2, int pos0, int pos1, int lo0, int lo1, bool masked) {
     const int lane = threadIdx.x & 31, t = lane & 3;
+    const int mat = lane >> 3, mrow = lane & 7;
     float s[TK / 8][4];
 #pragma unroll
     for (int j = 0; j < TK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    const int mat = lane >> 3, mrow = lane & 7;
+    {
+        // row = jp*16 + (mat>>1)*8 + mrow, chunk = ksx*2 + (mat&1); the swizzle is chunk ^ (row & 7)
+        const bf16* kbase = ks + ((mat >> 1) * 8 + mrow) * DMAX;
+        const int kx = (mat & 1) ^ mrow;
 #pragma unroll
-    for (int ksx = 0; ksx < DMAX / 16; ++ksx) {
-        if (ksx * 16 < d) {
+        for (int ksx = 0; ksx < DMAX / 16; ++ksx) {
+            if (ksx * 16 < d) {
 #pragma unroll
-            for (int jp = 0; jp < TK / 16; ++jp) {
-                unsigned r0, r1, r2, r3;
-                const int row = jp * 16 + (mat >> 1) * 8 + mrow;
-                ldmatrix_x4(r0, r1, r2, r3, ks + tile_offset<DMAX>(row, ksx * 2 + (mat & 1)));
-                mma16816(s[jp * 2], qfrag[ksx], r0, r1);
-                mma16816(s[jp * 2 + 1], qfrag[ksx], r2, r3);
+                for (int jp = 0; jp < TK / 16; ++jp) {
+                    unsigned r0, r1, r2, r3;
+                    ldmatrix_x4(r0, r1, r2, r3, kbase + jp * 16 * DMAX + (ksx >> 2) * 64 + ((((ksx * 2) & 7) ^ kx) << 3));
+                    mma16816(s[jp * 2], qfrag[ksx], r0, r1);
+                    mma16816(s[jp * 2 + 1], qfrag[ksx], r2, r3);
+                }
             }
         }
     }
-    const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0;
-    const int lo1 = window > 0 ? max(0, pos1 - window + 1) : 0;
+    if (masked) {
+#pragma unroll
+        for (int j = 0; j < TK / 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < (UPPER ? 4 : 2); ++e) {
+                const int key = first_key + j * 8 + 2 * t + (e & 1);
+                const bool vis = e < 2 ? (key <= pos0 && key >= lo0) : (key <= pos1 && key >= lo1);
+                if (!vis) s[j][e] = -CUDART_INF_F;
+            }
+        }
+    }
     float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
 #pragma unroll
     for (int j = 0; j < TK / 8; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int key = tile * TK + j * 8 + 2 * t + (e & 1);
-            const bool upper = e < 2;
-            const bool vis = upper ? (key <= pos0 && key >= lo0) : (key <= pos1 && key >= lo1);
-            const float v = vis ? s[j][e] * scale_log2 : -CUDART_INF_F;
-            s[j][e] = v;
-            if (upper) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-        }
+        mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+        if (UPPER) mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    if (UPPER) { mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2)); }
+    const float mn0 = fmaxf(m[0], mx0 * scale_log2), mn1 = UPPER ? fmaxf(m[1], mx1 * scale_log2) : m[1];
     const float ms0 = mn0 == -CUDART_INF_F ? 0.f : mn0, ms1 = mn1 == -CUDART_INF_F ? 0.f : mn1;
-    const float al0 = exp2f(m[0] - ms0), al1 = exp2f(m[1] - ms1);      // exp2(-inf) = 0 on the first visible tile
-    m[0] = mn0; m[1] = mn1;
+    const bool changed = mn0 != m[0] || (UPPER && mn1 != m[1]);
+    if (__any_sync(0xffffffffu, changed)) {
+        const float al0 = ex2(m[0] - ms0), al1 = UPPER ? ex2(m[1] - ms1) : 1.f;   // 2^-inf = 0 at the start
+        l[0] *= al0;
+        if (UPPER) l[1] *= al1;
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n) {
+            o[n][0] *= al0; o[n][1] *= al0;
+            if (UPPER) { o[n][2] *= al1; o[n][3] *= al1; }
+        }
+        m[0] = mn0; m[1] = mn1;
+    }
     float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
     for (int j = 0; j < TK / 8; ++j) {
-        s[j][0] = exp2f(s[j][0] - ms0); s[j][1] = exp2f(s[j][1] - ms0);
-        s[j][2] = exp2f(s[j][2] - ms1); s[j][3] = exp2f(s[j][3] - ms1);
-        sum0 += s[j][0] + s[j][1]; sum1 += s[j][2] + s[j][3];
+        s[j][0] = ex2(fmaf(s[j][0], scale_log2, -ms0)); s[j][1] = ex2(fmaf(s[j][1], scale_log2, -ms0));
+        sum0 += s[j][0] + s[j][1];
+        if (UPPER) {
+            s[j][2] = ex2(fmaf(s[j][2], scale_log2, -ms1)); s[j][3] = ex2(fmaf(s[j][3], scale_log2, -ms1));
+            sum1 += s[j][2] + s[j][3];
+        }
     }
-    l[0] = l[0] * al0 + sum0; l[1] = l[1] * al1 + sum1;                 // per-thread partial sums of the row
+    l[0] += sum0; l[1] += sum1;                       // per-thread partial sums of the rows
+    {
+        // row = kk*16 + (mat&1)*8 + mrow, chunk = np*2 + (mat>>1)
+        const bf16* vbase = vs + ((mat & 1) * 8 + mrow) * DMAX;
+        const int vx = (mat >> 1) ^ mrow;
 #pragma unroll
-    for (int n = 0; n < DMAX / 8; ++n) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
+        for (int kk = 0; kk < TK / 16; ++kk) {
+            unsigned a[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            a[1] = UPPER ? pack_bf16(s[2 * kk][2], s[2 * kk][3]) : 0u;
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            a[3] = UPPER ? pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]) : 0u;
 #pragma unroll
-    for (int kk = 0; kk < TK / 16; ++kk) {
-        unsigned a[4];
-        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-        for (int np = 0; np < DMAX / 16; ++np) {
-            if (np * 16 < d) {
-                unsigned r0, r1, r2, r3;
-                const int row = kk * 16 + (mat & 1) * 8 + mrow;
-                ldmatrix_x4_trans(r0, r1, r2, r3, vs + tile_offset<DMAX>(row, np * 2 + (mat >> 1)));
-                mma16816(o[np * 2], a, r0, r1);
-                mma16816(o[np * 2 + 1], a, r2, r3);
+            for (int np = 0; np < DMAX / 16; ++np) {
+                if (np * 16 < d) {
+                    unsigned r0, r1, r2, r3;
+                    ldmatrix_x4_trans(r0, r1, r2, r3, vbase + kk * 16 * DMAX + (np >> 2) * 64 + ((((np * 2) & 7) ^ vx) << 3));
+                    mma16816(o[np * 2], a, r0, r1);
+                    mma16816(o[np * 2 + 1], a, r2, r3);
+                }
             }
         }
     }
@@ -186,8 +236,11 @@ __device__ __forceinline__ void load_q(unsigned (*qfrag)[4], const bf16* src0, c
 }
 
 // ---------------------------------------------------------------------------------------------
-// decode: grid (splits, nkv, requests), one warp.  Every request brings exactly one token.
-template <int DMAX>
+// decode: grid (splits, nkv, requests), one warp, two stages of 32 keys.  Every request brings
+// exactly one token.
+constexpr int DECODE_STAGES = 2;
+
+template <int DMAX, bool UPPER>
 __global__ void __launch_bounds__(32)
 paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                     float* __restrict__ part_o, float* __restrict__ part_lse, const bf16* __restrict__ kc,
@@ -206,35 +259,33 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     const int tile_lo = lo / TK, tile_hi = pos / TK;
     const int per = (tile_hi - tile_lo + 1 + splits - 1) / splits;
     const int t_begin = tile_lo + split * per, t_end = min(tile_hi + 1, t_begin + per);
+    const int n_tiles = max(0, t_end - t_begin);
+
+    KvSource src{kc, vc, block_table + (size_t)b * bt_stride, nkv, kvh, d, ps, num_pages};
+    if (n_tiles > 0) load_stage<DMAX, 32, TK>(smem, smem + TILE, src, t_begin * TK, lo, pos, status);
+    cp_async_commit();
 
     unsigned qfrag[DMAX / 16][4];
     const bf16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * d;
-    load_q<DMAX>(qfrag, g < G ? qrow + (size_t)g * d : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * d : nullptr, d);
+    load_q<DMAX>(qfrag, g < G ? qrow + (size_t)g * d : nullptr, (UPPER && g + 8 < G) ? qrow + (size_t)(g + 8) * d : nullptr, d);
 
     float o[DMAX / 8][4];
 #pragma unroll
     for (int n = 0; n < DMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
 
-    KvSource src{kc, vc, block_table + (size_t)b * bt_stride, nkv, kvh, d, ps, num_pages};
-    const int n_tiles = max(0, t_end - t_begin);
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_tiles) load_tile<DMAX, 32>(smem + s * 2 * TILE, smem + s * 2 * TILE + TILE, src, t_begin + s, lo, pos, status);
-        cp_async_commit();
-    }
     for (int it = 0; it < n_tiles; ++it) {
-        cp_async_wait<STAGES - 2>();
+        cp_async_wait<0>();
         __syncwarp();
-        const int nxt = it + STAGES - 1;
-        if (nxt < n_tiles) {
-            const int st = nxt % STAGES;
-            load_tile<DMAX, 32>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, src, t_begin + nxt, lo, pos, status);
+        if (it + 1 < n_tiles) {
+            bf16* st = smem + ((it + 1) & 1) * 2 * TILE;
+            load_stage<DMAX, 32, TK>(st, st + TILE, src, (t_begin + it + 1) * TK, lo, pos, status);
         }
         cp_async_commit();
-        const int st = it % STAGES;
-        compute_tile<DMAX>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, qfrag, o, m, l, t_begin + it, d,
-                           scale_log2, pos, pos, window);
+        const bf16* st = smem + (it & 1) * 2 * TILE;
+        const int first = (t_begin + it) * TK;
+        compute_tile<DMAX, UPPER>(st, st + TILE, qfrag, o, m, l, first, d, scale_log2, pos, pos, lo, lo,
+                                  first + TK - 1 > pos || first < lo);
         __syncwarp();
     }
     cp_async_wait<0>();
@@ -244,7 +295,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < (UPPER ? 2 : 1); ++i) {
         const int row = g + 8 * i;
         if (row >= G) continue;
         const int head = kvh * G + row;
@@ -293,10 +344,13 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 }
 
 // ---------------------------------------------------------------------------------------------
-// prefill: grid (row tiles, nkv, requests), four warps.  Row m of a (request, kv head) is the pair
-// (query m / G, head m % G of the group); a block takes 64 consecutive rows.
+// prefill: grid (row tiles, nkv, requests), four warps, two stages of 64 keys.  Row m of a
+// (request, kv head) is the pair (query m / G, head m % G of the group); a block takes 64
+// consecutive rows; blocks with the most keys to walk (the last rows) are scheduled first.
 constexpr int PREFILL_WARPS = 4;
 constexpr int PREFILL_ROWS = PREFILL_WARPS * 16;
+constexpr int PREFILL_KEYS = 64;                 // keys per stage
+constexpr int PREFILL_STAGES = 2;
 
 template <int DMAX>
 __global__ void __launch_bounds__(PREFILL_WARPS * 32)
@@ -306,13 +360,13 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
                      int d, int ps, int num_pages, float scale_log2, int window, int* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    constexpr int TILE = TK * DMAX;
+    constexpr int STAGE = PREFILL_KEYS * DMAX;       // elements per K (or V) stage
     constexpr int THREADS = PREFILL_WARPS * 32;
     const int kvh = blockIdx.y, r = blockIdx.z;
     const int G = nq / nkv;
     const int tok0 = cu_q[r], n_q = cu_q[r + 1] - tok0;
     const int rows = n_q * G;
-    const int m_block = blockIdx.x * PREFILL_ROWS;
+    const int m_block = (gridDim.x - 1 - blockIdx.x) * PREFILL_ROWS;
     if (m_block >= rows) return;
     const int start = q_start[r];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -320,7 +374,17 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
     const bool v0 = m0 < rows, v1 = m1 < rows;
     const int qi0 = v0 ? m0 / G : 0, qi1 = v1 ? m1 / G : 0;
     const int pos0 = v0 ? start + qi0 : -1, pos1 = v1 ? start + qi1 : -1;
+    const int lo0 = window > 0 ? max(0, pos0 - window + 1) : 0, lo1 = window > 0 ? max(0, pos1 - window + 1) : 0;
     const int head0 = kvh * G + (v0 ? m0 % G : 0), head1 = kvh * G + (v1 ? m1 % G : 0);
+
+    // keys this block needs: from the window edge of its first query to its last query
+    const int qi_first = m_block / G, qi_last = min(n_q - 1, (m_block + PREFILL_ROWS - 1) / G);
+    const int hi = start + qi_last;
+    const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
+    const int s_begin = lo / PREFILL_KEYS, n_stages = hi / PREFILL_KEYS - s_begin + 1;
+    KvSource src{kc, vc, block_table + (size_t)r * bt_stride, nkv, kvh, d, ps, num_pages};
+    load_stage<DMAX, THREADS, PREFILL_KEYS>(smem, smem + STAGE, src, s_begin * PREFILL_KEYS, lo, hi, status);
+    cp_async_commit();
 
     unsigned qfrag[DMAX / 16][4];
     load_q<DMAX>(qfrag, v0 ? q + (size_t)(tok0 + qi0) * q_stride + (size_t)head0 * d : nullptr,
@@ -330,36 +394,31 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
     for (int n = 0; n < DMAX / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
 
-    // keys this block needs: from the window edge of its first query to its last query
-    const int qi_first = m_block / G, qi_last = min(n_q - 1, (m_block + PREFILL_ROWS - 1) / G);
-    const int hi = start + qi_last;
-    const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
-    const int t_begin = lo / TK, n_tiles = hi / TK - t_begin + 1;
-    // this warp's rows see no key beyond its last valid row's position
-    const int warp_last = min(rows - 1, m_block + warp * 16 + 15);
-    const int warp_hi = warp_last >= m_block + warp * 16 ? start + warp_last / G : -1;
-    const int warp_lo = window > 0 ? max(0, start + (m_block + warp * 16) / G - window + 1) : 0;
+    // this warp's rows: the first and last position any of them has, and the widest window edge
+    const int w_first = m_block + warp * 16, w_last = min(rows - 1, w_first + 15);
+    const bool w_any = w_first < rows;
+    const int w_pos_min = w_any ? start + w_first / G : -1, w_pos_max = w_any ? start + w_last / G : -1;
+    const int w_lo_min = window > 0 ? max(0, w_pos_min - window + 1) : 0;
+    const int w_lo_max = window > 0 ? max(0, w_pos_max - window + 1) : 0;
 
-    KvSource src{kc, vc, block_table + (size_t)r * bt_stride, nkv, kvh, d, ps, num_pages};
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < n_tiles) load_tile<DMAX, THREADS>(smem + s * 2 * TILE, smem + s * 2 * TILE + TILE, src, t_begin + s, lo, hi, status);
-        cp_async_commit();
-    }
-    for (int it = 0; it < n_tiles; ++it) {
-        cp_async_wait<STAGES - 2>();
-        __syncthreads();                 // tile ``it`` has landed; everyone is done with tile it - 1
-        const int nxt = it + STAGES - 1;
-        if (nxt < n_tiles) {
-            const int st = nxt % STAGES;
-            load_tile<DMAX, THREADS>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, src, t_begin + nxt, lo, hi, status);
+    for (int it = 0; it < n_stages; ++it) {
+        cp_async_wait<0>();
+        __syncthreads();                 // stage ``it`` has landed; everyone is done with stage it - 1
+        if (it + 1 < n_stages) {
+            bf16* st = smem + ((it + 1) & 1) * 2 * STAGE;
+            load_stage<DMAX, THREADS, PREFILL_KEYS>(st, st + STAGE, src, (s_begin + it + 1) * PREFILL_KEYS, lo, hi, status);
         }
         cp_async_commit();
-        const int tile = t_begin + it;
-        if (tile * TK <= warp_hi && tile * TK + TK - 1 >= warp_lo) {
-            const int st = it % STAGES;
-            compute_tile<DMAX>(smem + st * 2 * TILE, smem + st * 2 * TILE + TILE, qfrag, o, m, l, tile, d,
-                               scale_log2, pos0, pos1, window);
+        const bf16* st = smem + (it & 1) * 2 * STAGE;
+#pragma unroll
+        for (int sub = 0; sub < PREFILL_KEYS / TK; ++sub) {
+            const int first = (s_begin + it) * PREFILL_KEYS + sub * TK;
+            if (w_any && first <= w_pos_max && first + TK - 1 >= w_lo_min) {
+                // rows differ in what they see only near the diagonal and the window edge
+                const bool masked = first + TK - 1 > w_pos_min || first < w_lo_max || !(v0 && v1);
+                compute_tile<DMAX, true>(st + sub * TK * DMAX, st + STAGE + sub * TK * DMAX, qfrag, o, m, l, first, d,
+                                         scale_log2, pos0, pos1, lo0, lo1, masked);
+            }
         }
     }
     cp_async_wait<0>();
@@ -385,7 +444,8 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
 
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int DMAX> size_t ring_bytes() { return (size_t)STAGES * 2 * TK * DMAX * sizeof(bf16); }
+template <int DMAX> size_t decode_smem() { return (size_t)DECODE_STAGES * 2 * TK * DMAX * sizeof(bf16); }
+template <int DMAX> size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * PREFILL_KEYS * DMAX * sizeof(bf16); }
 
 template <typename K> int allow_smem(K kernel, size_t bytes, const char* what) {
     if (bytes > 48 * 1024) {
@@ -430,16 +490,17 @@ extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out,
     float* part_lse = part_o ? part_o + (size_t)requests * nq * splits * d : nullptr;
     const dim3 grid(splits, nkv, requests);
     const float scale_log2 = scale * LOG2E;
-#define FE_DECODE(DMAX)                                                                                           \
+#define FE_DECODE(DMAX, UPPER)                                                                                    \
     do {                                                                                                          \
-        if (allow_smem(paged_decode_kernel<DMAX>, ring_bytes<DMAX>(), "paged_decode")) return 1;                  \
-        paged_decode_kernel<DMAX><<<grid, 32, ring_bytes<DMAX>(), stream>>>(                                      \
+        if (allow_smem(paged_decode_kernel<DMAX, UPPER>, decode_smem<DMAX>(), "paged_decode")) return 1;          \
+        paged_decode_kernel<DMAX, UPPER><<<grid, 32, decode_smem<DMAX>(), stream>>>(                              \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, part_o, part_lse, (const bf16*)kc, (const bf16*)vc, \
             block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);        \
     } while (0)
-    if (d <= 64) FE_DECODE(64);
-    else if (d <= 128) FE_DECODE(128);
-    else FE_DECODE(256);
+    const bool upper = nq / nkv > 8;
+    if (d <= 64) { if (upper) FE_DECODE(64, true); else FE_DECODE(64, false); }
+    else if (d <= 128) { if (upper) FE_DECODE(128, true); else FE_DECODE(128, false); }
+    else { if (upper) FE_DECODE(256, true); else FE_DECODE(256, false); }
 #undef FE_DECODE
     if (fe_check_launch("paged_decode")) return 2;
     if (splits > 1) {
@@ -465,8 +526,8 @@ extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out
     const float scale_log2 = scale * LOG2E;
 #define FE_PREFILL(DMAX)                                                                                       \
     do {                                                                                                       \
-        if (allow_smem(paged_prefill_kernel<DMAX>, ring_bytes<DMAX>(), "paged_prefill")) return 1;             \
-        paged_prefill_kernel<DMAX><<<grid, PREFILL_WARPS * 32, ring_bytes<DMAX>(), stream>>>(                  \
+        if (allow_smem(paged_prefill_kernel<DMAX>, prefill_smem<DMAX>(), "paged_prefill")) return 1;           \
+        paged_prefill_kernel<DMAX><<<grid, PREFILL_WARPS * 32, prefill_smem<DMAX>(), stream>>>(                \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table,  \
             bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);                  \
     } while (0)

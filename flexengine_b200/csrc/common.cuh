@@ -76,6 +76,23 @@ template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* ou
     }
 }
 
+// Store 8 consecutive elements from floats (same alignment as load8).
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* v);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float* v) {
+    uint4 raw;
+    unsigned* w = reinterpret_cast<unsigned*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const unsigned*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
 }  // namespace fe
 
 // Host side: the last error message of this thread, and a checked launch epilogue.

@@ -67,30 +67,93 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>(row[j] * inv * weight[j]);
 }
 
+// The same, four elements at a time (H % 4 == 0): 16-byte loads and stores of the float residual.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                           __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const unsigned*>(&a);
+        raw.y = *reinterpret_cast<const unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, float eps, T* __restrict__ out,
+                                       const int* __restrict__ rows, int H, int n_rows_total) {
+    extern __shared__ float row[];
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    int r = rows ? rows[i] : i;
+    if (r < 0 || r >= n_rows_total) r = 0;
+    float* res = residual + (size_t)r * H;
+    const T* del = delta ? delta + (size_t)r * H : nullptr;
+    float ss = 0.f;
+    for (int j = threadIdx.x * 4; j < H; j += blockDim.x * 4) {
+        float4 v = *reinterpret_cast<const float4*>(res + j);
+        if (del) {
+            const float4 dv = Vec4<T>::load(del + j);
+            v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            if (!rows) *reinterpret_cast<float4*>(res + j) = v;
+        }
+        *reinterpret_cast<float4*>(row + j) = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)H + eps);
+    T* o = out + (size_t)i * H;
+    for (int j = threadIdx.x * 4; j < H; j += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + j);
+        const float4 w = *reinterpret_cast<const float4*>(weight + j);
+        Vec4<T>::store(o + j, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+    }
+}
+
+template <typename T>
+static int launch_add_rmsnorm(float* residual, const void* delta, const float* weight, float eps, void* out,
+                              const int* rows, int n_out, int H, int n_rows_total, cudaStream_t stream) {
+    const size_t smem = (size_t)H * sizeof(float);
+    const bool vec = H % 4 == 0;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    cudaError_t err = cudaSuccess;
+    if (vec) {
+        if (smem > 48 * 1024)
+            err = cudaFuncSetAttribute(add_rmsnorm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
+        add_rmsnorm_vec_kernel<T><<<n_out, threads, smem, stream>>>(residual, (const T*)delta, weight, eps, (T*)out,
+                                                                    rows, H, n_rows_total);
+    } else {
+        if (smem > 48 * 1024)
+            err = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
+        add_rmsnorm_kernel<T><<<n_out, threads, smem, stream>>>(residual, (const T*)delta, weight, eps, (T*)out, rows,
+                                                                H, n_rows_total);
+    }
+    return fe_check_launch("add_rmsnorm");
+}
+
 extern "C" int fe_add_rmsnorm(float* residual, const void* delta, const float* weight, float eps, void* out,
                               const int* rows, int n_out, int H, int n_rows_total, int dtype, cudaStream_t stream) {
     FE_REQUIRE(n_out >= 0 && H > 0, "add_rmsnorm: bad sizes n=%d H=%d", n_out, H);
     if (n_out == 0) return 0;
-    const size_t smem = (size_t)H * sizeof(float);
-    FE_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory (limit 204800)", H, smem);
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    cudaError_t err = cudaSuccess;
-    if (dtype == FE_F32) {
-        if (smem > 48 * 1024)
-            err = cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
-        add_rmsnorm_kernel<float><<<n_out, threads, smem, stream>>>(residual, (const float*)delta, weight, eps,
-                                                                     (float*)out, rows, H, n_rows_total);
-    } else if (dtype == FE_BF16) {
-        if (smem > 48 * 1024)
-            err = cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
-        add_rmsnorm_kernel<bf16><<<n_out, threads, smem, stream>>>(residual, (const bf16*)delta, weight, eps,
-                                                                    (bf16*)out, rows, H, n_rows_total);
-    } else {
-        FE_REQUIRE(false, "add_rmsnorm: unknown dtype %d", dtype);
-    }
-    return fe_check_launch("add_rmsnorm");
+    FE_REQUIRE((size_t)H * sizeof(float) <= 200 * 1024,
+               "add_rmsnorm: hidden size %d needs %zu bytes of shared memory (limit 204800)", H, (size_t)H * sizeof(float));
+    if (dtype == FE_F32)
+        return launch_add_rmsnorm<float>(residual, delta, weight, eps, out, rows, n_out, H, n_rows_total, stream);
+    if (dtype == FE_BF16)
+        return launch_add_rmsnorm<bf16>(residual, delta, weight, eps, out, rows, n_out, H, n_rows_total, stream);
+    FE_REQUIRE(false, "add_rmsnorm: unknown dtype %d", dtype);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -151,25 +214,107 @@ __global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __r
     }
 }
 
+// The same for head sizes and rotary widths that are multiples of 16: one block per token; sine
+// and cosine of the token's angles are computed once (they do not depend on the head) and
+// every thread moves eight elements of each half at a time.
+template <typename T>
+__global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+                                               const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                               int rot, const int* __restrict__ slot_mapping, T* __restrict__ kc,
+                                               T* __restrict__ vc, int nq, int nkv, int d, int ps,
+                                               long long num_slots, int* __restrict__ status) {
+    extern __shared__ float trig[];                  // cos [rot/2], sin [rot/2]
+    const int t = blockIdx.x;
+    const int half = rot / 2;
+    const bool rotary = inv_freq != nullptr && rot > 0;
+    if (rotary) {
+        const float pos = (float)positions[t];
+        for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &trig[half + j], &trig[j]);
+    }
+    long long slot = slot_mapping ? slot_mapping[t] : -1;
+    if (slot >= num_slots) {
+        if (threadIdx.x == 0 && status) atomicOr(status, FE_STATUS_BAD_SLOT);
+        slot = -1;
+    }
+    __syncthreads();
+    const int heads = nq + 2 * nkv;
+    const int width = heads * d;
+    T* x = qkv + (size_t)t * width;
+    // unit = (head, group of 8 elements of the first half of the rotated part, or of the rest)
+    const int rot_units = rotary ? half / 8 : 0, rest_units = (d - (rotary ? rot : 0)) / 8;
+    const int per_head = rot_units + rest_units;
+    for (int u = threadIdx.x; u < heads * per_head; u += blockDim.x) {
+        const int head = u / per_head, k = u - head * per_head;
+        const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
+        T* hx = x + (size_t)head * d;
+        const float* hb = bias ? bias + (size_t)head * d : nullptr;
+        T* dst = nullptr;
+        if (!is_q && slot >= 0) {
+            const int kvh = is_k ? head - nq : head - nq - nkv;
+            dst = (is_k ? kc : vc) + (((slot / ps) * nkv + kvh) * ps + (slot % ps)) * d;
+        }
+        if (k < rot_units && (is_q || is_k)) {
+            const int j = k * 8;
+            float a[8], c[8];
+            load8<T>(hx + j, a);
+            load8<T>(hx + j + half, c);
+            float ra[8], rc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float av = a[e], cv = c[e];
+                if (hb) { av += hb[j + e]; cv += hb[j + half + e]; }
+                const float cs = trig[j + e], sn = trig[half + j + e];
+                ra[e] = av * cs - cv * sn;
+                rc[e] = cv * cs + av * sn;
+            }
+            store8<T>(hx + j, ra);
+            store8<T>(hx + j + half, rc);
+            if (dst) { store8<T>(dst + j, ra); store8<T>(dst + j + half, rc); }
+        } else {
+            // a value head's "rotated" range, or the part of the head beyond the rotary width
+            int j;
+            if (k < rot_units) j = k * 8;
+            else j = (rotary ? rot : 0) + (k - rot_units) * 8;
+            for (int rep = 0; rep < ((k < rot_units) ? 2 : 1); ++rep, j += half) {
+                float a[8];
+                load8<T>(hx + j, a);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) if (hb) a[e] += hb[j + e];
+                store8<T>(hx + j, a);
+                if (dst) store8<T>(dst + j, a);
+            }
+        }
+    }
+}
+
+template <typename T>
+static int launch_rope(void* qkv, const float* bias, const int* positions, const float* inv_freq, int rot,
+                       const int* slot_mapping, void* kc, void* vc, int T_tokens, int nq, int nkv, int d, int ps,
+                       long long num_slots, int* status, cudaStream_t stream) {
+    if (d % 16 == 0 && rot % 16 == 0) {
+        const int units = (nq + 2 * nkv) * (d / 8 - (inv_freq && rot ? rot / 16 : 0));
+        const int threads = units >= 256 ? 256 : (units >= 128 ? 128 : 64);
+        qkv_bias_rope_cache_vec_kernel<T><<<T_tokens, threads, (size_t)rot * sizeof(float), stream>>>(
+            (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
+    } else {
+        const dim3 grid(T_tokens, nq + 2 * nkv);
+        qkv_bias_rope_cache_kernel<T><<<grid, d / 2 >= 64 ? 64 : 32, 0, stream>>>(
+            (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
+    }
+    return fe_check_launch("qkv_bias_rope_cache");
+}
+
 extern "C" int fe_qkv_bias_rope_cache(void* qkv, const float* bias, const int* positions, const float* inv_freq,
                                       int rot, const int* slot_mapping, void* kc, void* vc, int T, int nq, int nkv,
                                       int d, int ps, long long num_slots, int dtype, int* status, cudaStream_t stream) {
     FE_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && d > 0 && ps > 0, "qkv_bias_rope_cache: bad sizes");
     FE_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "qkv_bias_rope_cache: rotary width %d does not fit head size %d", rot, d);
     if (T == 0) return 0;
-    const dim3 grid(T, nq + 2 * nkv);
-    const int threads = d / 2 >= 64 ? 64 : 32;
     if (dtype == FE_F32)
-        qkv_bias_rope_cache_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, bias, positions, inv_freq, rot,
-                                                                        slot_mapping, (float*)kc, (float*)vc, nq, nkv,
-                                                                        d, ps, num_slots, status);
-    else if (dtype == FE_BF16)
-        qkv_bias_rope_cache_kernel<bf16><<<grid, threads, 0, stream>>>((bf16*)qkv, bias, positions, inv_freq, rot,
-                                                                       slot_mapping, (bf16*)kc, (bf16*)vc, nq, nkv, d,
-                                                                       ps, num_slots, status);
-    else
-        FE_REQUIRE(false, "qkv_bias_rope_cache: unknown dtype %d", dtype);
-    return fe_check_launch("qkv_bias_rope_cache");
+        return launch_rope<float>(qkv, bias, positions, inv_freq, rot, slot_mapping, kc, vc, T, nq, nkv, d, ps, num_slots, status, stream);
+    if (dtype == FE_BF16)
+        return launch_rope<bf16>(qkv, bias, positions, inv_freq, rot, slot_mapping, kc, vc, T, nq, nkv, d, ps, num_slots, status, stream);
+    FE_REQUIRE(false, "qkv_bias_rope_cache: unknown dtype %d", dtype);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -185,18 +330,37 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     }
 }
 
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long units, int I) {
+    const int per_row = I / 8;
+    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += (long long)gridDim.x * blockDim.x) {
+        const long long t = u / per_row;
+        const int i = (int)(u - t * per_row) * 8;
+        float g[8], up[8], r[8];
+        load8<T>(gate_up + t * 2 * I + i, g);
+        load8<T>(gate_up + t * 2 * I + I + i, up);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) r[e] = g[e] / (1.f + expf(-g[e])) * up[e];
+        store8<T>(out + t * I + i, r);
+    }
+}
+
 extern "C" int fe_swiglu(const void* gate_up, void* out, int T, int I, int dtype, cudaStream_t stream) {
     FE_REQUIRE(T >= 0 && I > 0, "swiglu: bad sizes");
     if (T == 0) return 0;
-    const long long total = (long long)T * I;
+    const bool vec = I % 8 == 0;
+    const long long total = vec ? (long long)T * (I / 8) : (long long)T * I;
     const int threads = 256;
     long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    if (dtype == FE_F32)
-        swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, I);
-    else if (dtype == FE_BF16)
-        swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, I);
-    else
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == FE_F32) {
+        if (vec) swiglu_vec_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, I);
+        else swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, I);
+    } else if (dtype == FE_BF16) {
+        if (vec) swiglu_vec_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, I);
+        else swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, I);
+    } else {
         FE_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
+    }
     return fe_check_launch("swiglu");
 }

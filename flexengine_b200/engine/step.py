@@ -83,6 +83,9 @@ class ModelRunner:
         self._ring_at = 0
         self.steps_run = 0
         self.h2d_bytes = 0           # bytes of step metadata copied to the device so far
+        self._graph_buckets = []
+        self._graphs = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------------------------------
     def _check(self, entries) -> None:
@@ -141,15 +144,20 @@ class ModelRunner:
             slot[0] = torch.empty(max(count, 2 * slot[0].numel()), dtype=torch.int32, pin_memory=True)
         return slot[0][:count]
 
-    def _upload(self, arrays: list) -> list:
-        """One host buffer, one transfer; returns device views in the order given."""
-        sizes = [len(a) for a in arrays]
-        # every piece starts on a 16-byte boundary so that kernels may use vector loads
+    @staticmethod
+    def _layout(sizes: list):
+        """Offsets of the pieces in one buffer; every piece starts on a 16-byte boundary."""
         offsets, total = [], 0
         for s in sizes:
             offsets.append(total)
             total += (s + 3) // 4 * 4
-        total = max(total, 4)
+        return offsets, max(total, 4)
+
+    def _upload(self, arrays: list, into=None) -> list:
+        """One host buffer, one transfer; returns device views in the order given.  ``into``: a
+        device buffer of fixed address to copy into (CUDA graphs), else a fresh one."""
+        sizes = [len(a) for a in arrays]
+        offsets, total = self._layout(sizes)
         if self.device.type == "cuda":
             host = self._staging(total)
         else:
@@ -160,74 +168,171 @@ class ModelRunner:
                 view[o:o + s] = a
         self.h2d_bytes += total * 4
         if self.device.type == "cuda":
-            dev = host.to(self.device, non_blocking=True)
+            if into is not None:
+                into[:total].copy_(host, non_blocking=True)
+                dev = into
+            else:
+                dev = host.to(self.device, non_blocking=True)
             self._ring[self._ring_at][1].record()       # the copy out of this buffer is done after this
         else:
             dev = host.clone()
         return [dev[o:o + s] for o, s in zip(offsets, sizes)]
 
     # ------------------------------------------------------------------------------------------
-    def build_context(self, entries) -> StepContext:
+    def _metadata(self, entries, pad_to: int = 0, max_pages: int = 0):
+        """The step's index arrays on the host.  ``pad_to`` > len(entries) appends padding requests of
+        one token each (token 0 at position 0, no cache write, state slot -1, page 0) so that a
+        batch fits a fixed shape; ``max_pages`` fixes the width of the block tables."""
+        cache = self.cache
+        starts = [cache.tokens_of(e.request_id) for e in entries]
+        lengths = [len(e.tokens) for e in entries]
+        pad = max(0, pad_to - len(entries))
+        token_ids = [t for e in entries for t in e.tokens] + [0] * pad
+        positions = [p for s, n in zip(starts, lengths) for p in range(s, s + n)] + [0] * pad
+        all_lengths = lengths + [1] * pad
+        all_starts = starts + [0] * pad
+        R = len(all_lengths)
+        token_request = [r for r, n in enumerate(all_lengths) for _ in range(n)]
+        cu_q = [0]
+        for n in all_lengths:
+            cu_q.append(cu_q[-1] + n)
+        ctx_len = [s + n for s, n in zip(all_starts, all_lengths)]
+        state_slots = [cache.requests[e.request_id].state_slot for e in entries] + [-1] * pad
+        logit_rows = [cu_q[r] + w for r, e in enumerate(entries) for w in e.want]
+        if pad_to:
+            logit_rows = list(range(R))          # a fixed shape: every request's one row, padding too
+        arrays = [np.asarray(token_ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
+                  np.asarray(token_request, dtype=np.int32), np.asarray(cu_q, dtype=np.int32),
+                  np.asarray(all_starts, dtype=np.int32), np.asarray(ctx_len, dtype=np.int32),
+                  np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32)]
+        widths = []
+        for gi, g in enumerate(cache.groups):
+            if not isinstance(g, PagedGroup):
+                widths.append(0)
+                continue
+            slots = []
+            for e, s, n in zip(entries, starts, lengths):
+                slots.extend(cache.slot_mapping(e.request_id, gi, s, n))
+            slots += [-1] * pad
+            width = max_pages or max(1, max(-(-c // cache.page_size) for c in ctx_len))
+            bt = np.full((R, width), -1, dtype=np.int32)
+            for r, e in enumerate(entries):
+                t = cache.table(e.request_id, gi)
+                k = min(len(t), width)
+                bt[r, :k] = t[:k]
+            bt[len(entries):, :] = 0
+            arrays += [np.asarray(slots, dtype=np.int32), bt.reshape(-1)]
+            widths.append(width)
+        info = dict(T=len(token_ids), R=R, rows=len(logit_rows), starts=all_starts, lengths=all_lengths,
+                    state_slots=state_slots, widths=widths, max_q_len=max(all_lengths), max_ctx_len=max(ctx_len),
+                    request_ids=[e.request_id for e in entries])
+        return arrays, info
+
+    def _context(self, dev: list, info: dict) -> StepContext:
         cache = self.cache
         ctx = StepContext()
         ctx.ops, ctx.dtype, ctx.device = self.ops, self.model.dtype, self.device
-        starts = [cache.tokens_of(e.request_id) for e in entries]
-        lengths = [len(e.tokens) for e in entries]
-        T, R = sum(lengths), len(entries)
-        token_ids = [t for e in entries for t in e.tokens]
-        positions = [p for s, n in zip(starts, lengths) for p in range(s, s + n)]
-        token_request = [r for r, n in enumerate(lengths) for _ in range(n)]
-        cu_q = [0]
-        for n in lengths:
-            cu_q.append(cu_q[-1] + n)
-        ctx_len = [s + n for s, n in zip(starts, lengths)]
-        state_slots = [cache.requests[e.request_id].state_slot for e in entries]
-        logit_rows = [cu_q[r] + w for r, e in enumerate(entries) for w in e.want]
-        arrays = [np.asarray(token_ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
-                  np.asarray(token_request, dtype=np.int32), np.asarray(cu_q, dtype=np.int32),
-                  np.asarray(starts, dtype=np.int32), np.asarray(ctx_len, dtype=np.int32),
-                  np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32)]
-        views = []
-        for gi, g in enumerate(cache.groups):
-            view = GroupView(g, cache.page_size)
-            if isinstance(g, PagedGroup):
-                slots = []
-                for e, s, n in zip(entries, starts, lengths):
-                    slots.extend(cache.slot_mapping(e.request_id, gi, s, n))
-                tables = [cache.table(e.request_id, gi) for e in entries]
-                view.max_pages = max(1, max(-(-c // cache.page_size) for c in ctx_len))
-                bt = np.full((R, view.max_pages), -1, dtype=np.int32)
-                for r, t in enumerate(tables):
-                    k = min(len(t), view.max_pages)
-                    bt[r, :k] = t[:k]
-                arrays += [np.asarray(slots, dtype=np.int32), bt.reshape(-1)]
-            views.append(view)
-        dev = self._upload(arrays)
         (ctx.token_ids, ctx.positions, ctx.token_request, ctx.cu_q, ctx.q_start, ctx.ctx_len,
          ctx.state_slots, ctx.logit_rows) = dev[:8]
         k = 8
-        for view, g in zip(views, cache.groups):
+        for gi, g in enumerate(cache.groups):
+            view = GroupView(g, cache.page_size)
             if isinstance(g, PagedGroup):
+                view.max_pages = info["widths"][gi]
                 view.slot_mapping = dev[k]
-                view.block_table = dev[k + 1].view(R, view.max_pages)
+                view.block_table = dev[k + 1].view(info["R"], view.max_pages)
                 k += 2
-        ctx.groups = views
-        ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows = T, R, len(logit_rows)
-        ctx.max_q_len, ctx.max_ctx_len = max(lengths), max(ctx_len)
+            ctx.groups.append(view)
+        ctx.num_tokens, ctx.num_requests, ctx.num_logit_rows = info["T"], info["R"], info["rows"]
+        ctx.max_q_len, ctx.max_ctx_len = info["max_q_len"], info["max_ctx_len"]
         ctx.decode_only = ctx.max_q_len == 1
-        ctx.host_starts, ctx.host_lengths, ctx.host_state_slots = starts, lengths, state_slots
-        ctx.request_ids = [e.request_id for e in entries]
+        ctx.host_starts, ctx.host_lengths = info["starts"], info["lengths"]
+        ctx.host_state_slots, ctx.request_ids = info["state_slots"], info["request_ids"]
         return ctx
+
+    def build_context(self, entries) -> StepContext:
+        arrays, info = self._metadata(entries)
+        return self._context(self._upload(arrays), info)
+
+    # ---- decode steps as CUDA graphs -----------------------------------------------------------------
+    def enable_decode_graphs(self, max_batch: int, max_model_len: int) -> None:
+        """Steps in which every request brings one token and wants its logits are replayed from a
+        CUDA graph captured per batch-size bucket (the reference captures buckets 1, 2, 4, 8:
+        src/flexengine/engine/execution/cuda_graph.py:18-125).  Index arrays live in buffers of
+        fixed address and shape: batches are padded up to the bucket, block tables to the longest
+        request the engine admits."""
+        if self.device.type != "cuda":
+            raise ValueError("CUDA graphs need a CUDA device")
+        buckets, b = [], 1
+        while b < max_batch:
+            buckets.append(b)
+            b *= 2
+        buckets.append(max_batch)
+        self._graph_buckets = buckets
+        self._graph_max_pages = -(-max_model_len // self.cache.page_size)
+        self._graph_max_len = max_model_len
+        self._graphs = {}
+
+    def _graph_for(self, bucket: int, arrays: list, info: dict):
+        """Capture the forward pass for ``bucket`` requests of one token (first use only)."""
+        if bucket in self._graphs:
+            return self._graphs[bucket]
+        sizes = [len(a) for a in arrays]
+        _offsets, total = self._layout(sizes)
+        with torch.inference_mode(False):
+            static = torch.zeros(total, dtype=torch.int32, device=self.device)
+        dev = self._upload(arrays, into=static)
+        info = dict(info, max_ctx_len=self._graph_max_len)       # fixes how decode attention splits the keys
+        ctx = self._context(dev, info)
+        # run once outside a graph on a side stream: libraries set themselves up, scratch is allocated
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.model.forward(ctx)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        launches_before = getattr(self.ops, "launches", 0)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        record = dict(graph=graph, static=static, logits=logits, total=total,
+                      launches=getattr(self.ops, "launches", 0) - launches_before)
+        self._graphs[bucket] = record
+        return record
+
+    def _graph_step(self, entries):
+        """Replay the graph of the smallest bucket that holds the batch; None if none does."""
+        bucket = next((b for b in self._graph_buckets if b >= len(entries)), None)
+        if bucket is None:
+            return None
+        if max(self.cache.tokens_of(e.request_id) for e in entries) + 1 > self._graph_max_len:
+            return None
+        arrays, info = self._metadata(entries, pad_to=bucket, max_pages=self._graph_max_pages)
+        fresh = bucket not in self._graphs
+        record = self._graph_for(bucket, arrays, info)
+        if not fresh:
+            self._upload(arrays, into=record["static"])
+        record["graph"].replay()
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += record["launches"]
+        self.graph_replays += 1
+        return record["logits"][:len(entries)]
 
     @torch.inference_mode()
     def step(self, entries):
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] in the order
-        of the entries and of their ``want`` (None when nothing is wanted)."""
+        of the entries and of their ``want`` (None when nothing is wanted).  With decode graphs
+        on, the returned tensor of a decode step is overwritten by the next such step."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._check(entries)
         self._reserve(entries)
-        ctx = self.build_context(entries)
-        logits = self.model.forward(ctx)
+        logits = None
+        decode = self._graph_buckets and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if decode:
+            logits = self._graph_step(entries)
+        if logits is None:
+            ctx = self.build_context(entries)
+            logits = self.model.forward(ctx)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1

@@ -203,7 +203,7 @@ def decode_splits(requests: int, nkv: int, max_ctx_len: int) -> int:
     """How many ways the keys of a request are split in decode: enough blocks to fill the GPU,
     but no split shorter than two tiles of 32 keys."""
     tiles = max(1, -(-max_ctx_len // 32))
-    want = max(1, (4 * SM_COUNT) // max(1, requests * nkv))
+    want = max(1, (7 * SM_COUNT) // max(1, requests * nkv))      # seven one-warp blocks fit an SM
     return int(max(1, min(want, tiles // 2)))
 
 

@@ -122,3 +122,46 @@ def test_host_running_ahead_of_the_device(model_dirs):
     for j in range(3):
         got = torch.cat([outs[0][20 * j:20 * (j + 1)]] + [o[j:j + 1] for o in outs[1:]])
         helpers.assert_logits_close(got, helpers.plain_logits(model_dirs[name], ids[j], DEV), "float32", f"ahead {j}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_give_the_same_logits(model_dirs, dtype):
+    """Decode steps replayed from CUDA graphs (batches padded up to a bucket) against the plain
+    implementation, with requests joining and leaving so that several buckets are captured."""
+    name = "B"
+    rng = random.Random(7)
+    ids = [helpers.random_prompt(rng, n, 512) for n in (60, 45, 70, 52, 64)]
+    runner = helpers.make_runner(model_dirs[name], dtype, DEV, 20, 32, max_requests=5)
+    runner.enable_decode_graphs(5, 128)
+    rows = {j: [] for j in range(5)}
+    fed = {j: 0 for j in range(5)}
+    for j in range(5):                                   # prompts: all but the last 30 tokens
+        n = len(ids[j]) - 30
+        rows[j].append(runner.step([StepEntry(f"r{j}", ids[j][:n], list(range(n)))]))
+        fed[j] = n
+    live = [0, 1, 2, 3, 4]
+    while live:
+        batch = [j for j in live if rng.random() < 0.8] or live[:1]
+        out = runner.step([StepEntry(f"r{j}", ids[j][fed[j]:fed[j] + 1], [0]) for j in batch])
+        for i, j in enumerate(batch):
+            rows[j].append(out[i:i + 1].clone())
+            fed[j] += 1
+            if fed[j] == len(ids[j]):
+                live.remove(j)
+                runner.finish(f"r{j}")
+    assert runner.graph_replays >= 30 and len(runner._graphs) >= 3
+    for j in range(5):
+        helpers.assert_logits_close(torch.cat(rows[j]), helpers.plain_logits(model_dirs[name], ids[j], DEV), dtype, f"graph {j}")
+    from flexengine_b200 import ops
+    ops.check_status(DEV)
+
+
+def test_engine_with_decode_graphs_generates_the_same_tokens(model_dirs):
+    config, weights = plain_model.read_model_folder(model_dirs["A"], DEV)
+    rng = random.Random(8)
+    prompts = [helpers.random_prompt(rng, n, 256) for n in (5, 17, 33, 1, 40, 12)]
+    engine = engine_for(model_dirs["A"], "A", "float32", cuda_graph=True, max_num_seqs=4)
+    outputs = engine.generate(prompts, max_tokens=10)
+    for prompt, out in zip(prompts, outputs):
+        assert out.token_ids == plain_model.greedy_generate(config, weights, prompt, 10)
+    assert engine.runner.graph_replays > 0 and engine.cache.used_pages == 0
