@@ -247,6 +247,8 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
                     const bf16* __restrict__ vc, const int* __restrict__ block_table, int bt_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv, int d, int ps,
                     int num_pages, float scale_log2, int window, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     constexpr int TILE = TK * DMAX;                  // elements per K (or V) stage
@@ -325,6 +327,8 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                       bf16* __restrict__ out, long long out_stride, const int* __restrict__ cu_q,
                                       int nq, int d, int splits) {
+    griddep_wait();
+    griddep_launch_dependents();
     const int head = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + head) * splits;
     float mx = -CUDART_INF_F;
@@ -358,6 +362,8 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
                      const bf16* __restrict__ kc, const bf16* __restrict__ vc, const int* __restrict__ block_table,
                      int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ q_start, int nq, int nkv,
                      int d, int ps, int num_pages, float scale_log2, int window, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     constexpr int STAGE = PREFILL_KEYS * DMAX;       // elements per K (or V) stage
@@ -493,7 +499,7 @@ extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out,
 #define FE_DECODE(DMAX, UPPER)                                                                                    \
     do {                                                                                                          \
         if (allow_smem(paged_decode_kernel<DMAX, UPPER>, decode_smem<DMAX>(), "paged_decode")) return 1;          \
-        paged_decode_kernel<DMAX, UPPER><<<grid, 32, decode_smem<DMAX>(), stream>>>(                              \
+        fe::launch(paged_decode_kernel<DMAX, UPPER>, grid, 32, decode_smem<DMAX>(), stream,                               \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, part_o, part_lse, (const bf16*)kc, (const bf16*)vc, \
             block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);        \
     } while (0)
@@ -504,7 +510,7 @@ extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out,
 #undef FE_DECODE
     if (fe_check_launch("paged_decode")) return 2;
     if (splits > 1) {
-        decode_combine_kernel<<<dim3(nq, requests), d >= 128 ? 128 : 64, 0, stream>>>(
+        fe::launch(decode_combine_kernel, dim3(nq, requests), d >= 128 ? 128 : 64, 0, stream, 
             part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits);
         return fe_check_launch("paged_decode combine");
     }
@@ -527,7 +533,7 @@ extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out
 #define FE_PREFILL(DMAX)                                                                                       \
     do {                                                                                                       \
         if (allow_smem(paged_prefill_kernel<DMAX>, prefill_smem<DMAX>(), "paged_prefill")) return 1;           \
-        paged_prefill_kernel<DMAX><<<grid, PREFILL_WARPS * 32, prefill_smem<DMAX>(), stream>>>(                \
+        fe::launch(paged_prefill_kernel<DMAX>, grid, PREFILL_WARPS * 32, prefill_smem<DMAX>(), stream,                 \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table,  \
             bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);                  \
     } while (0)

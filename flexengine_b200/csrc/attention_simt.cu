@@ -24,6 +24,8 @@ __global__ void paged_attention_simt_kernel(const T* __restrict__ q, long long q
                                             const int* __restrict__ q_start, const int* __restrict__ token_req,
                                             int T_tokens, int nq, int nkv, int d, int ps, int num_pages, float scale,
                                             int window, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
     extern __shared__ float q_smem[];
     const int lane = threadIdx.x & 31;
     const int warp_in_block = threadIdx.x >> 5;
@@ -110,7 +112,7 @@ static int launch_simt(const void* q, long long q_stride, void* out, long long o
     const int blocks = (int)((total + warps - 1) / warps);
     const size_t smem = (size_t)warps * d * sizeof(float);
 #define FE_LAUNCH_SIMT(DPL)                                                                                      \
-    paged_attention_simt_kernel<T, DPL><<<blocks, warps * 32, smem, stream>>>(                                   \
+    fe::launch(paged_attention_simt_kernel<T, DPL>, blocks, warps * 32, smem, stream,                                    \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)kc, (const T*)vc, block_table, bt_stride, cu_q,   \
         q_start, token_req, T_tokens, nq, nkv, d, ps, num_pages, scale, window, status)
     if (d <= 32) FE_LAUNCH_SIMT(1);

@@ -93,11 +93,40 @@ template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float* v
     *reinterpret_cast<uint4*>(p) = raw;
 }
 
+// Programmatic dependent launch: a kernel launched through fe::launch may begin while the kernel
+// before it in the stream is still running.  Everything it reads that an earlier kernel wrote,
+// and every write, must come after griddep_wait(); only data that no kernel writes (weights)
+// may be touched before.  launch_dependents lets the next kernel start its own preamble; it is
+// called after the wait, so that at most one kernel is resident ahead of the one that runs
+// (called before, every later kernel of a graph piles onto the SMs and starves the running one).
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace fe
 
 // Host side: the last error message of this thread, and a checked launch epilogue.
 void fe_set_error(const char* fmt, ...);
 int fe_check_launch(const char* what);
+int fe_pdl_enabled();
+
+namespace fe {
+// Launch with the programmatic-stream-serialization attribute (when enabled).
+template <typename... KArgs, typename... Args>
+inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = fe_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);       // errors surface in fe_check_launch
+}
+}  // namespace fe
 
 #define FE_REQUIRE(cond, ...)            \
     do {                                 \

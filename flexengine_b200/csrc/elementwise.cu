@@ -12,6 +12,8 @@ using namespace fe;
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out,
                                  int H, int V, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -30,9 +32,9 @@ extern "C" int fe_embedding(const int* ids, const void* table, float* out, int T
     if (T == 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == FE_F32)
-        embedding_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H, V, status);
+        fe::launch(embedding_kernel<float>, T, threads, 0, stream, ids, (const float*)table, out, H, V, status);
     else if (dtype == FE_BF16)
-        embedding_kernel<bf16><<<T, threads, 0, stream>>>(ids, (const bf16*)table, out, H, V, status);
+        fe::launch(embedding_kernel<bf16>, T, threads, 0, stream, ids, (const bf16*)table, out, H, V, status);
     else
         FE_REQUIRE(false, "embedding: unknown dtype %d", dtype);
     return fe_check_launch("embedding");
@@ -46,6 +48,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const float* __restrict__ weight, float eps, T* __restrict__ out,
                                    const int* __restrict__ rows, int H, int n_rows_total) {
+    griddep_wait();
+    griddep_launch_dependents();
     extern __shared__ float row[];
     __shared__ float scratch[33];
     const int i = blockIdx.x;
@@ -92,6 +96,8 @@ template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const float* __restrict__ weight, float eps, T* __restrict__ out,
                                        const int* __restrict__ rows, int H, int n_rows_total) {
+    griddep_wait();
+    griddep_launch_dependents();
     extern __shared__ float row[];
     __shared__ float scratch[33];
     const int i = blockIdx.x;
@@ -131,13 +137,13 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const float* w
         if (smem > 48 * 1024)
             err = cudaFuncSetAttribute(add_rmsnorm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
-        add_rmsnorm_vec_kernel<T><<<n_out, threads, smem, stream>>>(residual, (const T*)delta, weight, eps, (T*)out,
+        fe::launch(add_rmsnorm_vec_kernel<T>, n_out, threads, smem, stream, residual, (const T*)delta, weight, eps, (T*)out,
                                                                     rows, H, n_rows_total);
     } else {
         if (smem > 48 * 1024)
             err = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
-        add_rmsnorm_kernel<T><<<n_out, threads, smem, stream>>>(residual, (const T*)delta, weight, eps, (T*)out, rows,
+        fe::launch(add_rmsnorm_kernel<T>, n_out, threads, smem, stream, residual, (const T*)delta, weight, eps, (T*)out, rows,
                                                                 H, n_rows_total);
     }
     return fe_check_launch("add_rmsnorm");
@@ -167,6 +173,8 @@ __global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __r
                                            int rot, const int* __restrict__ slot_mapping, T* __restrict__ kc,
                                            T* __restrict__ vc, int nq, int nkv, int d, int ps, long long num_slots,
                                            int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
     const int t = blockIdx.x, head = blockIdx.y;
     const int width = (nq + 2 * nkv) * d;
     T* x = qkv + (size_t)t * width + (size_t)head * d;
@@ -223,6 +231,8 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
                                                int rot, const int* __restrict__ slot_mapping, T* __restrict__ kc,
                                                T* __restrict__ vc, int nq, int nkv, int d, int ps,
                                                long long num_slots, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
     extern __shared__ float trig[];                  // cos [rot/2], sin [rot/2]
     const int t = blockIdx.x;
     const int half = rot / 2;
@@ -294,11 +304,11 @@ static int launch_rope(void* qkv, const float* bias, const int* positions, const
     if (d % 16 == 0 && rot % 16 == 0) {
         const int units = (nq + 2 * nkv) * (d / 8 - (inv_freq && rot ? rot / 16 : 0));
         const int threads = units >= 256 ? 256 : (units >= 128 ? 128 : 64);
-        qkv_bias_rope_cache_vec_kernel<T><<<T_tokens, threads, (size_t)rot * sizeof(float), stream>>>(
+        fe::launch(qkv_bias_rope_cache_vec_kernel<T>, T_tokens, threads, (size_t)rot * sizeof(float), stream, 
             (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
     } else {
         const dim3 grid(T_tokens, nq + 2 * nkv);
-        qkv_bias_rope_cache_kernel<T><<<grid, d / 2 >= 64 ? 64 : 32, 0, stream>>>(
+        fe::launch(qkv_bias_rope_cache_kernel<T>, grid, d / 2 >= 64 ? 64 : 32, 0, stream, 
             (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
     }
     return fe_check_launch("qkv_bias_rope_cache");
@@ -320,6 +330,8 @@ extern "C" int fe_qkv_bias_rope_cache(void* qkv, const float* bias, const int* p
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int I) {
+    griddep_wait();
+    griddep_launch_dependents();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / I;
@@ -332,6 +344,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long units, int I) {
+    griddep_wait();
+    griddep_launch_dependents();
     const int per_row = I / 8;
     for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += (long long)gridDim.x * blockDim.x) {
         const long long t = u / per_row;
@@ -354,11 +368,11 @@ extern "C" int fe_swiglu(const void* gate_up, void* out, int T, int I, int dtype
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == FE_F32) {
-        if (vec) swiglu_vec_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, I);
-        else swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, total, I);
+        if (vec) fe::launch(swiglu_vec_kernel<float>, (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, I);
+        else fe::launch(swiglu_kernel<float>, (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, I);
     } else if (dtype == FE_BF16) {
-        if (vec) swiglu_vec_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, I);
-        else swiglu_kernel<bf16><<<(int)blocks, threads, 0, stream>>>((const bf16*)gate_up, (bf16*)out, total, I);
+        if (vec) fe::launch(swiglu_vec_kernel<bf16>, (int)blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, I);
+        else fe::launch(swiglu_kernel<bf16>, (int)blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, I);
     } else {
         FE_REQUIRE(false, "swiglu: unknown dtype %d", dtype);
     }

@@ -22,6 +22,13 @@ int fe_check_launch(const char* what) {
     return 0;
 }
 
+static int g_pdl = 1;
+
+int fe_pdl_enabled() { return g_pdl; }
+
+// 1: kernels may overlap their preamble with the tail of the kernel before them (default); 0: off.
+extern "C" void fe_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
 extern "C" const char* fe_last_error() { return g_last_error; }
 
 extern "C" int fe_abi_version() { return 1; }

@@ -12,6 +12,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
                  float* __restrict__ C, int M, int N, int K) {
+    fe::griddep_wait();
+    fe::griddep_launch_dependents();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -67,6 +69,6 @@ extern "C" int fe_gemm_fp32(const float* A, const float* W, const float* bias, f
     if (M == 0) return 0;
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     FE_REQUIRE(grid.y <= 65535, "gemm_fp32: too many rows (%d)", M);
-    gemm_fp32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K);
+    fe::launch(gemm_fp32_kernel, grid, 256, 0, stream, A, W, bias, C, M, N, K);
     return fe_check_launch("gemm_fp32");
 }

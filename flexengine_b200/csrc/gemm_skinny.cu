@@ -1,0 +1,197 @@
+// y[M, N] = x[M, K] . W[N, K]^T for a handful of rows (decode): the product is a stream of the
+// weight matrix, so the kernel is built around reading W once at full HBM speed.
+//
+// One block takes 16 rows of W (swap-AB: the rows of W are the 16 rows of mma.sync.m16n8k16,
+// the batch is its 8 columns).  Its eight warps split K; every lane reads 32 contiguous bytes
+// of "its" two W rows per step straight into MMA fragments.  The fragment layout wants
+// k = {2t, 2t+1, 2t+8, 2t+9} per lane; since a dot product does not care in which order k is
+// summed, lane t instead takes the 16 contiguous elements k0 + 16t .. +15 of a 64-wide step and
+// the activations are read with the same pattern, so both operands are 16-byte loads.  The eight
+// partial sums of a block are added in shared memory in a fixed order (deterministic).
+//
+// Epilogues: bfloat16 output; float output (vocabulary projection); SwiGLU, where a block pairs
+// 8 gate rows with their 8 up rows of a [2I, K] matrix and writes silu(gate) * up.
+// The reference runs these products through cuBLAS (inference/models/qwen2.py:99-101,129-135).
+#include "common.cuh"
+
+using namespace fe;
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int KSTEP = 64;       // k elements per warp step (4 MMAs)
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+
+__device__ __forceinline__ uint4 ld_stream(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_keep(const bf16* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ void mma16816(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                         unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// RT: 16-row tiles of W per block (2 for wide matrices: fewer, longer-lived blocks that fill the
+//     GPU in whole rounds, and the activations are read once for both tiles)
+// PF: k steps whose loads go out together before their math (bytes in flight per lane = RT * PF * 64)
+template <int NT, int EPI, int RT, int PF>
+__global__ void __launch_bounds__(WARPS * 32)
+skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
+                   int I) {
+    __shared__ float red[WARPS][RT * NT * 8 * 16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    // rows of W behind accumulator rows g and g + 8 of tile r
+    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? 8 : 16) * RT;
+    const bf16* w0[RT];
+    const bf16* w1[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+        int row0, row1;
+        if (EPI == EPI_SWIGLU) {
+            row0 = min(n0 + r * 8 + g, I - 1);          // gate row
+            row1 = I + row0;                            // its up row
+        } else {
+            row0 = min(n0 + r * 16 + g, N - 1);
+            row1 = min(n0 + r * 16 + g + 8, N - 1);
+        }
+        w0[r] = W + (size_t)row0 * K + 16 * t;
+        w1[r] = W + (size_t)row1 * K + 16 * t;
+    }
+    const bf16* xr[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xr[nt] = nt * 8 + g < M ? x + (size_t)(nt * 8 + g) * K + 16 * t : nullptr;
+
+    float acc[RT][NT][4];
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc[r][nt][0] = acc[r][nt][1] = acc[r][nt][2] = acc[r][nt][3] = 0.f;
+
+    // this warp's k steps are warp, warp + 8, ...; the loads of PF steps go out together, then their math
+    const int steps = K / KSTEP;
+    for (int s = warp; s < steps; s += WARPS * PF) {
+        uint4 a0[PF][RT][2], a1[PF][RT][2], b[PF][NT][2];
+#pragma unroll
+        for (int p = 0; p < PF; ++p) {
+            const int sp = s + p * WARPS;
+            if (sp < steps) {
+                const size_t k = (size_t)sp * KSTEP;
+#pragma unroll
+                for (int r = 0; r < RT; ++r) {
+                    a0[p][r][0] = ld_stream(w0[r] + k); a0[p][r][1] = ld_stream(w0[r] + k + 8);
+                    a1[p][r][0] = ld_stream(w1[r] + k); a1[p][r][1] = ld_stream(w1[r] + k + 8);
+                }
+            }
+        }
+        // the weights above depend on no kernel; the activations below are the previous kernel's
+        // output, so the first batch of weight loads is already in flight while that kernel ends
+        if (s == warp) { griddep_wait(); griddep_launch_dependents(); }
+#pragma unroll
+        for (int p = 0; p < PF; ++p) {
+            const int sp = s + p * WARPS;
+            if (sp < steps) {
+                const size_t k = (size_t)sp * KSTEP;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    if (xr[nt]) { b[p][nt][0] = ld_keep(xr[nt] + k); b[p][nt][1] = ld_keep(xr[nt] + k + 8); }
+                    else { b[p][nt][0] = make_uint4(0, 0, 0, 0); b[p][nt][1] = make_uint4(0, 0, 0, 0); }
+                }
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < PF; ++p) {
+            if (s + p * WARPS < steps) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int r = 0; r < RT; ++r) {
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            mma16816(acc[r][nt], a0[p][r][h].x, a1[p][r][h].x, a0[p][r][h].y, a1[p][r][h].y,
+                                     b[p][nt][h].x, b[p][nt][h].y);
+                            mma16816(acc[r][nt], a0[p][r][h].z, a1[p][r][h].z, a0[p][r][h].w, a1[p][r][h].w,
+                                     b[p][nt][h].z, b[p][nt][h].w);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (warp >= steps) { griddep_wait(); griddep_launch_dependents(); }   // a warp without work has not waited yet
+    // accumulator (tile r, row g + 8 (e >> 1), batch column nt * 8 + 2t + (e & 1)) -> red[warp][(r, column, row)]
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                red[warp][(r * NT * 8 + nt * 8 + 2 * t + (e & 1)) * 16 + g + 8 * (e >> 1)] = acc[r][nt][e];
+    __syncthreads();
+    if (EPI == EPI_SWIGLU) {
+        for (int idx = threadIdx.x; idx < RT * NT * 8 * 8; idx += WARPS * 32) {
+            const int r = idx / (NT * 64), rest = idx - r * (NT * 64);
+            const int m = rest >> 3, row = rest & 7;
+            const int n = n0 + r * 8 + row;
+            if (m >= M || n >= I) continue;
+            float gate = 0.f, up = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                gate += red[w][(r * NT * 8 + m) * 16 + row];
+                up += red[w][(r * NT * 8 + m) * 16 + row + 8];
+            }
+            reinterpret_cast<bf16*>(out)[(size_t)m * I + n] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < RT * NT * 8 * 16; idx += WARPS * 32) {
+            const int r = idx / (NT * 128), rest = idx - r * (NT * 128);
+            const int m = rest >> 4, row = rest & 15;
+            const int n = n0 + r * 16 + row;
+            if (m >= M || n >= N) continue;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) v += red[w][(r * NT * 8 + m) * 16 + row];
+            if (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
+            else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+template <int EPI>
+int launch(const void* x, const void* W, void* out, int M, int N, int K, int I, cudaStream_t stream) {
+    const int tiles = EPI == EPI_SWIGLU ? (I + 7) / 8 : (N + 15) / 16;
+    // a wide matrix: two tiles per block; a narrow one with a long K: every warp has a long stream
+    // and must keep more of it in flight
+    const bool wide = tiles >= 4 * 148;
+    const bool deep = !wide && tiles <= 2 * 148 && K / KSTEP >= 4 * WARPS * 4;
+    const int blocks = wide ? (tiles + 1) / 2 : tiles;
+#define FE_SKINNY(NT, RT, PF) \
+    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF>, blocks, WARPS * 32, 0, stream, (const bf16*)x, (const bf16*)W, out, M, N, K, I)
+    if (M <= 8) { if (wide) FE_SKINNY(1, 2, 2); else if (deep) FE_SKINNY(1, 1, 4); else FE_SKINNY(1, 1, 2); }
+    else { if (wide) FE_SKINNY(2, 2, 2); else if (deep) FE_SKINNY(2, 1, 4); else FE_SKINNY(2, 1, 2); }
+#undef FE_SKINNY
+    return fe_check_launch("skinny_gemm");
+}
+
+}  // namespace
+
+// epilogue: 0 bfloat16 [M, N]; 1 float [M, N]; 2 SwiGLU: W is [2 I, K] (gate rows, then up rows), out bfloat16 [M, I].
+extern "C" int fe_skinny_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
+                              cudaStream_t stream) {
+    FE_REQUIRE(M >= 1 && M <= 16, "skinny_gemm: %d rows; this kernel takes 1 to 16", M);
+    FE_REQUIRE(N > 0 && K > 0 && K % KSTEP == 0, "skinny_gemm: K = %d must be a positive multiple of %d", K, KSTEP);
+    FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_gemm: operands must be 16-byte aligned");
+    if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, 0, stream);
+    if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, M, N, K, 0, stream);
+    if (epilogue == EPI_SWIGLU) {
+        FE_REQUIRE(N % 2 == 0, "skinny_gemm: SwiGLU needs an even number of weight rows, got %d", N);
+        return launch<EPI_SWIGLU>(x, W, out, M, N, K, N / 2, stream);
+    }
+    FE_REQUIRE(false, "skinny_gemm: unknown epilogue %d", epilogue);
+}

@@ -55,6 +55,8 @@ __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const long long* __restrict__ seed,
               const long long* __restrict__ draw, int* __restrict__ out) {
+    griddep_wait();
+    griddep_launch_dependents();
     __shared__ float s_val[THREADS];
     __shared__ int s_idx[THREADS];
     __shared__ unsigned int hist[256];
@@ -210,6 +212,6 @@ extern "C" int fe_sample(const float* logits, long long ld, int R, int V, const 
                          cudaStream_t stream) {
     FE_REQUIRE(R >= 0 && V > 0 && ld >= V, "sample: bad sizes R=%d V=%d ld=%lld", R, V, ld);
     if (R == 0) return 0;
-    sample_kernel<<<R, THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, seed, draw, out);
+    fe::launch(sample_kernel, R, THREADS, 0, stream, logits, ld, V, temperature, top_k, seed, draw, out);
     return fe_check_launch("sample");
 }

@@ -127,10 +127,38 @@ def linear(x, w, bias=None, out_float32=False):
         return y if (out_float32 or x.dtype == torch.float32) else y.to(x.dtype)
     if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         raise TypeError(f"linear: weight {w.dtype} with activations {x.dtype}")
-    y = torch.mm(x, w.t(), out_dtype=torch.float32) if out_float32 else torch.mm(x, w.t())
+    if skinny_ok(x, w):
+        y = skinny_gemm(x, w, EPI_F32 if out_float32 else EPI_BF16)
+    else:
+        y = torch.mm(x, w.t(), out_dtype=torch.float32) if out_float32 else torch.mm(x, w.t())
     if bias is not None:
         y += bias.to(y.dtype)
     return y
+
+
+SKINNY_MAX_ROWS = 8          # beyond this the library product is as fast or faster
+EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
+
+
+def skinny_ok(x, w) -> bool:
+    """Whether the weight-streaming kernel is used for this product: bfloat16, up to 8 rows (the
+    kernel itself takes up to 16), K a multiple of 64."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 <= x.shape[0] <= SKINNY_MAX_ROWS
+            and x.shape[1] % 64 == 0 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def skinny_gemm(x, w, epilogue: int = EPI_BF16):
+    """x [M <= 16, K] times w [N, K]^T by streaming w once; see csrc/gemm_skinny.cu."""
+    M, K = x.shape
+    N = w.shape[0]
+    if epilogue == EPI_SWIGLU:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    else:
+        out = torch.empty((M, N), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=x.device)
+    _run(_bf16(), "fe_skinny_gemm", _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue),
+         _stream())
+    return out
 
 
 def swiglu(gate_up, intermediate):
@@ -145,7 +173,9 @@ def swiglu(gate_up, intermediate):
 
 
 def linear_swiglu(x, w, intermediate):
-    """silu(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K])."""
+    """silu(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]); one kernel for a handful of rows."""
+    if skinny_ok(x, w) and w.shape[0] == 2 * intermediate:
+        return skinny_gemm(x, w, EPI_SWIGLU)
     return swiglu(linear(x, w), intermediate)
 
 

@@ -29,7 +29,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 # compiles only that
 GROUPS = {
     "core": ["errors.cu", "elementwise.cu", "attention_simt.cu", "gemm_fp32.cu", "sampling.cu"],
-    "bf16": ["errors.cu", "attention_mma.cu"],
+    "bf16": ["errors.cu", "attention_mma.cu", "gemm_skinny.cu"],
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -155,6 +155,9 @@ def load(group: str) -> ctypes.CDLL:
         except OSError as ex:
             raise KernelLibraryError(f"cannot load {path}: {ex}") from ex
         lib.fe_last_error.restype = ctypes.c_char_p
+        # programmatic dependent launch (a kernel's preamble overlaps the tail of the one before):
+        # measured to bring nothing inside CUDA graphs, so it is off unless FLEXENGINE_PDL=1
+        lib.fe_set_pdl(ctypes.c_int(1 if os.environ.get("FLEXENGINE_PDL", "0") == "1" else 0))
         _loaded[group] = lib
         return lib
 

@@ -95,6 +95,32 @@ def test_linear_bf16(M, N, K, gen):
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(301, 64), (24, 192), (768, 384), (4608, 3584), (16, 18944)])
+def test_skinny_gemm(M, N, K, gen):
+    x, w = rand((M, K), torch.bfloat16, gen), rand((N, K), torch.bfloat16, gen, 0.05)
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(ops().skinny_gemm(x, w, ops().EPI_F32), want, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(ops().skinny_gemm(x, w, ops().EPI_BF16).float(), want, atol=2e-2, rtol=2e-2)
+    if N % 2 == 0:
+        got = ops().skinny_gemm(x, w, ops().EPI_SWIGLU)
+        assert tuple(got.shape) == (M, N // 2)
+        torch.testing.assert_close(got.float(), kernel_refs.swiglu(want.to(torch.bfloat16), N // 2).float(), atol=2e-2, rtol=3e-2)
+    # the dispatch uses it for up to 8 rows and gives the same numbers either way
+    torch.testing.assert_close(ops().linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
+    # twice the same: the reduction order is fixed
+    assert torch.equal(ops().skinny_gemm(x, w, ops().EPI_F32), ops().skinny_gemm(x, w, ops().EPI_F32))
+
+
+def test_skinny_gemm_refuses_what_it_cannot_take(gen):
+    x, w = rand((4, 80), torch.bfloat16, gen), rand((32, 80), torch.bfloat16, gen)
+    with pytest.raises(RuntimeError, match="multiple of 64"):
+        ops().skinny_gemm(x, w)
+    with pytest.raises(RuntimeError, match="1 to 16"):
+        ops().skinny_gemm(rand((17, 64), torch.bfloat16, gen), rand((32, 64), torch.bfloat16, gen))
+    torch.testing.assert_close(ops().linear(x, w).float(), x.float() @ w.float().T, atol=2e-2, rtol=2e-2)   # library product
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,I", [(1, 160), (9, 112), (33, 18944)])
 def test_swiglu(dtype, T, I, gen):
