@@ -6,9 +6,12 @@
 // t <= p (and t > p - window when window > 0); query head h reads key/value head h / (nq / nkv).
 //
 // Both kernels walk the keys in tiles of 32 aligned to position 0.  A tile's keys and values are
-// gathered page by page with 16-byte asynchronous copies into a ring of shared-memory stages
-// (rows swizzled against bank conflicts), read back with ldmatrix and multiplied with
-// mma.sync.m16n8k16.  The 16 rows of an MMA tile are the query heads of one key/value group
+// gathered page by page with 16-byte asynchronous copies (cp.async) into a ring of shared-memory
+// stages whose rows are padded by 16 bytes against bank conflicts, read back with ldmatrix and
+// multiplied with mma.sync.m16n8k16.  One thread per key looks its page up and leaves the row's
+// offset in shared memory; the copies then cost a handful of instructions each.  (Row-sized bulk
+// copies of the TMA engine were measured slower here: at 256 bytes a copy the engine, not HBM,
+// set the pace.)  The 16 rows of an MMA tile are the query heads of one key/value group
 // (decode) or (query, head-of-group) pairs (prefill), so the group shares every key it loads.
 //
 // decode:  one warp per (split of the keys, key/value head, request); partial results of the
@@ -59,62 +62,46 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// Element offset of 16-byte chunk c of row r in a tile whose rows are PITCH elements apart:
-// chunks are XOR-swizzled with the row inside each group of eight chunks.
-template <int PITCH> __device__ __forceinline__ int tile_offset(int r, int c) {
-    return r * PITCH + (((c & ~7) | ((c ^ r) & 7)) << 3);
-}
+// Rows of a stage are PITCH = DMAX + 8 elements apart: the 16 bytes of padding shift consecutive
+// rows by one bank group, so the eight rows an ldmatrix touches never collide.
+template <int DMAX> __host__ __device__ constexpr int pitch() { return DMAX + 8; }
 
 struct KvSource {
     const bf16* kc;
     const bf16* vc;
     const int* table;      // this request's row of the block table
-    int nkv, kvh, d, ps, num_pages;
+    int nkv, kvh, d, ps, ps_shift, num_pages;     // ps_shift: log2(ps) when ps is a power of two, else -1
 };
 
-// Gather ROWS keys/values starting at key ``first`` into one stage.  Keys outside [lo, hi] are
-// filled with zeros (their scores are masked; zero values keep 0 * v finite).  Lane r of every
-// warp looks up the pages of keys r, r + 32, ... once; the 16-byte copies then take their row's
-// offset by shuffle, so no copy waits on a table load of its own, and the (row, chunk) walk is
-// incremental (no division in the loop).
-template <int DMAX, int THREADS, int ROWS>
-__device__ __forceinline__ void load_stage(bf16* ks, bf16* vs, const KvSource& src, int first, int lo, int hi,
-                                           int* status) {
-    const int lane = threadIdx.x & 31;
-    long long row_off[ROWS / 32];
-#pragma unroll
-    for (int i = 0; i < ROWS / 32; ++i) {
-        const int key = first + i * 32 + lane;
-        row_off[i] = -1;
-        if (key >= lo && key <= hi) {
-            const int page = src.table[key / src.ps];
-            if (page < 0 || page >= src.num_pages) {
-                if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
-            } else {
-                row_off[i] = (((long long)page * src.nkv + src.kvh) * src.ps + (key % src.ps)) * src.d;
-            }
-        }
+// Element offset of key ``key``'s row in the cache, or -1 for a key outside [lo, hi] (or whose
+// page id is out of range, which also sets the status word).
+__device__ __forceinline__ long long row_offset(const KvSource& src, int key, int lo, int hi, int* status) {
+    if (key < lo || key > hi) return -1;
+    const int page = src.table[src.ps_shift >= 0 ? key >> src.ps_shift : key / src.ps];
+    if (page < 0 || page >= src.num_pages) {
+        if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
+        return -1;
     }
+    const int within = src.ps_shift >= 0 ? key & (src.ps - 1) : key % src.ps;
+    return (((long long)page * src.nkv + src.kvh) * src.ps + within) * src.d;
+}
+
+// Copy ROWS key rows and ROWS value rows into a stage with 16-byte asynchronous copies, THREADS
+// threads sharing the work.  ``offs`` (shared memory) holds each row's offset in the cache, -1
+// for rows that are filled with zeros instead (their scores are masked; zero values keep
+// 0 * v finite).
+template <int DMAX, int THREADS, int ROWS>
+__device__ __forceinline__ void copy_rows(bf16* ks, bf16* vs, const KvSource& src, const long long* offs) {
     const int cpr = src.d >> 3;                       // 16-byte chunks per row
     const int step_r = THREADS / cpr, step_c = THREADS - step_r * cpr;
     int r = threadIdx.x / cpr, c = threadIdx.x - r * cpr;
-    const int total = ROWS * cpr;
-    for (int base = 0; base < total; base += THREADS) {
-        const bool active = base + (int)threadIdx.x < total;
-        const int rr = active ? r : 0;
-        long long off = __shfl_sync(0xffffffffu, row_off[0], rr & 31);
-#pragma unroll
-        for (int i = 1; i < ROWS / 32; ++i) {
-            const long long other = __shfl_sync(0xffffffffu, row_off[i], rr & 31);
-            if ((rr >> 5) == i) off = other;
-        }
-        if (active) {
-            const int o = tile_offset<DMAX>(r, c);
-            const bool valid = off >= 0;
-            const long long from = valid ? off + (c << 3) : 0;
-            cp_async16(ks + o, src.kc + from, valid ? 16 : 0);
-            cp_async16(vs + o, src.vc + from, valid ? 16 : 0);
-        }
+    for (int idx = threadIdx.x; idx < ROWS * cpr; idx += THREADS) {
+        const long long off = offs[r];
+        const bool valid = off >= 0;
+        const long long from = valid ? off + (c << 3) : 0;
+        const int o = r * pitch<DMAX>() + (c << 3);
+        cp_async16(ks + o, src.kc + from, valid ? 16 : 0);
+        cp_async16(vs + o, src.vc + from, valid ? 16 : 0);
         r += step_r; c += step_c;
         if (c >= cpr) { c -= cpr; ++r; }
     }
@@ -134,16 +121,15 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
 #pragma unroll
     for (int j = 0; j < TK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     {
-        // row = jp*16 + (mat>>1)*8 + mrow, chunk = ksx*2 + (mat&1); the swizzle is chunk ^ (row & 7)
-        const bf16* kbase = ks + ((mat >> 1) * 8 + mrow) * DMAX;
-        const int kx = (mat & 1) ^ mrow;
+        // row = jp*16 + (mat>>1)*8 + mrow, 16-byte chunk = ksx*2 + (mat&1)
+        const bf16* kbase = ks + ((mat >> 1) * 8 + mrow) * pitch<DMAX>() + (mat & 1) * 8;
 #pragma unroll
         for (int ksx = 0; ksx < DMAX / 16; ++ksx) {
             if (ksx * 16 < d) {
 #pragma unroll
                 for (int jp = 0; jp < TK / 16; ++jp) {
                     unsigned r0, r1, r2, r3;
-                    ldmatrix_x4(r0, r1, r2, r3, kbase + jp * 16 * DMAX + (ksx >> 2) * 64 + ((((ksx * 2) & 7) ^ kx) << 3));
+                    ldmatrix_x4(r0, r1, r2, r3, kbase + jp * 16 * pitch<DMAX>() + ksx * 16);
                     mma16816(s[jp * 2], qfrag[ksx], r0, r1);
                     mma16816(s[jp * 2 + 1], qfrag[ksx], r2, r3);
                 }
@@ -195,9 +181,8 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
     }
     l[0] += sum0; l[1] += sum1;                       // per-thread partial sums of the rows
     {
-        // row = kk*16 + (mat&1)*8 + mrow, chunk = np*2 + (mat>>1)
-        const bf16* vbase = vs + ((mat & 1) * 8 + mrow) * DMAX;
-        const int vx = (mat >> 1) ^ mrow;
+        // row = kk*16 + (mat&1)*8 + mrow, 16-byte chunk = np*2 + (mat>>1)
+        const bf16* vbase = vs + ((mat & 1) * 8 + mrow) * pitch<DMAX>() + (mat >> 1) * 8;
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {
             unsigned a[4];
@@ -209,7 +194,7 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
             for (int np = 0; np < DMAX / 16; ++np) {
                 if (np * 16 < d) {
                     unsigned r0, r1, r2, r3;
-                    ldmatrix_x4_trans(r0, r1, r2, r3, vbase + kk * 16 * DMAX + (np >> 2) * 64 + ((((np * 2) & 7) ^ vx) << 3));
+                    ldmatrix_x4_trans(r0, r1, r2, r3, vbase + kk * 16 * pitch<DMAX>() + np * 16);
                     mma16816(o[np * 2], a, r0, r1);
                     mma16816(o[np * 2 + 1], a, r2, r3);
                 }
@@ -236,7 +221,7 @@ __device__ __forceinline__ void load_q(unsigned (*qfrag)[4], const bf16* src0, c
 }
 
 // ---------------------------------------------------------------------------------------------
-// decode: grid (splits, nkv, requests), one warp, two stages of 32 keys.  Every request brings
+// decode: grid (splits, nkv, requests), one warp, a ring of 32-key stages.  Every request brings
 // exactly one token.
 constexpr int DECODE_STAGES = 2;
 
@@ -250,8 +235,9 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ long long offs[TK];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    constexpr int TILE = TK * DMAX;                  // elements per K (or V) stage
+    constexpr int TILE = TK * pitch<DMAX>();         // elements per K (or V) stage
     const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
     const int G = nq / nkv;
@@ -263,8 +249,14 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     const int t_begin = tile_lo + split * per, t_end = min(tile_hi + 1, t_begin + per);
     const int n_tiles = max(0, t_end - t_begin);
 
-    KvSource src{kc, vc, block_table + (size_t)b * bt_stride, nkv, kvh, d, ps, num_pages};
-    if (n_tiles > 0) load_stage<DMAX, 32, TK>(smem, smem + TILE, src, t_begin * TK, lo, pos, status);
+    KvSource src{kc, vc, block_table + (size_t)b * bt_stride, nkv, kvh, d, ps, (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1,
+                 num_pages};
+    // lane r looks up key r of a tile; then the warp copies the 32 rows
+    if (n_tiles > 0) {
+        offs[lane] = row_offset(src, t_begin * TK + lane, lo, pos, status);
+        __syncwarp();
+        copy_rows<DMAX, 32, TK>(smem, smem + TILE, src, offs);
+    }
     cp_async_commit();
 
     unsigned qfrag[DMAX / 16][4];
@@ -277,16 +269,21 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
 
     for (int it = 0; it < n_tiles; ++it) {
-        cp_async_wait<0>();
+        // the other stage is free (the warp finished tile it - 1): start tile it + 1 into it
+        long long next = -1;
+        if (it + 1 < n_tiles) next = row_offset(src, (t_begin + it + 1) * TK + lane, lo, pos, status);
+        cp_async_wait<0>();                          // tile ``it`` has landed
         __syncwarp();
         if (it + 1 < n_tiles) {
+            offs[lane] = next;
+            __syncwarp();
             bf16* st = smem + ((it + 1) & 1) * 2 * TILE;
-            load_stage<DMAX, 32, TK>(st, st + TILE, src, (t_begin + it + 1) * TK, lo, pos, status);
+            copy_rows<DMAX, 32, TK>(st, st + TILE, src, offs);
         }
         cp_async_commit();
-        const bf16* st = smem + (it & 1) * 2 * TILE;
+        const bf16* sp = smem + (it & 1) * 2 * TILE;
         const int first = (t_begin + it) * TK;
-        compute_tile<DMAX, UPPER>(st, st + TILE, qfrag, o, m, l, first, d, scale_log2, pos, pos, lo, lo,
+        compute_tile<DMAX, UPPER>(sp, sp + TILE, qfrag, o, m, l, first, d, scale_log2, pos, pos, lo, lo,
                                   first + TK - 1 > pos || first < lo);
         __syncwarp();
     }
@@ -365,9 +362,10 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
-    constexpr int STAGE = PREFILL_KEYS * DMAX;       // elements per K (or V) stage
+    __shared__ long long offs[2][PREFILL_KEYS];
     constexpr int THREADS = PREFILL_WARPS * 32;
+    bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+    constexpr int STAGE = PREFILL_KEYS * pitch<DMAX>();   // elements per K (or V) stage
     const int kvh = blockIdx.y, r = blockIdx.z;
     const int G = nq / nkv;
     const int tok0 = cu_q[r], n_q = cu_q[r + 1] - tok0;
@@ -388,8 +386,15 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
     const int hi = start + qi_last;
     const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
     const int s_begin = lo / PREFILL_KEYS, n_stages = hi / PREFILL_KEYS - s_begin + 1;
-    KvSource src{kc, vc, block_table + (size_t)r * bt_stride, nkv, kvh, d, ps, num_pages};
-    load_stage<DMAX, THREADS, PREFILL_KEYS>(smem, smem + STAGE, src, s_begin * PREFILL_KEYS, lo, hi, status);
+    KvSource src{kc, vc, block_table + (size_t)r * bt_stride, nkv, kvh, d, ps, (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1,
+                 num_pages};
+    // threads 0 .. 63 look up one key each of the stage after next; all threads copy
+    if (threadIdx.x < PREFILL_KEYS) {
+        offs[0][threadIdx.x] = row_offset(src, s_begin * PREFILL_KEYS + threadIdx.x, lo, hi, status);
+        offs[1][threadIdx.x] = n_stages > 1 ? row_offset(src, (s_begin + 1) * PREFILL_KEYS + threadIdx.x, lo, hi, status) : -1;
+    }
+    __syncthreads();
+    copy_rows<DMAX, THREADS, PREFILL_KEYS>(smem, smem + STAGE, src, offs[0]);
     cp_async_commit();
 
     unsigned qfrag[DMAX / 16][4];
@@ -412,7 +417,7 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
         __syncthreads();                 // stage ``it`` has landed; everyone is done with stage it - 1
         if (it + 1 < n_stages) {
             bf16* st = smem + ((it + 1) & 1) * 2 * STAGE;
-            load_stage<DMAX, THREADS, PREFILL_KEYS>(st, st + STAGE, src, (s_begin + it + 1) * PREFILL_KEYS, lo, hi, status);
+            copy_rows<DMAX, THREADS, PREFILL_KEYS>(st, st + STAGE, src, offs[(it + 1) & 1]);
         }
         cp_async_commit();
         const bf16* st = smem + (it & 1) * 2 * STAGE;
@@ -422,10 +427,14 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
             if (w_any && first <= w_pos_max && first + TK - 1 >= w_lo_min) {
                 // rows differ in what they see only near the diagonal and the window edge
                 const bool masked = first + TK - 1 > w_pos_min || first < w_lo_max || !(v0 && v1);
-                compute_tile<DMAX, true>(st + sub * TK * DMAX, st + STAGE + sub * TK * DMAX, qfrag, o, m, l, first, d,
-                                         scale_log2, pos0, pos1, lo0, lo1, masked);
+                compute_tile<DMAX, true>(st + sub * TK * pitch<DMAX>(), st + STAGE + sub * TK * pitch<DMAX>(), qfrag, o, m,
+                                         l, first, d, scale_log2, pos0, pos1, lo0, lo1, masked);
             }
         }
+        // offsets of stage it + 2 go where those of stage ``it`` were: all copies of stage ``it``'s
+        // offsets were issued before the barrier above, and the next barrier publishes the new ones
+        if (it + 2 < n_stages && threadIdx.x < PREFILL_KEYS)
+            offs[it & 1][threadIdx.x] = row_offset(src, (s_begin + it + 2) * PREFILL_KEYS + threadIdx.x, lo, hi, status);
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -450,8 +459,8 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
 
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int DMAX> size_t decode_smem() { return (size_t)DECODE_STAGES * 2 * TK * DMAX * sizeof(bf16); }
-template <int DMAX> size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * PREFILL_KEYS * DMAX * sizeof(bf16); }
+template <int DMAX> size_t decode_smem() { return (size_t)DECODE_STAGES * 2 * TK * pitch<DMAX>() * sizeof(bf16); }
+template <int DMAX> size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * PREFILL_KEYS * pitch<DMAX>() * sizeof(bf16); }
 
 template <typename K> int allow_smem(K kernel, size_t bytes, const char* what) {
     if (bytes > 48 * 1024) {

@@ -230,10 +230,11 @@ def scratch(device, nbytes: int) -> torch.Tensor:
 
 
 def decode_splits(requests: int, nkv: int, max_ctx_len: int) -> int:
-    """How many ways the keys of a request are split in decode: enough blocks to fill the GPU,
-    but no split shorter than two tiles of 32 keys."""
+    """How many ways the keys of a request are split in decode: about one round of resident blocks
+    (six one-warp blocks fit an SM), but no split shorter than two tiles of 32 keys."""
     tiles = max(1, -(-max_ctx_len // 32))
-    want = max(1, (7 * SM_COUNT) // max(1, requests * nkv))      # seven one-warp blocks fit an SM
+    pairs = max(1, requests * nkv)
+    want = max(1, (6 * SM_COUNT + pairs // 2) // pairs)
     return int(max(1, min(want, tiles // 2)))
 
 

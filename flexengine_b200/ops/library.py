@@ -137,11 +137,26 @@ def build(group: str, force: bool = False, verbose: bool = True) -> str:
             if proc.returncode != 0:
                 raise KernelLibraryError(f"linking {group} failed:\n{proc.stdout}\n{proc.stderr}")
             os.replace(tmp, path)
+            _prune(root, group, keep=_sources_hash(group))
         finally:
             stop.set()
         if verbose:
             _log(f"built {os.path.basename(path)} in {time.time() - started:.0f} s")
     return path
+
+
+def _prune(root: str, group: str, keep: str) -> None:
+    """Remove builds of ``group`` made from older sources."""
+    for name in os.listdir(root):
+        stale_lib = name.startswith(f"libflexengine_{group}.") and name.endswith(".so") and keep not in name
+        stale_obj = name.startswith(f"obj_{group}_") and keep not in name
+        if stale_lib:
+            try:
+                os.remove(os.path.join(root, name))
+            except OSError:
+                pass
+        elif stale_obj:
+            shutil.rmtree(os.path.join(root, name), ignore_errors=True)
 
 
 def load(group: str) -> ctypes.CDLL:
