@@ -552,3 +552,43 @@ extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out
 #undef FE_PREFILL
     return fe_check_launch("paged_prefill");
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate: the scratch memory is a fixed
+// array of this library (see no_alloc_api.h for who needs this and what the limits are).
+#include "no_alloc_api.h"
+
+// In host code this name is only a handle for the symbol, not a device address: the address a
+// kernel can use comes from cudaGetSymbolAddress, looked up once per device below.
+static __device__ __align__(256) unsigned char g_static_decode_scratch[FE_STATIC_SCRATCH_BYTES];
+
+extern "C" long long fe_static_scratch_bytes(void) { return (long long)FE_STATIC_SCRATCH_BYTES; }
+
+extern "C" int fe_paged_decode_mma_static(const void* q, long long q_stride, void* out, long long out_stride,
+                                          const void* kc, const void* vc, const int* block_table, int bt_stride,
+                                          const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d,
+                                          int ps, int num_pages, float scale, int window, int splits, int* status,
+                                          cudaStream_t stream) {
+    constexpr int MAX_DEVICES = 64;
+    static void* address_on[MAX_DEVICES] = {nullptr};
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    FE_REQUIRE(err == cudaSuccess, "paged_decode (static scratch): cudaGetDevice: %s", cudaGetErrorString(err));
+    FE_REQUIRE(device >= 0 && device < MAX_DEVICES, "paged_decode (static scratch): device %d is out of range", device);
+    if (address_on[device] == nullptr) {
+        // set-up, once per device, with that device current: ask the runtime where the array lives there
+        void* where = nullptr;
+        err = cudaGetSymbolAddress(&where, g_static_decode_scratch);
+        FE_REQUIRE(err == cudaSuccess && where != nullptr, "paged_decode (static scratch): cudaGetSymbolAddress: %s",
+                   cudaGetErrorString(err));
+        address_on[device] = where;
+    }
+    FE_REQUIRE(requests >= 0 && nq > 0 && d > 0 && splits >= 1, "paged_decode (static scratch): bad sizes");
+    const long long need = fe_paged_decode_scratch_bytes(requests, nq, d, splits);
+    FE_REQUIRE(need <= (long long)FE_STATIC_SCRATCH_BYTES,
+               "paged_decode (static scratch): %d requests x %d heads x %d splits x head size %d need %lld bytes of "
+               "scratch; the built-in array holds %lld (use fewer splits or requests, or the entry point that takes "
+               "the caller's scratch)", requests, nq, splits, d, need, (long long)FE_STATIC_SCRATCH_BYTES);
+    return fe_paged_decode_mma(q, q_stride, out, out_stride, address_on[device], kc, vc, block_table, bt_stride, cu_q,
+                               q_start, requests, nq, nkv, d, ps, num_pages, scale, window, splits, status, stream);
+}
