@@ -298,8 +298,8 @@ def run_reference(args):
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=32)
-    p.add_argument("--warmup", type=int, default=4)
+    p.add_argument("--steps", type=int, default=16)
+    p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")

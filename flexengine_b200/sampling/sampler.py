@@ -23,6 +23,7 @@ class Sampler:
             from .. import ops as cuda_ops
             ops = cuda_ops
         self.ops = ops
+        self._zeros = {}
 
     def sample(self, logits: torch.Tensor, temperatures, top_ks, seeds, draws) -> list:
         """logits float32 [R, V]; the other arguments are sequences of length R.  Returns R token ids."""
@@ -31,8 +32,23 @@ class Sampler:
         for t, k in zip(temperatures, top_ks):
             validate_sampling(t, k)
         dev = logits.device
-        temperature = torch.tensor(list(temperatures), dtype=torch.float32, device=dev)
-        top_k = torch.tensor(list(top_ks), dtype=torch.int32, device=dev)
-        seed = torch.tensor(list(seeds), dtype=torch.int64, device=dev)
-        draw = torch.tensor(list(draws), dtype=torch.int64, device=dev)
-        return self.ops.sample(logits, temperature, top_k, seed, draw).tolist()
+        n = len(temperatures)
+        if all(t == 0.0 for t in temperatures):
+            # greedy rows need no parameters: zeros kept on the device, no copy per step
+            key = (str(dev), n)
+            if key not in self._zeros:
+                self._zeros[key] = (torch.zeros(n, dtype=torch.float32, device=dev),
+                                    torch.zeros(n, dtype=torch.int32, device=dev),
+                                    torch.zeros(n, dtype=torch.int64, device=dev))
+            temperature, top_k, zero64 = self._zeros[key]
+            return self.ops.sample(logits, temperature, top_k, zero64, zero64).tolist()
+        # one host buffer, one copy: [temperature bits | top_k | seed lo, hi | draw lo, hi] as 64-bit words
+        packed = torch.empty((4, n), dtype=torch.int64, pin_memory=dev.type == "cuda")
+        packed[0] = torch.tensor(list(temperatures), dtype=torch.float32).view(torch.int32).to(torch.int64)
+        packed[1] = torch.tensor(list(top_ks), dtype=torch.int64)
+        packed[2] = torch.tensor(list(seeds), dtype=torch.int64)
+        packed[3] = torch.tensor(list(draws), dtype=torch.int64)
+        on_dev = packed.to(dev, non_blocking=True)
+        temperature = on_dev[0].to(torch.int32).view(torch.float32)
+        top_k = on_dev[1].to(torch.int32)
+        return self.ops.sample(logits, temperature, top_k, on_dev[2].contiguous(), on_dev[3].contiguous()).tolist()
