@@ -161,6 +161,20 @@ def skinny_gemm(x, w, epilogue: int = EPI_BF16):
     return out
 
 
+def gemm_tcgen05(x, w, epilogue: int = EPI_BF16):
+    """x [M, K] times w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator);
+    epilogue EPI_BF16 or EPI_SWIGLU.  See csrc/gemm_tcgen05.cu."""
+    _need_cuda(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not x.is_contiguous() or not w.is_contiguous():
+        raise TypeError("gemm_tcgen05 takes contiguous bfloat16 operands")
+    out = torch.empty((M, N // 2 if epilogue == EPI_SWIGLU else N), dtype=torch.bfloat16, device=x.device)
+    _run(_bf16(), "fe_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue),
+         _ptr(status_word(x.device)), _stream())
+    return out
+
+
 def swiglu(gate_up, intermediate):
     _need_cuda(gate_up)
     T = gate_up.shape[0]

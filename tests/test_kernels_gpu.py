@@ -112,6 +112,28 @@ def test_skinny_gemm(M, N, K, gen):
     assert torch.equal(ops().skinny_gemm(x, w, ops().EPI_F32), ops().skinny_gemm(x, w, ops().EPI_F32))
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (128, 128, 256), (100, 200, 192), (300, 384, 3584), (2048, 512, 320),
+                                   (129, 24, 72)])
+def test_gemm_tcgen05(M, N, K, gen):
+    """The tcgen05 / TMEM / TMA product against float32 PyTorch: tails in M, N and K, several
+    passes round the ring of stages, both epilogues."""
+    x, w = rand((M, K), torch.bfloat16, gen), rand((N, K), torch.bfloat16, gen, 0.05)
+    want = x.float() @ w.float().T
+    bar16 = dict(atol=2e-2 * max(1.0, float(want.abs().max()) / 4), rtol=2e-2)
+    torch.testing.assert_close(ops().gemm_tcgen05(x, w, ops().EPI_BF16).float(), want, **bar16)
+    if N % 2 == 0:
+        got = ops().gemm_tcgen05(x, w, ops().EPI_SWIGLU)
+        assert tuple(got.shape) == (M, N // 2)
+        g, u = want[:, :N // 2], want[:, N // 2:]
+        torch.testing.assert_close(got.float(), g / (1 + torch.exp(-g)) * u, **bar16)
+    ops().check_status(DEV)
+
+
+def test_gemm_tcgen05_refuses_what_it_cannot_take(gen):
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        ops().gemm_tcgen05(rand((4, 60), torch.bfloat16, gen), rand((32, 60), torch.bfloat16, gen))
+
+
 def test_skinny_gemm_refuses_what_it_cannot_take(gen):
     x, w = rand((4, 80), torch.bfloat16, gen), rand((32, 80), torch.bfloat16, gen)
     with pytest.raises(RuntimeError, match="multiple of 64"):
