@@ -2,18 +2,22 @@
 // accumulator in tensor memory (TMEM), operands brought to shared memory by TMA tensor copies
 // (128-byte swizzle), completion tracked by mbarriers.  bfloat16 inputs, float accumulation.
 //
-// One block computes a 128-row tile of the output.  Warp 0 (one lane) is the TMA producer, warp 1
-// (one lane) issues the MMAs and owns the TMEM allocation, warps 2..5 are the epilogue: each reads
-// its quarter of the accumulator's lanes with tcgen05.ld and writes the rows out.
-//   plain epilogue:  a 128 x 128 output tile, bfloat16
+// Blocks are persistent: one per SM, each walks over output tiles (row tiles fastest, so blocks
+// that run together share their rows of W: W is larger than L2 and then comes from HBM once).
+// Warp 0 (one lane) is the TMA producer, warp 1 (one lane) issues the MMAs and owns the TMEM
+// allocation, warps 2..5 are the epilogue: each reads its quarter of the accumulator's lanes with
+// tcgen05.ld and writes the rows out.  The accumulator is double-buffered in TMEM (2 x 256
+// columns), so the epilogue of one tile runs under the MMAs of the next.  UMMA shape 128 x 256 x 16.
+//   plain epilogue:  a 128 x 256 output tile, bfloat16
 //   SwiGLU epilogue: W is [2I, K] (gate rows, then up rows); the block loads 128 gate rows and
 //                    their 128 up rows as one 256-row B tile, so accumulator columns j and 128 + j
-//                    belong to output column j: out = silu(gate) * up, bfloat16 [M, I].
+//                    belong to output column j: out = silu(gate) * up, a 128 x 128 tile of bfloat16 [M, I].
 // The reference runs these products through cuBLAS (inference/models/qwen2.py:99-101,129-130).
 //
 // Every wait on an mbarrier is bounded (about two seconds): when it runs out the thread records it
-// in the status word and leaves its loop; all threads still meet at the final barrier, tensor
-// memory is freed, the block returns.  No cluster launch, no multicast.
+// in the status word and raises a flag that makes every role leave its loop; all threads still
+// meet at the final barrier, tensor memory is freed, the block returns.  No cluster launch, no
+// multicast.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -35,6 +39,9 @@ __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)_
 
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -115,33 +122,37 @@ template <int NCOLS> __device__ __forceinline__ void tmem_dealloc(unsigned taddr
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "n"(NCOLS) : "memory");
 }
 
-// BN: accumulator columns (UMMA N): 128 for the plain epilogue, 256 for SwiGLU (128 gate + 128 up).
-template <int BN, int EPI>
+constexpr int BN = 256;             // accumulator columns of one tile = UMMA N
+constexpr int ACC_BUFFERS = 2;
+
+template <int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    bf16* __restrict__ out, int M, int N_out, int K, int up_row_offset, int* __restrict__ status) {
+                    bf16* __restrict__ out, int M, int N_out, int K, int up_row_offset, int m_tiles, int n_tiles,
+                    int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], accum_bar;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES];
+    __shared__ __align__(8) unsigned long long acc_full[ACC_BUFFERS], acc_empty[ACC_BUFFERS];
     __shared__ unsigned tmem_holder;
+    __shared__ volatile int give_up;
     constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : 256;      // output columns per tile
     // the dynamic segment is aligned by hand: the swizzle atoms want 1024 bytes
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     griddep_wait();
     griddep_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // row tiles are the fast grid dimension: blocks that run together share their rows of W, which
-    // then come from HBM once and from L2 for the other row tiles (W is larger than L2, x is not)
-    const int m0 = blockIdx.x * BM;
-    const int n0 = blockIdx.y * 128;             // output columns of this block (both epilogues write 128)
     const int num_kb = (K + BK - 1) / BK;
+    const int total_tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(&accum_bar, 1);
+        for (int b = 0; b < ACC_BUFFERS; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) tmem_alloc<BN>(&tmem_holder);
+    if (warp == 1) tmem_alloc<ACC_BUFFERS * BN>(&tmem_holder);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -149,81 +160,87 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ----
-        bool ok = true;
-        int issued = 0;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-            const int s = kb % STAGES, use = kb / STAGES;
-            ok = mbar_wait(&empty_bar[s], (use & 1) ^ 1);         // free from the start: parity 1 passes at once
-            if (!ok) break;
-            unsigned char* a = smem + s * STAGE_BYTES;
-            unsigned char* b = a + A_BYTES;
-            mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-            tma_load_2d(a, &map_a, kb * BK, m0, &full_bar[s]);
-            if (EPI == EPI_SWIGLU) {
-                tma_load_2d(b, &map_b, kb * BK, n0, &full_bar[s]);                              // 128 gate rows
-                tma_load_2d(b + 128 * BK * 2, &map_b, kb * BK, up_row_offset + n0, &full_bar[s]);  // their up rows
-            } else {
-                tma_load_2d(b, &map_b, kb * BK, n0, &full_bar[s]);
+        int kbg = 0;                                   // k blocks issued so far, over all tiles
+        for (int t = blockIdx.x; t < total_tiles && !give_up; t += gridDim.x) {
+            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * OUT_COLS;
+            for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+                const int s = kbg % STAGES, use = kbg / STAGES;
+                if (!mbar_wait(&empty_bar[s], (use & 1) ^ 1)) { give_up = 1; break; }   // parity 1 passes at once at the start
+                unsigned char* a = smem + s * STAGE_BYTES;
+                unsigned char* b = a + A_BYTES;
+                mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+                tma_load_2d(a, &map_a, kb * BK, m0, &full_bar[s]);
+                tma_load_2d(b, &map_b, kb * BK, n0, &full_bar[s]);                      // 128 rows of W (gate rows for SwiGLU)
+                tma_load_2d(b + 128 * BK * 2, &map_b, kb * BK, (EPI == EPI_SWIGLU ? up_row_offset + n0 : n0 + 128),
+                            &full_bar[s]);                                              // the next 128 rows, or their up rows
             }
-            ++issued;
         }
-        if (!ok && status) atomicOr(status, FE_STATUS_WAIT_EXPIRED);
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
         constexpr unsigned idesc = instr_desc(BM, BN);
-        bool ok = true;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-            const int s = kb % STAGES, use = kb / STAGES;
-            ok = mbar_wait(&full_bar[s], use & 1);
-            if (!ok) break;
+        int kbg = 0, i = 0;
+        for (int t = blockIdx.x; t < total_tiles && !give_up; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            if (!mbar_wait(&acc_empty[buf], ((i >> 1) & 1) ^ 1)) { give_up = 1; break; }     // the epilogue has drained it
             tc_fence_after();
-            const unsigned char* a = smem + s * STAGE_BYTES;
-            const unsigned long long adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
+            const unsigned acc = tmem_base + buf * BN;
+            for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
+                const int s = kbg % STAGES, use = kbg / STAGES;
+                if (!mbar_wait(&full_bar[s], use & 1)) { give_up = 1; break; }
+                tc_fence_after();
+                const unsigned char* a = smem + s * STAGE_BYTES;
+                const unsigned long long adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-                // 16 elements along K = 32 bytes inside the swizzle atom: +2 in the address field
-                umma(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 elements along K = 32 bytes inside the swizzle atom: +2 in the address field
+                    umma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[s]);            // the stage is free once these MMAs have read it
             }
-            umma_commit(&empty_bar[s]);                 // the stage is free once these MMAs have read it
+            umma_commit(&acc_full[buf]);               // arrives even after a failed wait, so the epilogue is released
         }
-        umma_commit(&accum_bar);                        // arrives even after a failed wait, so the epilogue is released
-        if (!ok && status) atomicOr(status, FE_STATUS_WAIT_EXPIRED);
     } else if (warp >= 2) {
         // ---- epilogue: warp w may read TMEM lanes 32 (w % 4) .. + 31 ----
-        const bool ok = mbar_wait(&accum_bar, 0);
-        tc_fence_after();
-        if (!ok) {
-            if (lane == 0 && status) atomicOr(status, FE_STATUS_WAIT_EXPIRED);
-        } else {
-            const int quarter = warp & 3;
+        const int quarter = warp & 3;
+        int i = 0;
+        for (int t = blockIdx.x; t < total_tiles && !give_up; t += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * OUT_COLS;
+            if (!mbar_wait(&acc_full[buf], (i >> 1) & 1)) { give_up = 1; break; }
+            tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
-            const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
+            const unsigned lane_addr = tmem_base + buf * BN + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < 128; c += 32) {
+            for (int c = 0; c < OUT_COLS; c += 32) {
                 float v[32];
                 tmem_load32(lane_addr + c, v);
                 if (EPI == EPI_SWIGLU) {
                     float u[32];
                     tmem_load32(lane_addr + 128 + c, u);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
+                    for (int j = 0; j < 32; ++j) v[j] = v[j] / (1.f + expf(-v[j])) * u[j];
                 }
                 if (row < M) {
                     bf16* dst = out + (size_t)row * N_out + n0 + c;
                     if (n0 + c + 32 <= N_out && (N_out & 7) == 0) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) store8<bf16>(dst + i, v + i);
+                        for (int j = 0; j < 32; j += 8) store8<bf16>(dst + j, v + j);
                     } else {
-                        for (int i = 0; i < 32; ++i)
-                            if (n0 + c + i < N_out) dst[i] = __float2bfloat16_rn(v[i]);
+                        for (int j = 0; j < 32; ++j)
+                            if (n0 + c + j < N_out) dst[j] = __float2bfloat16_rn(v[j]);
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);       // this warp has read its quarter of the buffer
         }
     }
+    __syncthreads();
+    if (give_up && threadIdx.x == 0 && status) atomicOr(status, FE_STATUS_WAIT_EXPIRED);
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc<BN>(tmem_base);
+    if (warp == 1) tmem_dealloc<ACC_BUFFERS * BN>(tmem_base);
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -257,18 +274,28 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
     return 0;
 }
 
-template <int BN, int EPI>
+template <int EPI>
 int launch(const void* x, const void* W, void* out, int M, int N, int K, int* status, cudaStream_t stream) {
     const int n_out = EPI == EPI_SWIGLU ? N / 2 : N;
+    constexpr int OUT_COLS = EPI == EPI_SWIGLU ? 128 : 256;
     CUtensorMap map_a, map_b;
     if (make_map(&map_a, x, M, K, BM)) return 1;
     if (make_map(&map_b, W, N, K, 128)) return 1;
     const size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
-    const cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FE_REQUIRE(err == cudaSuccess, "gemm_tcgen05: %s", cudaGetErrorString(err));
-    const dim3 grid((M + BM - 1) / BM, (n_out + 127) / 128);
-    FE_REQUIRE(grid.y <= 65535, "gemm_tcgen05: too many column tiles (%u)", grid.y);
-    fe::launch(gemm_tcgen05_kernel<BN, EPI>, grid, THREADS, smem, stream, map_a, map_b, (bf16*)out, M, n_out, K, n_out, status);
+    static int sms = 0;
+    if (!sms) {
+        int device = 0;
+        cudaGetDevice(&device);
+        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        FE_REQUIRE(err == cudaSuccess && sms > 0, "gemm_tcgen05: cannot read the number of SMs");
+    }
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (n_out + OUT_COLS - 1) / OUT_COLS;
+    const long long total = (long long)m_tiles * n_tiles;
+    const int blocks = (int)(total < sms ? total : sms);        // one persistent block per SM
+    fe::launch(gemm_tcgen05_kernel<EPI>, blocks, THREADS, smem, stream, map_a, map_b, (bf16*)out, M, n_out, K, n_out,
+               m_tiles, n_tiles, status);
     return fe_check_launch("gemm_tcgen05");
 }
 
@@ -280,10 +307,10 @@ extern "C" int fe_gemm_tcgen05(const void* x, const void* W, void* out, int M, i
     FE_REQUIRE(M >= 1 && N >= 1 && K >= 8, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     FE_REQUIRE(K % 8 == 0, "gemm_tcgen05: K = %d must be a multiple of 8 (rows must start on 16-byte boundaries)", K);
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
-    if (epilogue == EPI_BF16) return launch<128, EPI_BF16>(x, W, out, M, N, K, status, stream);
+    if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, status, stream);
     if (epilogue == EPI_SWIGLU) {
         FE_REQUIRE(N % 2 == 0, "gemm_tcgen05: SwiGLU needs an even number of weight rows, got %d", N);
-        return launch<256, EPI_SWIGLU>(x, W, out, M, N, K, status, stream);
+        return launch<EPI_SWIGLU>(x, W, out, M, N, K, status, stream);
     }
     FE_REQUIRE(false, "gemm_tcgen05: unknown epilogue %d", epilogue);
 }

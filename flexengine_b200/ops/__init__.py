@@ -161,6 +161,16 @@ def skinny_gemm(x, w, epilogue: int = EPI_BF16):
     return out
 
 
+TCGEN05_MIN_ROWS = 1024      # measured: from about this many rows the fused kernel matches the library + activation
+
+
+def tcgen05_ok(x, w) -> bool:
+    """Whether the tcgen05 kernel is used for this product: bfloat16, many rows (prefill), K a multiple of 8."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] >= TCGEN05_MIN_ROWS
+            and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
 def gemm_tcgen05(x, w, epilogue: int = EPI_BF16):
     """x [M, K] times w [N, K]^T on tcgen05 tensor cores (TMA operands, TMEM accumulator);
     epilogue EPI_BF16 or EPI_SWIGLU.  See csrc/gemm_tcgen05.cu."""
@@ -190,6 +200,8 @@ def linear_swiglu(x, w, intermediate):
     """silu(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]); one kernel for a handful of rows."""
     if skinny_ok(x, w) and w.shape[0] == 2 * intermediate:
         return skinny_gemm(x, w, EPI_SWIGLU)
+    if tcgen05_ok(x, w) and w.shape[0] == 2 * intermediate:
+        return gemm_tcgen05(x, w, EPI_SWIGLU)
     return swiglu(linear(x, w), intermediate)
 
 
