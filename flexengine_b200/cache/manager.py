@@ -71,11 +71,12 @@ class CacheManager:
                 self.groups.append(PagedGroup(spec, n, self.page_size, dtype, self.device))
         self.requests: dict[str, RequestCache] = {}
         self.free_state_slots = list(range(self.max_requests - 1, -1, -1))
+        self._paged = [(gi, g) for gi, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
 
     # --- sizes -----------------------------------------------------------------------------
     @property
     def paged(self):
-        return [(gi, g) for gi, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
+        return self._paged
 
     @property
     def free_pages(self) -> int:
@@ -128,6 +129,8 @@ class CacheManager:
         fresh = rc is None
         if fresh:
             rc = self.admit(request_id)
+        elif all(len(rc.tables[gi]) * self.page_size >= target_tokens for gi, _ in self._paged):
+            return                      # already reserved (the usual case in decode)
         needs = [(gi, g, self._pages_needed(rc, gi, target_tokens)) for gi, g in self.paged]
         short = [(g.spec.name, n, g.pool.free_pages) for _, g, n in needs if n > g.pool.free_pages]
         if short:

@@ -109,6 +109,9 @@ class ModelRunner:
     def _reserve(self, entries) -> None:
         """Reserve for the whole batch or for none of it."""
         cache = self.cache
+        if all(e.request_id in cache.requests and
+               cache.reserved_tokens(e.request_id) >= cache.tokens_of(e.request_id) + len(e.tokens) for e in entries):
+            return                      # the scheduler reserved already
         made = []
         try:
             for e in entries:
