@@ -165,3 +165,20 @@ def test_engine_with_decode_graphs_generates_the_same_tokens(model_dirs):
     for prompt, out in zip(prompts, outputs):
         assert out.token_ids == plain_model.greedy_generate(config, weights, prompt, 10)
     assert engine.runner.graph_replays > 0 and engine.cache.used_pages == 0
+
+
+def test_generate_command_line(model_dirs, capsys):
+    """``flexengine generate`` on a model folder and with --random-weights, options under the reference's names."""
+    import json
+    from flexengine_b200.cli import main
+    main(["generate", "--model", model_dirs["A"], "--prompt-ids", "3 14 15 92 65", "--prompt-ids", "7,8,9", "--max-tokens", "6",
+          "--dtype", "float32", "--token-budget", "16", "--block-size", "16", "--num-blocks", "16", "--max-model-len", "128",
+          "--max-num-seqs", "2", "--policy", "decode_first"])
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    config, weights = plain_model.read_model_folder(model_dirs["A"], DEV)
+    assert lines[0]["token_ids"] == plain_model.greedy_generate(config, weights, [3, 14, 15, 92, 65], 6)
+    assert lines[1]["token_ids"] == plain_model.greedy_generate(config, weights, [7, 8, 9], 6)
+    main(["generate", "--model", model_dirs["A"], "--random-weights", "--weights-seed", "2", "--prompt-ids", "1 2 3", "--max-tokens", "4",
+          "--temperature", "0.7", "--top-k", "10", "--seed", "5", "--num-blocks", "16", "--max-model-len", "128", "--cuda-graph"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert len(out["token_ids"]) == 4 and out["finish_reason"] in ("length", "stop")

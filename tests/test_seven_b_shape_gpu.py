@@ -1,0 +1,76 @@
+"""The layer sizes of the Qwen2.5-7B shape (hidden 3584, 28 heads over 4, head size 128, feed-forward
+18944, vocabulary 152064) with two layers and random weights drawn on the device: the kernels at
+the sizes they are tuned for (the weight-streaming GEMM's wide and deep variants, the tcgen05
+product from 1,024 rows, split-KV decode under CUDA graphs) against the plain implementation."""
+import random
+
+import pytest
+import torch
+
+import helpers
+import plain_model
+from flexengine_b200.cache import CacheManager
+from flexengine_b200.config import resolve
+from flexengine_b200.engine import ModelRunner, StepEntry
+from flexengine_b200.weights import checkpoint_tensors, random_model, random_tensor
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+SHAPE = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=3584,
+             num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944, vocab_size=152064,
+             rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+
+
+@pytest.fixture(scope="module")
+def plain_weights():
+    _cfg, plan = resolve(SHAPE)
+    return {name: random_tensor(plan, name, shape, 5, torch.bfloat16, DEV) for name, shape in checkpoint_tensors(plan)}
+
+
+def runner_for(dtype, pages, max_requests=3):
+    _cfg, plan, model = random_model(SHAPE, seed=5, dtype=dtype, device=DEV)
+    torch_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    cache = CacheManager(plan.cache_groups, pages, 16, max_requests, torch_dtype, DEV)
+    return ModelRunner(model, cache)
+
+
+def test_bfloat16_prefill_on_tcgen05_then_graph_decode(plain_weights):
+    rng = random.Random(1)
+    long_ids = helpers.random_prompt(rng, 1100, SHAPE["vocab_size"])
+    short = [helpers.random_prompt(rng, n, SHAPE["vocab_size"]) for n in (40, 75)]
+    runner = runner_for("bfloat16", 90)
+    runner.enable_decode_graphs(3, 1200)
+    rows = {0: [], 1: [], 2: []}
+    rows[0].append(runner.step([StepEntry("r0", long_ids[:1030], [0, 500, 1023, 1029])]))       # 1,030 rows: tcgen05 product
+    for j, ids in enumerate(short, start=1):
+        rows[j].append(runner.step([StepEntry(f"r{j}", ids[:-30], [len(ids) - 31])]))
+    # a mixed step: a portion of the long request beside decoded tokens of the others
+    out = runner.step([StepEntry("r0", long_ids[1030:1070], [39]), StepEntry("r1", short[0][-30:-29], [0]),
+                       StepEntry("r2", short[1][-30:-29], [0])])
+    rows[0].append(out[0:1]); rows[1].append(out[1:2]); rows[2].append(out[2:3])
+    for step in range(29):                                      # decode steps of all three, from CUDA graphs
+        out = runner.step([StepEntry("r0", [long_ids[1070 + step]], [0]), StepEntry("r1", [short[0][-29 + step]], [0]),
+                           StepEntry("r2", [short[1][-29 + step]], [0])])
+        for j in range(3):
+            rows[j].append(out[j:j + 1].clone())
+    assert runner.graph_replays == 29
+    from flexengine_b200 import ops
+    ops.check_status(DEV)
+    want = plain_model.forward_logits(SHAPE, plain_weights, long_ids[:1099]).cpu()
+    picks = [0, 500, 1023, 1029, 1069] + list(range(1070, 1099))
+    helpers.assert_logits_close(torch.cat(rows[0]), want[picks], "bfloat16", "7B-shape long request")
+    for j, ids in enumerate(short, start=1):
+        want = plain_model.forward_logits(SHAPE, plain_weights, ids).cpu()
+        helpers.assert_logits_close(torch.cat(rows[j]), want[len(ids) - 31:], "bfloat16", f"7B-shape short request {j}")
+
+
+def test_float32_path_at_the_seven_b_widths(plain_weights):
+    rng = random.Random(2)
+    ids = helpers.random_prompt(rng, 150, SHAPE["vocab_size"])
+    runner = runner_for("float32", 12, max_requests=1)
+    got = [runner.step([StepEntry("a", ids[:100], [0, 50, 99])])]
+    got.append(runner.step([StepEntry("a", ids[100:147], [46])]))
+    for p in range(147, 150):
+        got.append(runner.step([StepEntry("a", ids[p:p + 1], [0])]))
+    want = plain_model.forward_logits(SHAPE, plain_weights, ids).cpu()
+    helpers.assert_logits_close(torch.cat(got), want[[0, 50, 99, 146, 147, 148, 149]], "float32", "7B-shape float32")
