@@ -161,6 +161,38 @@ def skinny_gemm(x, w, epilogue: int = EPI_BF16):
     return out
 
 
+STREAM_MAX_ROWS = 128
+
+
+def stream_ok(x, w) -> bool:
+    """Whether the swap-AB tcgen05 streaming kernel is used: bfloat16, 9 to 128 rows, K a multiple of 8."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS
+            and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def stream_gemm(x, w, epilogue: int = EPI_BF16):
+    """x [M <= 128, K] times w [N, K]^T as a stream of w through tcgen05 (operands swapped);
+    see csrc/gemm_stream_tcgen05.cu."""
+    _need_cuda(x, w)
+    M, K = x.shape
+    N = w.shape[0]
+    lib = _bf16()
+    work = None
+    if epilogue == EPI_SWIGLU:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    elif epilogue == EPI_F32:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    else:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        splits = lib.fe_stream_gemm_splits(_c_int(N), _c_int(K))
+        if splits > 1:
+            work = scratch(x.device, splits * M * N * 4)
+    _run(lib, "fe_stream_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(out), _ptr(work), _c_int(M), _c_int(N), _c_int(K),
+         _c_int(epilogue), _ptr(status_word(x.device)), _stream())
+    return out
+
+
 TCGEN05_MIN_ROWS = 1024      # measured: from about this many rows the fused kernel matches the library + activation
 
 
