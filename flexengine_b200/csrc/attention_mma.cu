@@ -320,27 +320,46 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     }
 }
 
-// Merge the splits: grid (nq, requests), one thread per element of the head.
+// Merge the splits: grid (nq, requests), one thread per element of the head.  The weights of the
+// splits are computed once per block; the sums run four splits at a time so that their loads
+// overlap (the order of the additions is fixed all the same).
+constexpr int MAX_SPLITS_SHARED = 256;
+
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                       bf16* __restrict__ out, long long out_stride, const int* __restrict__ cu_q,
                                       int nq, int d, int splits) {
     griddep_wait();
     griddep_launch_dependents();
+    __shared__ float weight[MAX_SPLITS_SHARED];
+    __shared__ float inv_total;
     const int head = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + head) * splits;
-    float mx = -CUDART_INF_F;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_lse[base + s]);
-    bf16* op = out + (size_t)cu_q[b] * out_stride + (size_t)head * d;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        float acc = 0.f, wsum = 0.f;
-        if (mx != -CUDART_INF_F) {
-            for (int s = 0; s < splits; ++s) {
-                const float w = exp2f(part_lse[base + s] - mx);
-                wsum += w;
-                acc += w * part_o[(base + s) * d + j];
-            }
+    if (threadIdx.x < 32) {
+        float mx = -CUDART_INF_F;
+        for (int s = threadIdx.x; s < splits; s += 32) mx = fmaxf(mx, part_lse[base + s]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int s = threadIdx.x; s < splits; s += 32) {
+            const float w = mx == -CUDART_INF_F ? 0.f : exp2f(part_lse[base + s] - mx);
+            if (s < MAX_SPLITS_SHARED) weight[s] = w;
+            sum += w;
         }
-        op[j] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+        sum = warp_sum(sum);
+        if (threadIdx.x == 0) inv_total = sum > 0.f ? 1.f / sum : 0.f;
+    }
+    __syncthreads();
+    bf16* op = out + (size_t)cu_q[b] * out_stride + (size_t)head * d;
+    const float* po = part_o + base * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float acc = 0.f;
+        int s = 0;
+        for (; s + 4 <= splits; s += 4) {
+            const float v0 = po[(size_t)s * d + j], v1 = po[(size_t)(s + 1) * d + j];
+            const float v2 = po[(size_t)(s + 2) * d + j], v3 = po[(size_t)(s + 3) * d + j];
+            acc += weight[s] * v0; acc += weight[s + 1] * v1; acc += weight[s + 2] * v2; acc += weight[s + 3] * v3;
+        }
+        for (; s < splits; ++s) acc += weight[s] * po[(size_t)s * d + j];
+        op[j] = __float2bfloat16_rn(acc * inv_total);
     }
 }
 
@@ -498,7 +517,8 @@ extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out,
                                    cudaStream_t stream) {
     if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
-    FE_REQUIRE(splits >= 1 && splits <= 65535 && requests >= 0, "paged_decode: bad split or request count");
+    FE_REQUIRE(splits >= 1 && splits <= MAX_SPLITS_SHARED && requests >= 0,
+               "paged_decode: %d splits; this kernel takes 1 to %d", splits, MAX_SPLITS_SHARED);
     FE_REQUIRE(splits == 1 || scratch != nullptr, "paged_decode: %d splits need scratch memory", splits);
     if (requests == 0) return 0;
     float* part_o = (float*)scratch;

@@ -73,9 +73,33 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     // ---- maximum and its lowest index (needed by both branches)
     float best = -CUDART_INF_F;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < V; i += THREADS) {
-        const float v = sanitize(x[i]);
-        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    if ((V & 3) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
+        // four logits per load, two loads in flight per thread
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        const int n4 = V >> 2;
+        for (int i = tid; i < n4; i += 2 * THREADS) {
+            const float4 a = x4[i];
+            const int j = i + THREADS;
+            const float4 b = j < n4 ? x4[j] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+            const float va[4] = {a.x, a.y, a.z, a.w}, vb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v = sanitize(va[e]);
+                if (v > best || (v == best && 4 * i + e < best_i)) { best = v; best_i = 4 * i + e; }
+            }
+            if (j < n4) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float v = sanitize(vb[e]);
+                    if (v > best || (v == best && 4 * j + e < best_i)) { best = v; best_i = 4 * j + e; }
+                }
+            }
+        }
+    } else {
+        for (int i = tid; i < V; i += THREADS) {
+            const float v = sanitize(x[i]);
+            if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+        }
     }
     s_val[tid] = best; s_idx[tid] = best_i;
     __syncthreads();

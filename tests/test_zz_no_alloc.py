@@ -69,6 +69,6 @@ def test_static_scratch_entry_point_matches_the_ordinary_one():
     # more scratch than the built-in array holds: refused with the reason, nothing launched
     rc = fn(vp(q.data_ptr()), ll(q.stride(0)), vp(got.data_ptr()), ll(got.stride(0)), vp(kc.data_ptr()), vp(vc.data_ptr()),
             vp(table.data_ptr()), ci(table.shape[1]), vp(cu_q.data_ptr()), vp(q_start.data_ptr()), ci(len(positions)),
-            ci(nq), ci(nkv), ci(d), ci(ps), ci(kc.shape[0]), cf(scale), ci(0), ci(4000), vp(status.data_ptr()),
+            ci(nq), ci(nkv), ci(d), ci(ps), ci(kc.shape[0]), cf(scale), ci(0), ci(200), vp(status.data_ptr()),
             vp(torch.cuda.current_stream().cuda_stream))
     assert rc != 0 and b"built-in array holds" in lib.fe_last_error()
