@@ -21,7 +21,42 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int KSTEP = 64;       // k elements per warp step (4 MMAs)
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
+
+// What the fused query/key/value epilogue needs beside the product: bias, rotary table, where the
+// new keys and values go in the paged cache (see elementwise.cu for the unfused form of the same).
+struct QkvEpilogue {
+    const float* bias;          // [(nq + 2 nkv) d] or nullptr
+    const int* positions;       // [M]
+    const float* inv_freq;      // [d / 2]
+    const int* slot_mapping;    // [M] or nullptr (no cache write)
+    bf16* kc;
+    bf16* vc;
+    int nq, nkv, d, ps;
+    long long num_slots;
+    int* status;
+};
+
+// Tile ``tile`` of the fused epilogue: rotated heads (queries and keys) pair feature j with its
+// rotation partner j + d/2 in accumulator rows g and g + 8, so one thread holds both; value heads
+// take 16 consecutive features.
+__device__ __forceinline__ void qkv_tile_rows(const QkvEpilogue& e, int tile, int g, int& row0, int& row1, int& head,
+                                              int& j0) {
+    const int half = e.d >> 1;
+    const int rot_tiles = (e.nq + e.nkv) * (half >> 3);
+    if (tile < rot_tiles) {
+        head = tile / (half >> 3);
+        j0 = (tile - head * (half >> 3)) << 3;
+        row0 = head * e.d + j0 + g;
+        row1 = row0 + half;
+    } else {
+        const int t = tile - rot_tiles;
+        head = e.nq + e.nkv + t / (e.d >> 4);
+        j0 = (t % (e.d >> 4)) << 4;
+        row0 = head * e.d + j0 + g;
+        row1 = row0 + 8;
+    }
+}
 
 __device__ __forceinline__ uint4 ld_stream(const bf16* p) {
     uint4 v;
@@ -44,7 +79,7 @@ __device__ __forceinline__ void mma16816(float* c, unsigned a0, unsigned a1, uns
 template <int NT, int EPI, int RT, int PF>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
-                   int I) {
+                   int I, const QkvEpilogue qkv) {
     __shared__ float red[WARPS][RT * NT * 8 * 16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     // rows of W behind accumulator rows g and g + 8 of tile r
@@ -57,6 +92,9 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
         if (EPI == EPI_SWIGLU) {
             row0 = min(n0 + r * 8 + g, I - 1);          // gate row
             row1 = I + row0;                            // its up row
+        } else if (EPI == EPI_QKV) {
+            int head, j0;
+            qkv_tile_rows(qkv, blockIdx.x, g, row0, row1, head, j0);
         } else {
             row0 = min(n0 + r * 16 + g, N - 1);
             row1 = min(n0 + r * 16 + g + 8, N - 1);
@@ -134,7 +172,44 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             for (int e = 0; e < 4; ++e)
                 red[warp][(r * NT * 8 + nt * 8 + 2 * t + (e & 1)) * 16 + g + 8 * (e >> 1)] = acc[r][nt][e];
     __syncthreads();
-    if (EPI == EPI_SWIGLU) {
+    if (EPI == EPI_QKV) {
+        // bias, rotation by the token's position, and the write of new keys and values to their pages
+        int row0, row1, head, j0;
+        qkv_tile_rows(qkv, blockIdx.x, 0, row0, row1, head, j0);
+        const bool rotated = head < qkv.nq + qkv.nkv;
+        const int partner = rotated ? qkv.d >> 1 : 8;
+        for (int idx = threadIdx.x; idx < NT * 8 * 8; idx += WARPS * 32) {
+            const int m = idx >> 3, r = idx & 7;
+            if (m >= M) continue;
+            float a = 0.f, c = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) { a += red[w][m * 16 + r]; c += red[w][m * 16 + r + 8]; }
+            const int f0 = row0 + r, f1 = f0 + partner;              // features of the two values
+            if (qkv.bias) { a += qkv.bias[f0]; c += qkv.bias[f1]; }
+            if (rotated) {
+                float sn, cs;
+                sincosf((float)qkv.positions[m] * qkv.inv_freq[j0 + r], &sn, &cs);
+                const float ra = a * cs - c * sn, rc = c * cs + a * sn;
+                a = ra; c = rc;
+            }
+            const bf16 ba = __float2bfloat16_rn(a), bc = __float2bfloat16_rn(c);
+            bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N;
+            o[f0] = ba; o[f1] = bc;
+            if (head >= qkv.nq && qkv.slot_mapping) {
+                const long long slot = qkv.slot_mapping[m];
+                if (slot >= qkv.num_slots) {
+                    if (qkv.status) atomicOr(qkv.status, FE_STATUS_BAD_SLOT);
+                } else if (slot >= 0) {
+                    const bool is_k = head < qkv.nq + qkv.nkv;
+                    const int kvh = is_k ? head - qkv.nq : head - qkv.nq - qkv.nkv;
+                    bf16* dst = (is_k ? qkv.kc : qkv.vc) +
+                                (((slot / qkv.ps) * qkv.nkv + kvh) * qkv.ps + (slot % qkv.ps)) * qkv.d;
+                    dst[f0 - head * qkv.d] = ba;
+                    dst[f1 - head * qkv.d] = bc;
+                }
+            }
+        }
+    } else if (EPI == EPI_SWIGLU) {
         for (int idx = threadIdx.x; idx < RT * NT * 8 * 8; idx += WARPS * 32) {
             const int r = idx / (NT * 64), rest = idx - r * (NT * 64);
             const int m = rest >> 3, row = rest & 7;
@@ -164,15 +239,16 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 }
 
 template <int EPI>
-int launch(const void* x, const void* W, void* out, int M, int N, int K, int I, cudaStream_t stream) {
+int launch(const void* x, const void* W, void* out, int M, int N, int K, int I, cudaStream_t stream,
+           const QkvEpilogue& qkv = QkvEpilogue{}) {
     const int tiles = EPI == EPI_SWIGLU ? (I + 7) / 8 : (N + 15) / 16;
     // a wide matrix: two tiles per block; a narrow one (all its blocks are resident at once): every
     // warp sends twice as many loads ahead, which halves the number of round trips to memory
-    const bool wide = tiles >= 4 * 148;
+    const bool wide = EPI != EPI_QKV && tiles >= 4 * 148;
     const bool deep = !wide && tiles <= 2 * 148;
     const int blocks = wide ? (tiles + 1) / 2 : tiles;
 #define FE_SKINNY(NT, RT, PF) \
-    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF>, blocks, WARPS * 32, 0, stream, (const bf16*)x, (const bf16*)W, out, M, N, K, I)
+    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF>, blocks, WARPS * 32, 0, stream, (const bf16*)x, (const bf16*)W, out, M, N, K, I, qkv)
     if (M <= 8) { if (wide) FE_SKINNY(1, 2, 2); else if (deep) FE_SKINNY(1, 1, 4); else FE_SKINNY(1, 1, 2); }
     else { if (wide) FE_SKINNY(2, 2, 2); else if (deep) FE_SKINNY(2, 1, 4); else FE_SKINNY(2, 1, 2); }
 #undef FE_SKINNY
@@ -194,4 +270,20 @@ extern "C" int fe_skinny_gemm(const void* x, const void* W, void* out, int M, in
         return launch<EPI_SWIGLU>(x, W, out, M, N, K, N / 2, stream);
     }
     FE_REQUIRE(false, "skinny_gemm: unknown epilogue %d", epilogue);
+}
+
+// The query/key/value projection of an attention layer with its epilogue fused: y = x W^T + bias,
+// half-split rotation of the query and key heads by the tokens' positions, in place into
+// out [M, (nq + 2 nkv) d] (bfloat16), and the write of the new keys and values into their cache
+// slots.  The whole head is rotated (rotary width = head size, a multiple of 16); M <= 8.
+extern "C" int fe_skinny_qkv(const void* x, const void* W, void* out, const float* bias, const int* positions,
+                             const float* inv_freq, const int* slot_mapping, void* kc, void* vc, int M, int K, int nq,
+                             int nkv, int d, int ps, long long num_slots, int* status, cudaStream_t stream) {
+    FE_REQUIRE(M >= 1 && M <= 8, "skinny_qkv: %d rows; this kernel takes 1 to 8", M);
+    FE_REQUIRE(K > 0 && K % KSTEP == 0, "skinny_qkv: K = %d must be a positive multiple of %d", K, KSTEP);
+    FE_REQUIRE(d >= 16 && d % 16 == 0 && nq > 0 && nkv > 0 && ps > 0, "skinny_qkv: bad head size or counts");
+    FE_REQUIRE(positions != nullptr && inv_freq != nullptr, "skinny_qkv: positions and the rotary table are required");
+    FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_qkv: operands must be 16-byte aligned");
+    QkvEpilogue e{bias, positions, inv_freq, slot_mapping, (bf16*)kc, (bf16*)vc, nq, nkv, d, ps, num_slots, status};
+    return launch<EPI_QKV>(x, W, out, M, (nq + 2 * nkv) * d, K, 0, stream, e);
 }

@@ -258,6 +258,26 @@ def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cac
          _c_int(page_size), _c_ll(num_slots), _c_int(_code(qkv.dtype)), _ptr(status_word(qkv.device)), _stream())
 
 
+def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size):
+    """The query/key/value projection of an attention layer: h w^T + bias, rotary encoding of the
+    query and key heads, new keys and values written to their cache slots (slot_mapping None: no
+    write).  Returns qkv [T, (nq + 2 nkv) d].  For a handful of rows (decode) with the whole head
+    rotated this is ONE kernel (csrc/gemm_skinny.cu); otherwise the product and the fused
+    bias/rotation/cache-write kernel."""
+    _need_cuda(h, w, bias, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    if (skinny_ok(h, w) and inv_freq is not None and rot == d and d % 16 == 0 and k_cache.dtype == torch.bfloat16
+            and w.shape[0] == (nq + 2 * nkv) * d and (bias is None or bias.dtype == torch.float32)):
+        T = h.shape[0]
+        out = torch.empty((T, w.shape[0]), dtype=torch.bfloat16, device=h.device)
+        _run(_bf16(), "fe_skinny_qkv", _ptr(h), _ptr(w), _ptr(out), _ptr(bias), _ptr(positions), _ptr(inv_freq),
+             _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(h.shape[1]), _c_int(nq), _c_int(nkv),
+             _c_int(d), _c_int(page_size), _c_ll(k_cache.shape[0] * page_size), _ptr(status_word(h.device)), _stream())
+        return out
+    qkv = linear(h, w)
+    qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size)
+    return qkv
+
+
 def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, token_request, T, nq, nkv, d,
                          page_size, scale, window):
     out = torch.empty((T, nq * d), dtype=k_cache.dtype, device=k_cache.device)

@@ -58,18 +58,16 @@ class AttentionMixer(Mixer):
         ops = ctx.ops
         group = ctx.groups[entry.cache_group]
         k_cache, v_cache = group.kv_slot(entry.cache_slot)
-        qkv = ops.linear(h, self.qkv_weight)
         rotary = self.position.rotary_table(h.device)
         if rotary is None:
             inv_freq, rot = None, 0
         else:
             inv_freq, rot = rotary
-        # bias, rotation and the cache write are one kernel; a run entry that only reads
-        # another entry's cache passes no slot mapping, so nothing is written.
-        ops.qkv_bias_rope_cache(qkv, self.qkv_bias_, ctx.positions, inv_freq, rot,
-                                group.slot_mapping if entry.write_cache else None,
-                                k_cache, v_cache, self.num_heads, self.num_kv_heads, self.head_dim,
-                                group.page_size)
+        # projection, bias, rotation and the cache write are one operation (one kernel in decode); a
+        # run entry that only reads another entry's cache passes no slot mapping, so nothing is written
+        qkv = ops.qkv_projection(h, self.qkv_weight, self.qkv_bias_, ctx.positions, inv_freq, rot,
+                                 group.slot_mapping if entry.write_cache else None, k_cache, v_cache,
+                                 self.num_heads, self.num_kv_heads, self.head_dim, group.page_size)
         if rotary is None:
             self.position.apply(ctx, qkv, None)
         out = ops.paged_attention(qkv, k_cache, v_cache, group.block_table, ctx, self.num_heads,

@@ -70,6 +70,12 @@ def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cac
         v_cache[page, :, off] = out[keep, nq + nkv:]
 
 
+def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size):
+    qkv = linear(h, w)
+    qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size)
+    return qkv
+
+
 def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window):
     T = qkv.shape[0]
     out = torch.zeros(T, nq * d, dtype=qkv.dtype, device=qkv.device)

@@ -196,6 +196,31 @@ def test_qkv_bias_rope_cache(dtype, nq, nkv, d, rot, ps, gen):
     ops().check_status(DEV)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("nq,nkv,d,ps,K", [(4, 2, 16, 16, 64), (6, 1, 32, 32, 192), (6, 3, 48, 16, 128), (28, 4, 128, 16, 3584)])
+def test_fused_qkv_projection(M, nq, nkv, d, ps, K, gen):
+    """Decode-sized projection with bias, rotation and cache write in the GEMM's epilogue, against
+    the unfused reference."""
+    pages = 12
+    h = rand((M, K), torch.bfloat16, gen)
+    w = rand(((nq + 2 * nkv) * d, K), torch.bfloat16, gen, 0.05)
+    bias = torch.randn((nq + 2 * nkv) * d, device=DEV, generator=gen) * 0.1
+    positions = torch.tensor([0, 1, 17, 255, 4095, 32767, 100000, 131071][:M], device=DEV, dtype=torch.int32)
+    inv_freq = (1.0 / 1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d)).to(DEV)
+    slots = torch.randperm(pages * ps, device=DEV, generator=gen)[:M].to(torch.int32)
+    if M > 2:
+        slots[2] = -1
+    caches = [torch.zeros(2, pages, nkv, ps, d, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    got = ops().qkv_projection(h, w, bias, positions, inv_freq, d, slots, caches[0][0], caches[0][1], nq, nkv, d, ps)
+    want = kernel_refs.qkv_projection(h, w, bias, positions, inv_freq, d, slots, caches[1][0], caches[1][1], nq, nkv, d, ps)
+    torch.testing.assert_close(got.float(), want.float(), atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(caches[0].float(), caches[1].float(), atol=3e-2, rtol=3e-2)
+    untouched = torch.zeros_like(caches[0])
+    ops().qkv_projection(h, w, None, positions, inv_freq, d, None, untouched[0], untouched[1], nq, nkv, d, ps)
+    assert float(untouched.abs().max()) == 0.0
+    ops().check_status(DEV)
+
+
 def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None, splits=None,
                     simt=False):
     """chunks: [(start, n)] per request.  Fills the cache for positions < start + n."""
