@@ -204,6 +204,28 @@ def test_executor_failure_faults_the_engine_and_frees_everything():
         e.submit([1], max_tokens=1)
 
 
+def test_worker_thread_serves_requests_and_stop_cancels_the_rest():
+    """``start()`` runs the step loop on a thread of its own (the reference's serving mode); clients
+    read their request's event queue; ``stop()`` cancels what is still alive and frees its pages."""
+    import time
+    e = counting_engine()
+    e.start()
+    a = e.submit([5, 6, 7], max_tokens=4)
+    events = []
+    deadline = time.time() + 10
+    while time.time() < deadline:
+        ev = a.events.get(timeout=5)
+        events.append(ev)
+        if ev.kind == "done":
+            break
+    assert [ev.token_id for ev in events if ev.kind == "token"] == [8, 9, 10, 11] and events[-1].finish_reason == "length"
+    b = e.submit([3] * 39, max_tokens=16)
+    e.stop()
+    assert b.state in (State.CANCELLED, State.FINISHED) and e.cache.used_pages == 0
+    snap = e.snapshot()
+    assert snap["requests_total"] == 2 and snap["fault"] is None and snap["cache_free_blocks"] == e.cache.total_pages
+
+
 def test_step_trace_is_written(tmp_path):
     import json
     e = counting_engine(trace_dir=str(tmp_path))
