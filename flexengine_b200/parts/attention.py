@@ -21,6 +21,8 @@ class AttentionMixer(Mixer):
                  window: int = 0, scale: float | None = None):
         if num_heads % num_kv_heads:
             raise ValueError("Invalid GQA head ratio")
+        if head_dim % 16 or not (16 <= head_dim <= 256):
+            raise ValueError(f"head_dim={head_dim}: the attention kernels take head sizes in steps of 16 from 16 to 256")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = \
             int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)

@@ -74,3 +74,22 @@ def test_step_on_cpu_with_reference_kernels(model_dirs, name, kind):
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_step_on_gpu(model_dirs, name, kind, dtype):
     _run(model_dirs[name], name, kind, dtype, "cuda:0", None)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_weights_stored_in_32_bit(tmp_path_factory, dtype):
+    """A checkpoint stored in float32: in bfloat16 mode its matrices stay 32-bit (their products run
+    through the float32 GEMM), activations and cache are bfloat16; both modes match the plain implementation."""
+    model_dir = helpers.make_model_dir(tmp_path_factory, "C", seed=77, stored="float32")
+    _run(model_dir, "C", "portions", dtype, "cuda:0", None)
+    _run(model_dir, "C", "mixed", dtype, "cuda:0", None)
+
+
+def test_head_sizes_outside_the_kernels_range_are_refused_when_the_model_is_built():
+    from flexengine_b200.config import resolve
+    from flexengine_b200.parts import DecoderModel
+    bad = dict(helpers.TINY_A, head_dim=24)
+    _cfg, plan = resolve(bad)
+    with pytest.raises(ValueError, match="steps of 16"):
+        DecoderModel(plan)
