@@ -112,14 +112,17 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[r][nt][0] = acc[r][nt][1] = acc[r][nt][2] = acc[r][nt][3] = 0.f;
 
-    // this warp's k steps are warp, warp + 8, ...; the loads of PF steps go out together, then their math
+    // every warp owns one contiguous eighth of K (whole steps), so that the PF steps it loads together
+    // are one contiguous run of each row in memory; the loads of PF steps go out together, then their math
     const int steps = K / KSTEP;
-    for (int s = warp; s < steps; s += WARPS * PF) {
+    const int per_warp = (steps + WARPS - 1) / WARPS;
+    const int s_begin = warp * per_warp, s_end = min(steps, s_begin + per_warp);
+    for (int s = s_begin; s < s_end; s += PF) {
         uint4 a0[PF][RT][2], a1[PF][RT][2], b[PF][NT][2];
 #pragma unroll
         for (int p = 0; p < PF; ++p) {
-            const int sp = s + p * WARPS;
-            if (sp < steps) {
+            const int sp = s + p;
+            if (sp < s_end) {
                 const size_t k = (size_t)sp * KSTEP;
 #pragma unroll
                 for (int r = 0; r < RT; ++r) {
@@ -130,11 +133,11 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
         }
         // the weights above depend on no kernel; the activations below are the previous kernel's
         // output, so the first batch of weight loads is already in flight while that kernel ends
-        if (s == warp) { griddep_wait(); griddep_launch_dependents(); }
+        if (s == s_begin) { griddep_wait(); griddep_launch_dependents(); }
 #pragma unroll
         for (int p = 0; p < PF; ++p) {
-            const int sp = s + p * WARPS;
-            if (sp < steps) {
+            const int sp = s + p;
+            if (sp < s_end) {
                 const size_t k = (size_t)sp * KSTEP;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
@@ -145,7 +148,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
         }
 #pragma unroll
         for (int p = 0; p < PF; ++p) {
-            if (s + p * WARPS < steps) {
+            if (s + p < s_end) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -162,7 +165,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             }
         }
     }
-    if (warp >= steps) { griddep_wait(); griddep_launch_dependents(); }   // a warp without work has not waited yet
+    if (s_begin >= s_end) { griddep_wait(); griddep_launch_dependents(); }   // a warp without work has not waited yet
     // accumulator (tile r, row g + 8 (e >> 1), batch column nt * 8 + 2t + (e & 1)) -> red[warp][(r, column, row)]
 #pragma unroll
     for (int r = 0; r < RT; ++r)
