@@ -343,6 +343,17 @@ def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start,
     return out
 
 
+def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
+                          page_size, scale, window):
+    """Prefill attention on tcgen05 tensor cores: 128 (query, head) rows a block, head sizes 64 and 128."""
+    out = torch.empty((T, nq * d), dtype=torch.bfloat16, device=k_cache.device)
+    _run(_bf16(), "fe_paged_prefill_tcgen05", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
+         _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
+         _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
+         _c_float(scale), _c_int(window), _ptr(status_word(k_cache.device)), _stream())
+    return out
+
+
 def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window):
     """Causal grouped-query attention of the step's tokens over their requests' pages.
     qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d].

@@ -222,7 +222,7 @@ def test_fused_qkv_projection(M, nq, nkv, d, ps, K, gen):
 
 
 def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None, splits=None,
-                    simt=False):
+                    simt=False, tcgen05=False):
     """chunks: [(start, n)] per request.  Fills the cache for positions < start + n."""
     R = len(chunks)
     lens = [s + n for s, n in chunks]
@@ -270,6 +270,9 @@ def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered
     if splits is not None:            # the split-KV decode kernel, asked for by name
         got = ops().paged_decode_mma(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, R, nq, nkv, d, ps, scale,
                                      window, splits)
+    elif tcgen05:                     # the tcgen05 prefill kernel, asked for by name
+        got = ops().paged_prefill_tcgen05(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, T, R, ctx.max_q_len, nq,
+                                          nkv, d, ps, scale, window)
     elif simt:
         got = ops().paged_attention_simt(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, ctx.token_request, T,
                                          nq, nkv, d, ps, scale, window)
