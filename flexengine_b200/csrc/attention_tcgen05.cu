@@ -5,23 +5,28 @@
 // window > 0), running maximum / sum / output in float (online softmax), query head h reads
 // key/value head h / (nq / nkv).
 //
-// A block takes 128 rows of one (request, key/value head): row m is the pair (query m / G, head
-// m % G of the group), so the group shares every key it loads.  Keys are walked in tiles of 128
-// aligned to position 0.  Per tile:
-//   S = Q K^T    tcgen05.mma 128 x 128 x d, Q and K in shared memory (K-major, 128-byte swizzle),
-//                S in tensor memory
-//   softmax      warps 0..3, one thread per row: read S with tcgen05.ld, mask, running maximum and
-//                sum in float, P = exp2(...) as bfloat16 into shared memory (the A operand of the
-//                next product), rescale the row's output registers
-//   PV           tcgen05.mma 128 x d x 128, P (K-major) times V (rows of V as they lie in the
-//                cache: MN-major operand), into a second tensor-memory buffer, added to the
-//                output registers by the softmax threads
-// Warps 4..7 gather the next tile's keys and values from the pages with 16-byte asynchronous
-// copies into a two-stage ring while the others compute.  Products are issued by thread 0.
+// A block takes 256 rows of one (request, key/value head) as two tiles of 128: row m is the pair
+// (query m / G, head m % G of the group), so the group shares every key it loads.  Keys are walked
+// in tiles of 64 aligned to position 0.  Per key tile j and row tile i:
+//   S_i(j) = Q_i K^T  tcgen05.mma 128 x 64 x d, Q and K in shared memory (K-major, 128-byte
+//                     swizzle), into one of two score buffers of the row tile in tensor memory
+//   softmax           warps 4i..4i+3, one thread per row: the 64 scores into registers with
+//                     tcgen05.ld, mask, running maximum and sum in float, P = exp2(...) as
+//                     bfloat16 written over the scores in tensor memory with tcgen05.st
+//   O_i += P V        tcgen05.mma 128 x d x 64, P from tensor memory, V from shared memory as it
+//                     lies in the cache (one row per key: MN-major operand), accumulated in tensor
+//                     memory over all key tiles
+// The scores run two key tiles ahead of the softmax (S_i(j+2) is issued right after P_i(j) V,
+// into the buffer that P_i(j) leaves), so the softmax threads rarely wait and the tensor cores
+// fill in between.  The reference point of the exponentials moves only when a row's maximum has
+// grown by more than 2^8; the sum and O_i are then rescaled in place (after the last P V of the
+// row tile has completed), which is rare after the first tiles, so O_i stays in tensor memory
+// until the end.
+// Warps 8..11 gather keys and values from the pages with 16-byte asynchronous copies into a
+// four-stage ring; lane 0 of warp 12 + i issues the products of row tile i.
 //
-// Every wait on an mbarrier is bounded; when one runs out the block records it in the status
-// word and all its threads leave their loops together at the next group barrier; tensor memory is
-// freed before the block returns.
+// Every wait on an mbarrier is bounded, and ends early once any thread of the block has given up;
+// the block then records it in the status word, leaves its loops and frees its tensor memory.
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -30,13 +35,15 @@ using namespace fe;
 
 namespace {
 
-constexpr int ROWS = 128;        // rows of a block = UMMA M
-constexpr int KEYS = 128;        // keys per tile
-constexpr int BLOCK_BYTES = 128 * 128;   // one [128 rows x 64 elements] swizzled block
-constexpr int KV_STAGES = 2;
-constexpr int THREADS = 256;
-constexpr int TMEM_COLS = 256;   // S at column 0, PV at column 128
-constexpr long long WAIT_LIMIT = 4000000000LL;
+constexpr int ROWS = 128;        // rows of a row tile = UMMA M; a block takes two
+constexpr int KEYS = 64;         // keys per tile
+constexpr int Q_BLOCK = ROWS * 128;      // bytes of one [128 rows x 64 elements] swizzled block of Q
+constexpr int KV_BLOCK = KEYS * 128;     // bytes of one [64 keys x 64 elements] swizzled block of K or V
+constexpr int KV_STAGES = 4;
+constexpr int THREADS = 448;     // warps 0..7 softmax (two row tiles), 8..11 loaders, 12 + i issues the products of row tile i
+constexpr int TMEM_COLS = 512;   // score buffer b of row tile i at column 64 (2 i + b), O_i at column 256 + 128 i
+constexpr long long WAIT_LIMIT = 2000000000LL;
+constexpr float RESCALE_STEP = 8.f;      // log2 of the growth of a row's maximum that moves its reference point
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
@@ -51,11 +58,16 @@ __device__ __forceinline__ bool mbar_test(unsigned long long* bar, unsigned pari
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+// false when the wait ran out or another thread of the block has given up; sets the flag itself then
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* give_up) {
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_test(bar, parity)) {
-        if (clock64() - t0 > WAIT_LIMIT) return false;
+        if (*give_up) return false;
+        if (clock64() - t0 > WAIT_LIMIT) {
+            *give_up = 1;
+            return false;
+        }
     }
     return true;
 }
@@ -66,7 +78,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.com
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void group_barrier(int id) { asm volatile("bar.sync %0, 128;\n" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void loader_barrier() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
 // Shared-memory descriptors, 128-byte swizzle.  K-major: rows 128 bytes apart, 8-row groups 1024
 // bytes apart.  MN-major (V as it lies in the cache: one row per key, 64 head elements = 128 bytes
@@ -85,10 +97,17 @@ __device__ __forceinline__ unsigned long long desc_mn_major(const void* p, unsig
 __host__ __device__ constexpr unsigned instr_desc(int m, int n, bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
-__device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
-                                     unsigned accumulate) {
+// D[tmem] (+)= A[smem] B[smem]
+__device__ __forceinline__ void umma_ss(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                        unsigned accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] B[smem]: A lies row per lane, two bfloat16 per 32-bit column
+__device__ __forceinline__ void umma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long bdesc, unsigned idesc,
+                                        unsigned accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
@@ -108,76 +127,169 @@ __device__ __forceinline__ void tmem_load32(unsigned taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// Four loads of 32 columns in flight at once: issue all, then one wait; the empty statements tie the
+// registers to the wait so that nothing reads them before it.
+__device__ __forceinline__ void tmem_issue_load32(unsigned taddr, unsigned* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tie32(unsigned* r) {
+    asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                      "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                      "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                      "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31]) :: "memory");
+}
+__device__ __forceinline__ void tmem_store32(unsigned taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n"
+        ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]),
+          "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]), "f"(v[16]), "f"(v[17]),
+          "f"(v[18]), "f"(v[19]), "f"(v[20]), "f"(v[21]), "f"(v[22]), "f"(v[23]), "f"(v[24]), "f"(v[25]), "f"(v[26]),
+          "f"(v[27]), "f"(v[28]), "f"(v[29]), "f"(v[30]), "f"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store16(unsigned taddr, const unsigned* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
-// Byte offset of 16-byte chunk ``c`` (0 .. D/8 - 1) of row ``r`` in a tile made of [128 x 64] swizzled blocks.
-__device__ __forceinline__ int swizzled(int r, int c) {
-    return (c >> 3) * BLOCK_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+// Byte offset of 16-byte chunk ``c`` (0 .. D/8 - 1) of row ``r`` in a tile made of [rows x 64] swizzled blocks.
+__device__ __forceinline__ int swizzled(int r, int c, int block_bytes) {
+    return (c >> 3) * block_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+}
+
+// The softmax of one row over a key tile, the 64 scores in registers.  MASKED: the tile crosses
+// the causal edge or the window's edge for some row of the warp; ``hi`` and ``lo`` are then this
+// row's last and first visible key relative to the tile.
+template <bool MASKED>
+__device__ __forceinline__ float row_max(const unsigned* r, int hi, int lo) {
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, m2 = -CUDART_INF_F, m3 = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < KEYS; i += 4) {
+        float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]), v2 = __uint_as_float(r[i + 2]), v3 = __uint_as_float(r[i + 3]);
+        if (MASKED) {
+            if (i > hi || i < lo) v0 = -CUDART_INF_F;
+            if (i + 1 > hi || i + 1 < lo) v1 = -CUDART_INF_F;
+            if (i + 2 > hi || i + 2 < lo) v2 = -CUDART_INF_F;
+            if (i + 3 > hi || i + 3 < lo) v3 = -CUDART_INF_F;
+        }
+        m0 = fmaxf(m0, v0), m1 = fmaxf(m1, v1), m2 = fmaxf(m2, v2), m3 = fmaxf(m3, v3);
+    }
+    return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+// P = 2^(s scale - ref) as bfloat16 pairs over the scores' own columns (32 of the 64); returns the row's sum.
+template <bool MASKED>
+__device__ __forceinline__ float row_exp(const unsigned* r, unsigned p_addr, int hi, int lo, float scale_log2, float ref) {
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int c = 0; c < KEYS; c += 32) {
+        unsigned packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int k = c + 2 * i;
+            float x = ex2(fmaf(__uint_as_float(r[k]), scale_log2, -ref));
+            float y = ex2(fmaf(__uint_as_float(r[k + 1]), scale_log2, -ref));
+            if (MASKED) {
+                if (k > hi || k < lo) x = 0.f;
+                if (k + 1 > hi || k + 1 < lo) y = 0.f;
+            }
+            s0 += x, s1 += y;
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(x, y);
+            packed[i] = *reinterpret_cast<const unsigned*>(&pair);
+        }
+        tmem_store16(p_addr + (c >> 1), packed);
+    }
+    return s0 + s1;
 }
 
 template <int D>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                              const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                              const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ q_start, int nq, int nkv, int ps, int num_pages, float scale_log2,
                              int window, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long kv_full[KV_STAGES], kv_empty[KV_STAGES], mma_bar;
+    __shared__ __align__(8) unsigned long long kv_full[KV_STAGES], kv_empty[KV_STAGES], s_ready[2][2], p_ready[2][2], pv_done[2], o_final[2];
     __shared__ long long offs[KEYS];
     __shared__ unsigned tmem_holder;
     __shared__ volatile int give_up;
     constexpr int DB = D / 64;                       // 64-element blocks per row
-    constexpr int TILE_BYTES = DB * BLOCK_BYTES;     // one Q, K or V tile
+    constexpr int Q_BYTES = DB * Q_BLOCK;            // one row tile of Q
+    constexpr int KV_BYTES = DB * KV_BLOCK;          // one key tile of K or of V
+    constexpr unsigned FULL = 0xffffffffu;
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_s = smem;
-    unsigned char* p_s = q_s + TILE_BYTES;           // [128 rows x 128 keys] = two blocks
-    unsigned char* kv_s = p_s + 2 * BLOCK_BYTES;     // stage s: K at kv_s + s * 2 * TILE_BYTES, V after it
+    unsigned char* q_s = smem;                       // row tile i at q_s + i * Q_BYTES
+    unsigned char* kv_s = q_s + 2 * Q_BYTES;         // stage s: K at kv_s + s * 2 * KV_BYTES, V after it
 
     griddep_wait();
     griddep_launch_dependents();
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y, r = blockIdx.z;
     const int G = nq / nkv;
     const int tok0 = cu_q[r], n_q = cu_q[r + 1] - tok0;
     const int rows = n_q * G;
-    const int m_block = (gridDim.x - 1 - blockIdx.x) * ROWS;        // the rows with the most keys first
-    if (m_block >= rows) return;
+    const int m_pair = (gridDim.x - 1 - blockIdx.x) * 2 * ROWS;     // the rows with the most keys first
+    if (m_pair >= rows) return;
+    const bool two = m_pair + ROWS < rows;                          // else the second row tile is empty and left out
     const int start = q_start[r];
     // keys this block needs: from the window edge of its first query to its last query
-    const int qi_first = m_block / G, qi_last = min(n_q - 1, (m_block + ROWS - 1) / G);
+    const int qi_first = m_pair / G, qi_last = min(n_q - 1, (m_pair + (two ? 2 : 1) * ROWS - 1) / G);
     const int hi = start + qi_last;
     const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
     const int t_begin = lo / KEYS, n_tiles = hi / KEYS - t_begin + 1;
 
     if (tid == 0) {
-        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 128); mbar_init(&kv_empty[s], 1); }
-        mbar_init(&mma_bar, 1);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 128); mbar_init(&kv_empty[s], two ? 2 : 1); }
+        for (int i = 0; i < 2; ++i) {
+            for (int b = 0; b < 2; ++b) { mbar_init(&s_ready[i][b], 1); mbar_init(&p_ready[i][b], 128); }
+            mbar_init(&pv_done[i], 1);
+            mbar_init(&o_final[i], 1);
+        }
         give_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 0) {
+    if (warp == 12) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_holder)), "n"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
 
-    // this thread's row (compute threads only)
-    const int m = m_block + (tid & 127);
-    const bool valid = tid < 128 && m < rows;
+    // softmax threads: row tile ``ti``, row ``tid & 127`` of it
+    const int ti = warp >> 2;
+    const bool softmax_thread = warp < 8 && (ti == 0 || two);
+    const int m = m_pair + ti * ROWS + (tid & 127);
+    const bool valid = softmax_thread && m < rows;
     const int qi = valid ? m / G : 0, head = kvh * G + (valid ? m % G : 0);
     const int pos = valid ? start + qi : -1;
     const int row_lo = window > 0 ? max(0, pos - window + 1) : 0;
-    if (tid < 128) {
+    if (softmax_thread) {
         // the query row into shared memory, swizzled like a TMA tile (zeros for padding rows)
         const bf16* src = q + (size_t)(tok0 + qi) * q_stride + (size_t)head * D;
+        unsigned char* dst = q_s + ti * Q_BYTES;
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) {
             uint4 v = make_uint4(0, 0, 0, 0);
             if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-            *reinterpret_cast<uint4*>(q_s + swizzled(tid, c)) = v;
+            *reinterpret_cast<uint4*>(dst + swizzled(tid & 127, c, Q_BLOCK)) = v;
         }
         fence_proxy_async();
     }
@@ -186,157 +298,163 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     tc_fence_after();
     const unsigned tmem_base = tmem_holder;
 
-    if (tid >= 128) {
-        // ---- loaders: thread lt looks up key lt of the tile, then all copy ----
-        const int lt = tid - 128;
+    if (warp >= 8 && warp < 12) {
+        // ---- loaders: the first 64 look up one key of the tile each, then all copy ----
+        const int lt = tid - 256;
         const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
         for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
-            if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1)) give_up = 1;      // free from the start
-            const int key = (t_begin + j) * KEYS + lt;
-            long long off = -1;
-            if (key >= lo && key <= hi) {
-                const int page = block_table[(size_t)r * bt_stride + (ps_shift >= 0 ? key >> ps_shift : key / ps)];
-                if (page < 0 || page >= num_pages) {
-                    if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
-                } else {
-                    const int within = ps_shift >= 0 ? key & (ps - 1) : key % ps;
-                    off = (((long long)page * nkv + kvh) * ps + within) * D;
+            const int s = j % KV_STAGES;
+            mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, &give_up);     // free from the start
+            if (lt < KEYS) {
+                const int key = (t_begin + j) * KEYS + lt;
+                long long off = -1;
+                if (key >= lo && key <= hi) {
+                    const int page = block_table[(size_t)r * bt_stride + (ps_shift >= 0 ? key >> ps_shift : key / ps)];
+                    if (page < 0 || page >= num_pages) {
+                        if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
+                    } else {
+                        const int within = ps_shift >= 0 ? key & (ps - 1) : key % ps;
+                        off = (((long long)page * nkv + kvh) * ps + within) * D;
+                    }
                 }
+                offs[lt] = off;
             }
-            offs[lt] = off;
-            group_barrier(2);
+            loader_barrier();
             if (give_up) break;                                    // the same for all loaders after the barrier
-            unsigned char* k_s = kv_s + s * 2 * TILE_BYTES;
-            unsigned char* v_s = k_s + TILE_BYTES;
+            unsigned char* k_s = kv_s + s * 2 * KV_BYTES;
+            unsigned char* v_s = k_s + KV_BYTES;
             constexpr int CPR = D / 8;
             for (int idx = lt; idx < KEYS * CPR; idx += 128) {
                 const int row = idx / CPR, c = idx % CPR;
                 const long long ro = offs[row];
                 const bool ok = ro >= 0;
                 const long long from = ok ? ro + c * 8 : 0;
-                const int o = swizzled(row, c);
-                cp_async16(k_s + o, kc + from, ok ? 16 : 0);
+                const int o = swizzled(row, c, KV_BLOCK);
+                cp_async16(k_s + o, kc + from, ok ? 16 : 0);       // keys out of range read as zeros
                 cp_async16(v_s + o, vc + from, ok ? 16 : 0);
             }
             cp_async_wait_all();
             fence_proxy_async();
             mbar_arrive(&kv_full[s]);
-            group_barrier(2);                                      // offs may be rewritten
+            loader_barrier();                                      // offs may be rewritten
         }
-    } else {
-        // ---- compute: one thread per row; thread 0 also issues the products ----
-        float o_acc[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
-        float row_max = -CUDART_INF_F, row_sum = 0.f;
-        unsigned mma_phase = 0;
-        const unsigned lane_addr = tmem_base + ((unsigned)(warp * 32) << 16);
-        constexpr unsigned idesc_s = instr_desc(ROWS, KEYS, false), idesc_pv = instr_desc(ROWS, D, true);
-        for (int j = 0; j < n_tiles; ++j) {
-            const int s = j & 1;
-            const unsigned char* k_s = kv_s + s * 2 * TILE_BYTES;
-            const unsigned char* v_s = k_s + TILE_BYTES;
-            if (tid == 0) {
-                if (!mbar_wait(&kv_full[s], (j >> 1) & 1)) give_up = 1;
-                tc_fence_after();
+    } else if (warp >= 12) {
+        // ---- lane 0 of warp 12 + i issues the products of row tile i; the tensor cores keep each thread's order ----
+        const int i = warp - 12;
+        if (lane == 0 && (i == 0 || two)) {
+            constexpr unsigned idesc_s = instr_desc(ROWS, KEYS, false), idesc_pv = instr_desc(ROWS, D, true);
+            constexpr unsigned STAGE16 = (2 * KV_BYTES) >> 4;      // a stage's size in descriptor units
+            const unsigned long long q_desc = desc_k_major(q_s + i * Q_BYTES), k_desc0 = desc_k_major(kv_s),
+                                     v_desc0 = desc_mn_major(kv_s + KV_BYTES, KV_BLOCK);
+            const unsigned s_col = tmem_base + 2 * i * 64, o_col = tmem_base + 256 + i * 128;
+            auto issue_s = [&](int j) {                            // S_i of key tile j into score buffer j & 1
+                const unsigned long long k_desc = k_desc0 + (unsigned)(j % KV_STAGES) * STAGE16;
+                const unsigned dst = s_col + (j & 1) * 64;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks)
-                    umma(tmem_base, desc_k_major(q_s + (ks >> 2) * BLOCK_BYTES) + 2 * (ks & 3),
-                         desc_k_major(k_s + (ks >> 2) * BLOCK_BYTES) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
-                umma_commit(&mma_bar);
-            }
-            if (!mbar_wait(&mma_bar, mma_phase)) give_up = 1;
-            mma_phase ^= 1;
-            tc_fence_after();
-            // scores of this row: maximum first, then the exponentials (two passes over tensor memory)
-            const int key0 = (t_begin + j) * KEYS;
-            float mx = -CUDART_INF_F;
-#pragma unroll 1
-            for (int c = 0; c < KEYS; c += 32) {
-                float v[32];
-                tmem_load32(lane_addr + c, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c + i;
-                    if (key <= pos && key >= row_lo) mx = fmaxf(mx, v[i]);
-                }
-            }
-            const float m_new = fmaxf(row_max, mx * scale_log2);
-            const float m_safe = m_new == -CUDART_INF_F ? 0.f : m_new;
-            const float alpha = ex2(row_max - m_safe);             // 2^-inf = 0 at the start
-            row_max = m_new;
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < KEYS; c += 32) {
-                float v[32];
-                tmem_load32(lane_addr + c, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c + i;
-                    const bool vis = key <= pos && key >= row_lo;
-                    v[i] = vis ? ex2(fmaf(v[i], scale_log2, -m_safe)) : 0.f;
-                    sum += v[i];
-                }
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint4 pk;
-                    unsigned* w = reinterpret_cast<unsigned*>(&pk);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const __nv_bfloat162 pair = __floats2bfloat162_rn(v[i + 2 * e], v[i + 2 * e + 1]);
-                        w[e] = *reinterpret_cast<const unsigned*>(&pair);
-                    }
-                    *reinterpret_cast<uint4*>(p_s + swizzled(tid, (c + i) >> 3)) = pk;
-                }
-            }
-            row_sum = row_sum * alpha + sum;
-            if (alpha != 1.f) {
-#pragma unroll
-                for (int i = 0; i < D; ++i) o_acc[i] *= alpha;
-            }
-            fence_proxy_async();
-            tc_fence_before();
-            group_barrier(1);                                      // P is complete; S has been read by all
-            if (give_up) break;                                    // the same for all compute threads after the barrier
-            if (tid == 0) {
+                    umma_ss(dst, q_desc + (((ks >> 2) * Q_BLOCK + (ks & 3) * 32) >> 4),
+                            k_desc + (((ks >> 2) * KV_BLOCK + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
+                umma_commit(&s_ready[i][j & 1]);
+            };
+            bool ok = true;
+            for (int j = 0; j < 2 && j < n_tiles && ok; ++j) {
+                ok = mbar_wait(&kv_full[j], 0, &give_up);
                 tc_fence_after();
+                if (ok) issue_s(j);
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % KV_STAGES;
+                ok = mbar_wait(&p_ready[i][j & 1], (j >> 1) & 1, &give_up);
+                if (!ok) break;
+                tc_fence_after();
+                const unsigned long long v_desc = v_desc0 + (unsigned)s * STAGE16;
+                const unsigned p_col = s_col + (j & 1) * 64;
 #pragma unroll
                 for (int ks = 0; ks < KEYS / 16; ++ks)
-                    umma(tmem_base + 128, desc_k_major(p_s + (ks >> 2) * BLOCK_BYTES) + 2 * (ks & 3),
-                         desc_mn_major(v_s, BLOCK_BYTES) + ks * (2048 >> 4), idesc_pv, ks > 0 ? 1u : 0u);
-                umma_commit(&kv_empty[s]);                         // the stage may be refilled once these have read it
-                umma_commit(&mma_bar);
+                    umma_ts(o_col, p_col + ks * 8, v_desc + ks * (2048 >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(&pv_done[i]);
+                umma_commit(&kv_empty[s]);                         // the stage may be refilled once both row tiles have read it
+                if (j + 2 < n_tiles) {
+                    ok = mbar_wait(&kv_full[(j + 2) % KV_STAGES], ((j + 2) / KV_STAGES) & 1, &give_up);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_s(j + 2);                                // runs after P_i V above: it overwrites P_i
+                }
             }
-            if (!mbar_wait(&mma_bar, mma_phase)) give_up = 1;
-            mma_phase ^= 1;
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < D; c += 32) {
-                float v[32];
-                tmem_load32(lane_addr + 128 + c, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o_acc[c + i] += v[i];
-            }
-            tc_fence_before();
+            if (ok) umma_commit(&o_final[i]);
         }
-        if (valid && !give_up) {
+        __syncwarp();
+    } else if (softmax_thread) {
+        // ---- softmax: one thread per row ----
+        const unsigned lane_bits = (unsigned)((warp & 3) * 32) << 16;
+        const unsigned o_addr = tmem_base + lane_bits + 256 + ti * 128;
+        const int pos_min = __reduce_min_sync(FULL, pos), lo_max = __reduce_max_sync(FULL, row_lo);
+        float m_ref = -CUDART_INF_F, row_sum = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = __all_sync(FULL, mbar_wait(&s_ready[ti][j & 1], (j >> 1) & 1, &give_up));
+            if (!ok) break;
+            tc_fence_after();
+            const unsigned s_addr = tmem_base + lane_bits + (2 * ti + (j & 1)) * 64;
+            unsigned raw[KEYS];
+            tmem_issue_load32(s_addr, raw);
+            tmem_issue_load32(s_addr + 32, raw + 32);
+            tmem_load_wait();
+            tie32(raw);
+            tie32(raw + 32);
+            const int key0 = (t_begin + j) * KEYS;
+            const bool unmasked = key0 + KEYS - 1 <= pos_min && key0 >= lo_max;      // for the whole warp
+            const int rel_hi = pos - key0, rel_lo = row_lo - key0;
+            const float mx = unmasked ? row_max<false>(raw, rel_hi, rel_lo) : row_max<true>(raw, rel_hi, rel_lo);
+            const float m_new = fmaxf(m_ref, mx * scale_log2);
+            if (__any_sync(FULL, m_new > m_ref + RESCALE_STEP)) {
+                // move the reference point to the new maximum: O and the sum were taken against the old one
+                const float alpha = m_new == -CUDART_INF_F ? 1.f : ex2(m_ref - m_new);
+                if (j > 0) {
+                    ok = __all_sync(FULL, mbar_wait(&pv_done[ti], (j - 1) & 1, &give_up));      // O_i is at rest
+                    if (!ok) break;
+                    tc_fence_after();
+                    row_sum *= alpha;
+#pragma unroll 1
+                    for (int c = 0; c < D; c += 32) {
+                        float v[32];
+                        tmem_load32(o_addr + c, v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                        tmem_store32(o_addr + c, v);
+                    }
+                }
+                m_ref = m_new;
+            }
+            const float m_safe = m_ref == -CUDART_INF_F ? 0.f : m_ref;
+            row_sum += unmasked ? row_exp<false>(raw, s_addr, rel_hi, rel_lo, scale_log2, m_safe)
+                                : row_exp<true>(raw, s_addr, rel_hi, rel_lo, scale_log2, m_safe);
+            tmem_store_wait();
+            tc_fence_before();
+            mbar_arrive(&p_ready[ti][j & 1]);
+        }
+        if (ok) ok = __all_sync(FULL, mbar_wait(&o_final[ti], 0, &give_up));
+        if (ok) {
+            tc_fence_after();
             const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
             bf16* dst = out + (size_t)(tok0 + qi) * out_stride + (size_t)head * D;
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                float v[32];
+                tmem_load32(o_addr + c, v);
+                if (valid) {
 #pragma unroll
-            for (int c = 0; c < D; c += 8) {
-                float v[8];
+                    for (int i = 0; i < 32; ++i) v[i] *= inv;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = o_acc[c + i] * inv;
-                store8<bf16>(dst + c, v);
+                    for (int i = 0; i < 32; i += 8) store8<bf16>(dst + c + i, v + i);
+                }
             }
         }
     }
-    __syncthreads();
-    if (give_up && tid == 0 && status) atomicOr(status, FE_STATUS_WAIT_EXPIRED);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
+    if (give_up && tid == 0 && status) atomicOr(status, FE_STATUS_WAIT_EXPIRED);
+    if (warp == 12) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "n"(TMEM_COLS) : "memory");
 }
 
 constexpr float LOG2E = 1.4426950408889634f;
@@ -345,11 +463,11 @@ template <int D>
 int launch(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
            const int* block_table, int bt_stride, const int* cu_q, const int* q_start, int requests, int max_q_len, int nq,
            int nkv, int ps, int num_pages, float scale, int window, int* status, cudaStream_t stream) {
-    const size_t smem = (size_t)(D / 64) * BLOCK_BYTES * (1 + 2 * KV_STAGES) + 2 * BLOCK_BYTES + 1024;
+    const size_t smem = (size_t)(D / 64) * (2 * Q_BLOCK + 2 * KV_STAGES * KV_BLOCK) + 1024;
     const cudaError_t err = cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FE_REQUIRE(err == cudaSuccess, "paged_prefill_tcgen05: %s", cudaGetErrorString(err));
     const long long rows = (long long)max_q_len * (nq / nkv);
-    const long long tiles = (rows + ROWS - 1) / ROWS;
+    const long long tiles = (rows + 2 * ROWS - 1) / (2 * ROWS);
     FE_REQUIRE(tiles <= 2147483647LL && nkv <= 65535 && requests <= 65535, "paged_prefill_tcgen05: grid too large");
     fe::launch(paged_prefill_tcgen05_kernel<D>, dim3((unsigned)tiles, nkv, requests), THREADS, smem, stream, (const bf16*)q, q_stride,
                (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, nq, nkv, ps,

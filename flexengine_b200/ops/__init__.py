@@ -343,6 +343,12 @@ def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start,
     return out
 
 
+def tcgen05_attention_ok(max_q_len, nq, nkv, d):
+    """The tcgen05 prefill kernel takes head sizes 64 and 128 and pays off once the longest portion fills
+    a block's 256 (query, head) rows; shorter portions go to the mma.sync kernel with its 64-row blocks."""
+    return d in (64, 128) and max_q_len * (nq // nkv) >= 256
+
+
 def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
                           page_size, scale, window):
     """Prefill attention on tcgen05 tensor cores: 128 (query, head) rows a block, head sizes 64 and 128."""
@@ -358,7 +364,8 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     """Causal grouped-query attention of the step's tokens over their requests' pages.
     qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d].
     float32 runs on CUDA cores (true 32-bit); bfloat16 on tensor cores: the split-KV decode
-    kernel when every request brings one token, else the prefill kernel."""
+    kernel when every request brings one token, else a prefill kernel (tcgen05 for long portions of
+    head size 64 or 128, mma.sync otherwise)."""
     _need_cuda(qkv, k_cache, v_cache, block_table)
     T = qkv.shape[0]
     if qkv.dtype != k_cache.dtype:
@@ -371,8 +378,9 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
         return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
                                 nq, nkv, d, page_size, scale, window, splits)
-    return paged_prefill_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
-                             ctx.max_q_len, nq, nkv, d, page_size, scale, window)
+    prefill = paged_prefill_tcgen05 if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d) else paged_prefill_mma
+    return prefill(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
+                   ctx.max_q_len, nq, nkv, d, page_size, scale, window)
 
 
 def sample(logits, temperature, top_k, seed, draw):

@@ -222,7 +222,7 @@ def test_fused_qkv_projection(M, nq, nkv, d, ps, K, gen):
 
 
 def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None, splits=None,
-                    simt=False, tcgen05=False):
+                    simt=False, tcgen05=False, ramp=None):
     """chunks: [(start, n)] per request.  Fills the cache for positions < start + n."""
     R = len(chunks)
     lens = [s + n for s, n in chunks]
@@ -256,6 +256,13 @@ def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered
             kc[page, g, off] = (qvec.float() * 4.0).to(dtype)
         vc[page, :, off] = 10.0
         assert t_far < r0_len
+    if ramp is not None:
+        # every key along dimension 0 grows with its position and every query has a positive component there:
+        # each later key beats the earlier ones by a wide margin
+        qkv[:, :nq * d].view(T, nq, d)[:, :, 0] = 4.0
+        for r, n in enumerate(pages_per):
+            for t in range(lens[r]):
+                kc[int(bt[r, t // ps]), :, t % ps, 0] = ramp * t
     cu = [0]
     for _, n in chunks:
         cu.append(cu[-1] + n)
@@ -336,6 +343,43 @@ def test_split_kv_decode_kernel_window_and_far_key(window, gen):
         got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(799, 1), (3, 1)], 0, gen, boost=far, splits=5)
         torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
         assert float((got[0].float() - 10.0).abs().max()) < 0.5
+
+
+@pytest.mark.parametrize("nq,nkv,d,ps", [(2, 2, 64, 16), (28, 4, 128, 16), (6, 3, 128, 24), (5, 1, 64, 8), (16, 1, 128, 32)])
+def test_tcgen05_prefill_kernel(nq, nkv, d, ps, gen):
+    # portions around the 64-key tile, the 128- and 256-row block edges; short ones beside long ones
+    chunks = [(0, 1), (0, 64), (63, 2), (0, 300), (100, 129), (1000, 3), (5, 37), (64, 64)]
+    got, want, _ = _attention_case(torch.bfloat16, nq, nkv, d, ps, chunks, 0, gen, tcgen05=True)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
+
+
+@pytest.mark.parametrize("window", [1, 63, 64, 65, 200])
+def test_tcgen05_prefill_kernel_window_and_far_key(window, gen):
+    chunks = [(0, 300), (200, 77), (999, 1), (60, 10)]
+    got, want, _ = _attention_case(torch.bfloat16, 8, 2, 128, 16, chunks, window, gen, tcgen05=True)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    for far in (0, 63, 64, 333, 700):
+        got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(600, 200), (3, 2)], 0, gen, boost=far, tcgen05=True)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+        assert float((got[199].float() - 10.0).abs().max()) < 0.5
+    ops().check_status(DEV)
+
+
+def test_tcgen05_prefill_kernel_moves_its_reference_point(gen):
+    # scores that grow along the keys by far more than 2^8 make every row rescale its output in tensor memory
+    nq, nkv, d, ps, n = 4, 2, 64, 16, 400
+    got, want, _ = _attention_case(torch.bfloat16, nq, nkv, d, ps, [(0, n), (37, 200)], 0, gen, tcgen05=True, ramp=0.6)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    with pytest.raises(RuntimeError, match="head size"):
+        _attention_case(torch.bfloat16, 4, 2, 32, 16, [(0, 300)], 0, gen, tcgen05=True)
+
+
+def test_dispatch_takes_the_tcgen05_kernel_for_long_portions(gen):
+    assert ops().tcgen05_attention_ok(300, 4, 2, 128) and not ops().tcgen05_attention_ok(100, 4, 2, 128)
+    assert not ops().tcgen05_attention_ok(4096, 4, 2, 96)
+    got, want, _ = _attention_case(torch.bfloat16, 4, 2, 128, 16, [(0, 300), (100, 1), (7, 2)], 0, gen)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
 
 
 def test_bfloat16_on_cuda_cores_for_shapes_the_tensor_core_kernels_refuse(gen):
