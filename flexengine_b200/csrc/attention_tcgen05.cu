@@ -281,16 +281,22 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     const int qi = valid ? m / G : 0, head = kvh * G + (valid ? m % G : 0);
     const int pos = valid ? start + qi : -1;
     const int row_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    // where this thread's row starts in q and in out (in elements); other lanes fetch it by shuffle
+    const long long q_off = valid ? (long long)(tok0 + qi) * q_stride + (long long)head * D : -1;
+    const long long out_off = valid ? (long long)(tok0 + qi) * out_stride + (long long)head * D : -1;
+    constexpr int CPR = D / 8;                       // 16-byte chunks per row
+    constexpr int RPI = 32 / CPR;                    // rows a warp moves per instruction: a row's chunks side by side
     if (softmax_thread) {
-        // the query row into shared memory, swizzled like a TMA tile (zeros for padding rows)
-        const bf16* src = q + (size_t)(tok0 + qi) * q_stride + (size_t)head * D;
+        // the warp's 32 query rows into shared memory, swizzled like a TMA tile (zeros for padding rows)
         unsigned char* dst = q_s + ti * Q_BYTES;
+        const int c = lane % CPR;
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (valid) v = *reinterpret_cast<const uint4*>(src + c * 8);
-            *reinterpret_cast<uint4*>(dst + swizzled(tid & 127, c, Q_BLOCK)) = v;
+        for (int k = 0; k < CPR; ++k) {
+            const int row_in_warp = k * RPI + lane / CPR;
+            const long long from = __shfl_sync(FULL, q_off, row_in_warp);
+            cp_async16(dst + swizzled((warp & 3) * 32 + row_in_warp, c, Q_BLOCK), q + (from >= 0 ? from + c * 8 : 0), from >= 0 ? 16 : 0);
         }
+        cp_async_wait_all();
         fence_proxy_async();
     }
     tc_fence_before();
@@ -323,7 +329,6 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             if (give_up) break;                                    // the same for all loaders after the barrier
             unsigned char* k_s = kv_s + s * 2 * KV_BYTES;
             unsigned char* v_s = k_s + KV_BYTES;
-            constexpr int CPR = D / 8;
             for (int idx = lt; idx < KEYS * CPR; idx += 128) {
                 const int row = idx / CPR, c = idx % CPR;
                 const long long ro = offs[row];
@@ -437,17 +442,27 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
         if (ok) {
             tc_fence_after();
             const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
-            bf16* dst = out + (size_t)(tok0 + qi) * out_stride + (size_t)head * D;
+            // O through shared memory (this row tile's Q is no longer read), so that the warp writes whole rows:
+            // thread = row on the way in, a row's 16-byte chunks side by side on the way out
+            unsigned char* stage = q_s + ti * Q_BYTES + (warp & 3) * 32 * (2 * D);
 #pragma unroll 1
             for (int c = 0; c < D; c += 32) {
                 float v[32];
                 tmem_load32(o_addr + c, v);
-                if (valid) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] *= inv;
+                for (int i = 0; i < 32; ++i) v[i] *= inv;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) store8<bf16>(dst + c + i, v + i);
-                }
+                for (int i = 0; i < 32; i += 8)
+                    store8<bf16>(reinterpret_cast<bf16*>(stage + lane * (2 * D) + ((((c + i) >> 3) ^ (lane & 7)) << 4)), v + i);
+            }
+            __syncwarp();
+            const int c = lane % CPR;
+#pragma unroll
+            for (int k = 0; k < CPR; ++k) {
+                const int row_in_warp = k * RPI + lane / CPR;
+                const long long to = __shfl_sync(FULL, out_off, row_in_warp);
+                const uint4 v = *reinterpret_cast<const uint4*>(stage + row_in_warp * (2 * D) + ((c ^ (row_in_warp & 7)) << 4));
+                if (to >= 0) *reinterpret_cast<uint4*>(out + to + c * 8) = v;
             }
         }
     }
