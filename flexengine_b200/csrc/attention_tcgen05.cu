@@ -180,45 +180,51 @@ __device__ __forceinline__ int swizzled(int r, int c, int block_bytes) {
 // The softmax of one row over a key tile, the 64 scores in registers.  MASKED: the tile crosses
 // the causal edge or the window's edge for some row of the warp; ``hi`` and ``lo`` are then this
 // row's last and first visible key relative to the tile.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float m;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+    return m;
+}
 template <bool MASKED>
 __device__ __forceinline__ float row_max(const unsigned* r, int hi, int lo) {
     float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, m2 = -CUDART_INF_F, m3 = -CUDART_INF_F;
 #pragma unroll
-    for (int i = 0; i < KEYS; i += 4) {
-        float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]), v2 = __uint_as_float(r[i + 2]), v3 = __uint_as_float(r[i + 3]);
-        if (MASKED) {
-            if (i > hi || i < lo) v0 = -CUDART_INF_F;
-            if (i + 1 > hi || i + 1 < lo) v1 = -CUDART_INF_F;
-            if (i + 2 > hi || i + 2 < lo) v2 = -CUDART_INF_F;
-            if (i + 3 > hi || i + 3 < lo) v3 = -CUDART_INF_F;
+    for (int i = 0; i < KEYS; i += 8) {
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            v[e] = __uint_as_float(r[i + e]);
+            if (MASKED && (i + e > hi || i + e < lo)) v[e] = -CUDART_INF_F;
         }
-        m0 = fmaxf(m0, v0), m1 = fmaxf(m1, v1), m2 = fmaxf(m2, v2), m3 = fmaxf(m3, v3);
+        m0 = max3(m0, v[0], v[1]), m1 = max3(m1, v[2], v[3]), m2 = max3(m2, v[4], v[5]), m3 = max3(m3, v[6], v[7]);
     }
     return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 // P = 2^(s scale - ref) as bfloat16 pairs over the scores' own columns (32 of the 64); returns the row's sum.
+// The multiply-adds and the sums run two floats per instruction.
 template <bool MASKED>
 __device__ __forceinline__ float row_exp(const unsigned* r, unsigned p_addr, int hi, int lo, float scale_log2, float ref) {
-    float s0 = 0.f, s1 = 0.f;
+    float2 sum = make_float2(0.f, 0.f);
+    const float2 scale2 = make_float2(scale_log2, scale_log2), ref2 = make_float2(-ref, -ref);
 #pragma unroll
     for (int c = 0; c < KEYS; c += 32) {
         unsigned packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int k = c + 2 * i;
-            float x = ex2(fmaf(__uint_as_float(r[k]), scale_log2, -ref));
-            float y = ex2(fmaf(__uint_as_float(r[k + 1]), scale_log2, -ref));
+            const float2 t = __ffma2_rn(make_float2(__uint_as_float(r[k]), __uint_as_float(r[k + 1])), scale2, ref2);
+            float2 e = make_float2(ex2(t.x), ex2(t.y));
             if (MASKED) {
-                if (k > hi || k < lo) x = 0.f;
-                if (k + 1 > hi || k + 1 < lo) y = 0.f;
+                if (k > hi || k < lo) e.x = 0.f;
+                if (k + 1 > hi || k + 1 < lo) e.y = 0.f;
             }
-            s0 += x, s1 += y;
-            const __nv_bfloat162 pair = __floats2bfloat162_rn(x, y);
+            sum = __fadd2_rn(sum, e);
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(e.x, e.y);
             packed[i] = *reinterpret_cast<const unsigned*>(&pair);
         }
         tmem_store16(p_addr + (c >> 1), packed);
     }
-    return s0 + s1;
+    return sum.x + sum.y;
 }
 
 template <int D>
@@ -308,6 +314,8 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
         // ---- loaders: the first 64 look up one key of the tile each, then all copy ----
         const int lt = tid - 256;
         const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
+        constexpr int ROW_STEP = 128 / CPR;                        // 8 (head size 128) or 16 (head size 64) rows per pass
+        const int chunk = lt % CPR, row0 = lt / CPR, smem_off0 = swizzled(row0, chunk, KV_BLOCK);
         for (int j = 0; j < n_tiles; ++j) {
             const int s = j % KV_STAGES;
             mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, &give_up);     // free from the start
@@ -329,14 +337,14 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             if (give_up) break;                                    // the same for all loaders after the barrier
             unsigned char* k_s = kv_s + s * 2 * KV_BYTES;
             unsigned char* v_s = k_s + KV_BYTES;
-            for (int idx = lt; idx < KEYS * CPR; idx += 128) {
-                const int row = idx / CPR, c = idx % CPR;
-                const long long ro = offs[row];
+            // this thread's chunk of a row is always the same; its rows are ROW_STEP apart, which keeps row & 7
+#pragma unroll
+            for (int k = 0; k < KEYS / ROW_STEP; ++k) {
+                const long long ro = offs[row0 + k * ROW_STEP];
                 const bool ok = ro >= 0;
-                const long long from = ok ? ro + c * 8 : 0;
-                const int o = swizzled(row, c, KV_BLOCK);
-                cp_async16(k_s + o, kc + from, ok ? 16 : 0);       // keys out of range read as zeros
-                cp_async16(v_s + o, vc + from, ok ? 16 : 0);
+                const long long from = ok ? ro + chunk * 8 : 0;
+                cp_async16(k_s + smem_off0 + k * ROW_STEP * 128, kc + from, ok ? 16 : 0);     // keys out of range read as zeros
+                cp_async16(v_s + smem_off0 + k * ROW_STEP * 128, vc + from, ok ? 16 : 0);
             }
             cp_async_wait_all();
             fence_proxy_async();
