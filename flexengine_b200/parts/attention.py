@@ -60,18 +60,21 @@ class AttentionMixer(Mixer):
         ops = ctx.ops
         group = ctx.groups[entry.cache_group]
         k_cache, v_cache = group.kv_slot(entry.cache_slot)
-        rotary = self.position.rotary_table(h.device)
-        if rotary is None:
-            inv_freq, rot = None, 0
+        slot_mapping = group.slot_mapping if entry.write_cache else None
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        if self.position.applies_itself:
+            # an encoding of its own: projection and bias, the encoding on the query and key heads in place,
+            # then the keys and values to their cache slots
+            qkv = ops.linear(h, self.qkv_weight, self.qkv_bias_)
+            self.position.apply(ctx, qkv[:, :nq * d].view(-1, nq, d), qkv[:, nq * d:(nq + nkv) * d].view(-1, nkv, d))
+            ops.qkv_bias_rope_cache(qkv, None, ctx.positions, None, 0, slot_mapping, k_cache, v_cache, nq, nkv, d,
+                                    group.page_size)
         else:
-            inv_freq, rot = rotary
-        # projection, bias, rotation and the cache write are one operation (one kernel in decode); a
-        # run entry that only reads another entry's cache passes no slot mapping, so nothing is written
-        qkv = ops.qkv_projection(h, self.qkv_weight, self.qkv_bias_, ctx.positions, inv_freq, rot,
-                                 group.slot_mapping if entry.write_cache else None, k_cache, v_cache,
-                                 self.num_heads, self.num_kv_heads, self.head_dim, group.page_size)
-        if rotary is None:
-            self.position.apply(ctx, qkv, None)
+            # projection, bias, rotation and the cache write are one operation (one kernel in decode); a
+            # run entry that only reads another entry's cache passes no slot mapping, so nothing is written
+            inv_freq, rot = self.position.rotary_table(h.device) or (None, 0)
+            qkv = ops.qkv_projection(h, self.qkv_weight, self.qkv_bias_, ctx.positions, inv_freq, rot, slot_mapping,
+                                     k_cache, v_cache, nq, nkv, d, group.page_size)
         out = ops.paged_attention(qkv, k_cache, v_cache, group.block_table, ctx, self.num_heads,
                                   self.num_kv_heads, self.head_dim, group.page_size, self.scale, self.window)
         return ops.linear(out, self.out_weight, self.out_bias_)

@@ -16,8 +16,12 @@ Norm:            ``forward(ctx, residual, delta, rows=None) -> h``: adds ``delta
                  to the float32 residual stream in place and returns the normalised rows
                  in the compute dtype; with ``rows`` it reads only those rows and leaves the
                  residual untouched.
-PositionEncoding: ``rotary_table()`` -> (inv_freq float32 [rot/2], rot) to be fused into the
-                 mixer's kernel, or None; then ``apply(ctx, q, k)`` is called instead.
+PositionEncoding: ``rotary_table(device)`` -> (inv_freq float32 [rot/2], rot) for the half-split
+                 rotation that the mixer's kernel does itself, or None for no rotation there; an
+                 encoding of its own overrides ``apply(ctx, q, k)``, which rewrites the query heads
+                 q [T, nq, d] and key heads k [T, nkv, d] in place (views of one projection,
+                 biases added) before the keys go to the cache; ``ctx.positions`` are the tokens'
+                 absolute positions.
 Block:           ``forward(ctx, residual, pending, entry) -> pending``: the arrangement of
                  norms, mixer and feed-forward around the residual stream.
 """
@@ -111,3 +115,9 @@ class PositionEncoding(Part):
 
     def apply(self, ctx, q, k):
         return None
+
+    @property
+    def applies_itself(self) -> bool:
+        """True when the class brings an ``apply`` of its own: the mixer then projects, lets the encoding
+        rewrite queries and keys, and writes the cache afterwards, instead of the fused kernel."""
+        return type(self).apply is not PositionEncoding.apply

@@ -1,6 +1,8 @@
 """Each part alone against the plain implementation, and the generality of the arrangement:
 a toy mixer with state of its own, a run order that names a layer twice, and a run entry that
-reads another entry's cache: registered, built and stepped from this file alone.
+reads another entry's cache; and a second toy architecture whose feed-forward routes tokens to
+experts, whose position encoding rotates interleaved pairs and whose norm centres its rows:
+all registered, built and stepped from this file alone.
 
 Everything runs on the CPU with the reference kernels and, marked ``gpu``, with the CUDA kernels.
 """
@@ -18,8 +20,9 @@ import plain_model
 from flexengine_b200.cache import CacheManager
 from flexengine_b200.config import register_architecture
 from flexengine_b200.engine import ModelRunner, StepEntry
-from flexengine_b200.parts import (CacheGroupSpec, LayerSpec, Mixer, ModelPlan, PartSpec, RunEntry, WeightBinding,
-                                   WeightSource, build_part, register_mixer)
+from flexengine_b200.parts import (CacheGroupSpec, FeedForward, LayerSpec, Mixer, ModelPlan, Norm, PartSpec,
+                                   PositionEncoding, RunEntry, WeightBinding, WeightSource, build_part,
+                                   register_feed_forward, register_mixer, register_norm, register_position)
 from flexengine_b200.weights import load_model, write_random_model
 
 DEVICES = [pytest.param("cpu", id="cpu"), pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu)]
@@ -277,3 +280,192 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_dir, device):
         want = toy_reference(w, ids)
         got = torch.stack([results[(rid, p)] for p in range(len(ids))])
         helpers.assert_logits_close(got, want, "float32", f"toy {rid}")
+
+
+# ---- a second toy architecture: routed feed-forward, a position encoding and a norm of its own ----------------
+class InterleavedRotary(PositionEncoding):
+    """Rotation of the pairs (2i, 2i + 1) by position * base^(-2i/d): another pairing than the framework's
+    half-split form, so the mixer cannot fuse it and calls ``apply`` before the keys go to the cache."""
+
+    def __init__(self, head_dim: int, base: float):
+        self.head_dim, self.base = int(head_dim), float(base)
+
+    def apply(self, ctx, q, k):
+        d = self.head_dim
+        inv = 1.0 / self.base ** (torch.arange(0, d, 2, dtype=torch.float32, device=q.device) / d)
+        ang = ctx.positions.float()[:, None] * inv[None, :]
+        cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        for x in (q, k):
+            even, odd = x[..., 0::2].float(), x[..., 1::2].float()
+            new_even, new_odd = even * cos - odd * sin, odd * cos + even * sin       # both before either is written
+            x[..., 0::2] = new_even.to(x.dtype)
+            x[..., 1::2] = new_odd.to(x.dtype)
+
+
+class TopTwoExperts(FeedForward):
+    """Router logits and softmax in float32, the two best experts per token with weights renormalised to
+    one, each expert a two-matrix ReLU network."""
+
+    def __init__(self, hidden_size: int, inner_size: int, experts: int):
+        self.hidden_size, self.inner_size, self.experts = int(hidden_size), int(inner_size), int(experts)
+
+    def parameter_shapes(self):
+        h, i, e = self.hidden_size, self.inner_size, self.experts
+        return {"router.weight": ((e, h), "matrix"), "w_in": ((e, i, h), "matrix"), "w_out": ((e, h, i), "matrix")}
+
+    def forward(self, ctx, h):
+        probs = torch.softmax(h.float() @ self.router_weight.float().T, dim=-1)
+        top, which = probs.topk(2, dim=-1)
+        gate = torch.zeros_like(probs).scatter_(1, which, top / top.sum(-1, keepdim=True))
+        out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+        for e in range(self.experts):           # dense over experts: a token's unchosen experts weigh zero
+            inner = torch.relu(ctx.ops.linear(h, self.w_in[e]))
+            out += gate[:, e:e + 1] * ctx.ops.linear(inner, self.w_out[e]).float()
+        return out.to(h.dtype)
+
+
+class CentredNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * weight + bias over the float32 residual stream."""
+
+    def __init__(self, hidden_size: int, eps: float):
+        self.hidden_size, self.eps = int(hidden_size), float(eps)
+
+    def parameter_shapes(self):
+        return {"weight": ((self.hidden_size,), "vector"), "bias": ((self.hidden_size,), "vector")}
+
+    def forward(self, ctx, residual, delta, rows=None):
+        if rows is not None:
+            x = residual[rows.long()] + (delta[rows.long()].float() if delta is not None else 0.0)
+        else:
+            if delta is not None:
+                residual += delta.float()
+            x = residual
+        y = (x - x.mean(-1, keepdim=True)) * torch.rsqrt(x.var(-1, unbiased=False, keepdim=True) + self.eps)
+        return (y * self.weight + self.bias).to(ctx.dtype)
+
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    vocab_size: int
+    width: int
+    depth: int
+    heads: int
+    head_size: int
+    inner: int
+    experts: int
+    rope_base: float
+    eps: float
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(*(type_(data[name]) for name, type_ in (
+            ("vocab_size", int), ("width", int), ("depth", int), ("heads", int), ("head_size", int), ("inner", int),
+            ("experts", int), ("rope_base", float), ("eps", float))))
+
+
+ROUTED = {"architectures": ["ToyRoutedForCausalLM"], "vocab_size": 61, "width": 40, "depth": 2, "heads": 2,
+          "head_size": 16, "inner": 24, "experts": 3, "rope_base": 77.0, "eps": 2e-5}
+
+
+def build_routed_plan(cfg: RoutedConfig) -> ModelPlan:
+    h, v, nq, d = cfg.width, cfg.vocab_size, cfg.heads, cfg.head_size
+    norm = PartSpec("toy_centred_norm", {"hidden_size": h, "eps": cfg.eps})
+    mixer = PartSpec("attention", {"hidden_size": h, "num_heads": nq, "num_kv_heads": nq, "head_dim": d, "qkv_bias": False,
+                                   "position": PartSpec("toy_interleaved_rotary", {"head_dim": d, "base": cfg.rope_base})})
+    ffn = PartSpec("toy_top_two_experts", {"hidden_size": h, "inner_size": cfg.inner, "experts": cfg.experts})
+    layers = [LayerSpec(mixer, ffn, norm) for _ in range(cfg.depth)]
+    run = [RunEntry(l, 0, l, True) for l in range(cfg.depth)]
+    groups = [CacheGroupSpec("attention", "full", slots=cfg.depth, kv_heads=nq, head_dim=d)]
+
+    def src(name, *shape):
+        return WeightSource(name, tuple(shape))
+    bindings = [WeightBinding(("embedding", "weight"), (src("tok.weight", v, h),)),
+                WeightBinding(("lm_head", "weight"), (src("out.weight", v, h),)),
+                WeightBinding(("final_norm", "weight"), (src("ln_f.weight", h),), kind="vector"),
+                WeightBinding(("final_norm", "bias"), (src("ln_f.bias", h),), kind="vector")]
+    for l in range(cfg.depth):
+        p = f"blocks.{l}."
+        for part, short in (("input_norm", "ln1"), ("post_mixer_norm", "ln2")):
+            bindings += [WeightBinding(("layer", l, part, "weight"), (src(p + short + ".weight", h),), kind="vector"),
+                         WeightBinding(("layer", l, part, "bias"), (src(p + short + ".bias", h),), kind="vector")]
+        bindings += [WeightBinding(("layer", l, "mixer", "qkv.weight"), (src(p + "qkv.weight", 3 * nq * d, h),)),
+                     WeightBinding(("layer", l, "mixer", "out.weight"), (src(p + "proj.weight", h, nq * d),)),
+                     WeightBinding(("layer", l, "feed_forward", "router.weight"), (src(p + "router.weight", cfg.experts, h),)),
+                     WeightBinding(("layer", l, "feed_forward", "w_in"), (src(p + "experts.w_in", cfg.experts, cfg.inner, h),)),
+                     WeightBinding(("layer", l, "feed_forward", "w_out"), (src(p + "experts.w_out", cfg.experts, h, cfg.inner),))]
+    init = {"default": ("normal", 0.0, 0.2), "suffix": {".weight_of_norm": ("normal", 1.0, 0.05)}}
+    init["suffix"].update({f"{n}.weight": ("normal", 1.0, 0.05) for n in ("ln1", "ln2", "ln_f")})
+    init["suffix"].update({f"{n}.bias": ("normal", 0.0, 0.05) for n in ("ln1", "ln2", "ln_f")})
+    init["suffix"]["router.weight"] = ("normal", 0.0, 1.0)
+    return ModelPlan("ToyRoutedForCausalLM", v, h, layers, run, groups, norm, bindings, init=init)
+
+
+register_position("toy_interleaved_rotary", InterleavedRotary)
+register_feed_forward("toy_top_two_experts", TopTwoExperts)
+register_norm("toy_centred_norm", CentredNorm)
+register_architecture("ToyRoutedForCausalLM", RoutedConfig, build_routed_plan)
+
+
+def routed_reference(w: dict, ids) -> torch.Tensor:
+    """The routed toy over one whole sequence, written out plainly: no cache, no parts of the framework."""
+    cfg = ROUTED
+    T, nq, d, eps = len(ids), cfg["heads"], cfg["head_size"], cfg["eps"]
+
+    def norm(x, name):
+        y = (x - x.mean(-1, keepdim=True)) / torch.sqrt(x.var(-1, unbiased=False, keepdim=True) + eps)
+        return y * w[name + ".weight"] + w[name + ".bias"]
+
+    def rotate(x):                                            # [T, heads, d], pairs (2i, 2i + 1)
+        inv = 1.0 / cfg["rope_base"] ** (torch.arange(0, d, 2, dtype=torch.float32) / d)
+        ang = torch.arange(T, dtype=torch.float32)[:, None] * inv[None, :]
+        cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = torch.empty_like(x)
+        out[..., 0::2] = x[..., 0::2] * cos - x[..., 1::2] * sin
+        out[..., 1::2] = x[..., 1::2] * cos + x[..., 0::2] * sin
+        return out
+
+    x = w["tok.weight"][torch.tensor(ids)]
+    for l in range(cfg["depth"]):
+        p = f"blocks.{l}."
+        q, k, v = (norm(x, p + "ln1") @ w[p + "qkv.weight"].T).view(T, 3, nq, d).unbind(1)
+        x = x + plain_model.causal_gqa_attention(rotate(q), rotate(k), v).reshape(T, -1) @ w[p + "proj.weight"].T
+        h = norm(x, p + "ln2")
+        probs = torch.softmax(h @ w[p + "router.weight"].T, dim=-1)
+        delta = torch.zeros_like(x)
+        for t in range(T):
+            top, which = probs[t].topk(2)
+            for weight, e in zip(top / top.sum(), which.tolist()):
+                delta[t] += weight * (torch.relu(h[t] @ w[p + "experts.w_in"][e].T) @ w[p + "experts.w_out"][e].T)
+        x = x + delta
+    return norm(x, "ln_f") @ w["out.weight"].T
+
+
+@pytest.fixture(scope="module")
+def routed_dir(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("routed"))
+    write_random_model(ROUTED, d, seed=9, dtype="float32")
+    return d
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_routed_toy_with_its_own_feed_forward_position_encoding_and_norm(routed_dir, device):
+    _cfg, plan, model = load_model(routed_dir, "float32", device)
+    block = model.blocks[0]
+    assert type(block.feed_forward).__name__ == "TopTwoExperts" and type(block.mixer.position).__name__ == "InterleavedRotary"
+    assert block.mixer.position.applies_itself and type(model.final_norm).__name__ == "CentredNorm"
+    _, w = plain_model.read_model_folder(routed_dir)
+    rng = random.Random(1)
+    requests = {f"m{i}": helpers.random_prompt(rng, n, ROUTED["vocab_size"]) for i, n in enumerate([33, 12, 26, 19])}
+    steps = helpers.steps_mixed(requests, rng, live=3, decode_tail=5)
+    cache = CacheManager(plan.cache_groups, helpers.peak_pages(steps, 4), 4, 3, torch.float32, device)
+    runner = ModelRunner(model, cache, ops=provider(device))
+    results = helpers.run_steps(runner, steps)
+    assert cache.used_pages == 0
+    for rid, ids in requests.items():
+        want = routed_reference(w, ids)
+        got = torch.stack([results[(rid, p)] for p in range(len(ids))])
+        helpers.assert_logits_close(got, want, "float32", f"routed {rid}")
+    # the router did route: not every token chose the same pair of experts
+    h = torch.randn(50, ROUTED["width"], device=device)
+    chosen = (h @ block.feed_forward.router_weight.float().T).topk(2, dim=-1).indices.sort(-1).values
+    assert len({tuple(c) for c in chosen.tolist()}) > 1
