@@ -4,7 +4,8 @@ Names, defaults and checks follow the reference's EngineConfig
 (src/flexengine/engine/config.py:17-62) and its environment convention
 (config.py:64-86).  ``attention_backend`` and ``rmsnorm_backend`` are gone (there is
 one kernel path); ``dtype`` is "bfloat16" or "float32"; ``kv_num_blocks=0`` sizes the
-pool from free device memory.
+pool from free device memory; ``overlap_steps`` (no counterpart in the reference) lets the
+host plan and launch a step while the device still runs the one before.
 """
 from __future__ import annotations
 
@@ -39,6 +40,7 @@ class EngineConfig:
     kv_num_blocks: int = 1024          # 0: fill what device memory is left
     kv_memory_fraction: float = 0.9    # used only when kv_num_blocks == 0
     cuda_graph: bool = False
+    overlap_steps: bool = True         # launch a step before the host has read the tokens of the one before
     scheduler_policy: str = "fcfs"
     ttft_slo_ms: float = 2000.0
     itl_slo_ms: float = 200.0

@@ -41,6 +41,34 @@ extern "C" int fe_embedding(const int* ids, const void* table, float* out, int T
 }
 
 // ---------------------------------------------------------------------------------------------
+// token_ids[rows[i]] = previous[sources[i]] for every i with rows[i] >= 0: the tokens that the step
+// before sampled go into this step's input on the device, before the host has seen them.
+__global__ void carry_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ rows,
+                                    const int* __restrict__ sources, const int* __restrict__ previous, int n, int T,
+                                    int n_previous, int* __restrict__ status) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int r = rows[i], s = sources[i];
+    if (r < 0) return;
+    if (r >= T || s < 0 || s >= n_previous) {
+        if (status) atomicOr(status, FE_STATUS_BAD_TOKEN);
+        return;
+    }
+    token_ids[r] = previous[s];
+}
+
+extern "C" int fe_carry_tokens(int* token_ids, const int* rows, const int* sources, const int* previous, int n, int T,
+                               int n_previous, int* status, cudaStream_t stream) {
+    FE_REQUIRE(n >= 0 && T >= 0 && n_previous >= 0, "carry_tokens: bad sizes");
+    if (n == 0) return 0;
+    fe::launch(carry_tokens_kernel, (n + 127) / 128, 128, 0, stream, token_ids, rows, sources, previous, n, T, n_previous,
+               status);
+    return fe_check_launch("carry_tokens");
+}
+
+// ---------------------------------------------------------------------------------------------
 // One block per output row.  rows == nullptr: row i; the residual is updated in place (residual
 // += delta).  rows != nullptr: output row i reads residual row rows[i] (+ delta row rows[i]) and
 // the residual is left as it is.  The row is staged in shared memory (H floats).

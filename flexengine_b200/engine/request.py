@@ -43,6 +43,9 @@ class Event:
     timestamp: float = field(default_factory=monotonic)
 
 
+PENDING = -1      # in ``generated_ids``: a token that was sampled on the device and that the host has not read yet
+
+
 @dataclass
 class Request:
     request_id: str
@@ -88,6 +91,11 @@ class Request:
     @property
     def in_prefill(self) -> bool:
         return self.cached_tokens < self.context_length
+
+    @property
+    def awaits_last_token(self) -> bool:
+        """The token on its way is the last one ``max_tokens`` allows: nothing more is to be run."""
+        return bool(self.generated_ids) and self.generated_ids[-1] == PENDING and len(self.generated_ids) >= self.max_tokens
 
     def next_inputs(self, count: int) -> list:
         if count <= 0:

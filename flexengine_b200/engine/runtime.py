@@ -12,6 +12,14 @@ without sampling a second time from it (runtime.py:242-251,318-324); a token in 
 sequence set finishes with "stop", reaching ``max_tokens`` with "length" (runtime.py:343-346);
 an exception in the executor faults the engine and fails every live request
 (runtime.py:349-356).  Logits are asked for only where a token will be sampled.
+
+Unlike the reference, a step is launched before the host has read the tokens of the step before
+(``overlap_steps``): sampled tokens stay on the device, the next step takes them from there
+(``StepEntry.carry``), and the host reads them one step late, while the device is busy.  A request's
+``generated_ids`` holds ``PENDING`` in the place of a token that is on its way.  A request that turns
+out to have ended with an end-of-sequence token has then been run one token too far; that token is
+dropped.  Before anyone is preempted the tokens on their way are read, so that preemption and
+recomputation see exact state.
 """
 from __future__ import annotations
 
@@ -28,7 +36,7 @@ from ..cache.page_pool import CacheExhausted
 from ..config.engine_config import EngineConfig
 from ..observability.traces import TraceWriter, nvtx
 from ..sampling.sampler import Sampler
-from .request import TERMINAL, Event, Request, State
+from .request import PENDING, TERMINAL, Event, Request, State
 from .scheduler import Scheduler
 from .step import ModelRunner, StepEntry
 
@@ -44,6 +52,16 @@ class GenerationOutput:
     token_ids: list
     text: str
     finish_reason: str | None
+
+
+@dataclass
+class _InFlight:
+    """The step whose sampled tokens the host has not read yet."""
+    sampled: list                        # [(request, its place in generated_ids)] in the order of ``tokens``
+    tokens: torch.Tensor                 # int32 [len(sampled)], where the logits were
+    host: torch.Tensor | None = None     # pinned copy, complete once ``event`` has passed
+    event: object = None
+    index: dict | None = None            # request id -> place in ``tokens``
 
 
 class Engine:
@@ -71,6 +89,7 @@ class Engine:
         self.completed_count = 0
         self.preemption_count = 0
         self.output_tokens = 0
+        self._in_flight: _InFlight | None = None
         self.trace = TraceWriter(config.trace_dir)
         self.trace.metadata(config)
 
@@ -106,6 +125,7 @@ class Engine:
         if self.worker:
             self.worker.join(timeout=20)
         with self.lock:
+            self._collect()
             for req in list(self.all_requests.values()):
                 if req.state not in TERMINAL:
                     self._finish(req, State.CANCELLED, "cancelled")
@@ -168,6 +188,8 @@ class Engine:
         if req.state in TERMINAL:
             return
         req.transition(state)
+        while req.generated_ids and req.generated_ids[-1] == PENDING:      # run one token too far: dropped
+            req.generated_ids.pop()
         req.finished_at = time.monotonic()
         req.finish_reason = reason
         req.error = error
@@ -197,6 +219,9 @@ class Engine:
             self.running[req.request_id] = req
 
     def _preempt(self, victim: Request) -> None:
+        self._collect()                          # nobody is preempted with a token on its way
+        if victim.state in TERMINAL:
+            return
         self.cache.free(victim.request_id)
         victim.cached_tokens = 0
         victim.replaying = bool(victim.generated_ids)
@@ -216,6 +241,18 @@ class Engine:
             try:
                 self.cache.reserve(req.request_id, target)
             except CacheExhausted:
+                if self._in_flight is not None:
+                    # exact state first: requests that have just ended give their pages back, and nobody is
+                    # preempted with a token on its way
+                    self._collect()
+                    if req.request_id not in self.running:
+                        continue
+                    try:
+                        self.cache.reserve(req.request_id, target)
+                        planned.append(chunk)
+                        continue
+                    except CacheExhausted:
+                        pass
                 selected = {c.request_id for c in planned}
                 victims = [v for v in self.running.values()
                            if v.request_id != req.request_id and v.request_id not in selected
@@ -241,7 +278,11 @@ class Engine:
                 proposed = self.scheduler.plan(list(self.running.values()))
             with nvtx("kv/reserve"):
                 planned = self._reserve_or_preempt(proposed)
+                planned = [c for c in planned if c.request_id in self.running]     # reading tokens may have ended some
             if not planned:
+                if self._in_flight is not None:
+                    self._collect()          # nothing more to launch: the tokens on their way are the progress
+                    return True
                 return False
             scheduler_ms = (time.perf_counter() - t0) * 1000.0
             new_tokens = sum(len(c.input_ids) for c in planned)
@@ -249,31 +290,14 @@ class Engine:
             t1 = time.perf_counter()
             try:
                 with nvtx(f"executor/step batch={len(planned)} tokens={new_tokens}"):
-                    entries = [StepEntry(c.request_id, c.input_ids, [len(c.input_ids) - 1] if c.wants_logits else [])
-                               for c in planned]
-                    sampled = [c for c in planned if c.wants_logits]
-                    logits = self.runner.step(entries)
-                    tokens = []
-                    if sampled:
-                        reqs = [self.running[c.request_id] for c in sampled]
-                        tokens = self.sampler.sample(logits, [r.temperature for r in reqs], [r.top_k for r in reqs],
-                                                     [r.seed for r in reqs], [len(r.generated_ids) for r in reqs])
-                now = time.monotonic()
-                token_of = {c.request_id: int(t) for c, t in zip(sampled, tokens)}
-                for chunk in planned:
-                    req = self.running[chunk.request_id]
-                    if req.first_scheduled_at is None:
-                        req.first_scheduled_at = now
-                    req.cached_tokens += len(chunk.input_ids)
-                    if req.in_prefill:
-                        continue
-                    if req.replaying:
-                        # the recomputed context already gave its token before the preemption
-                        req.replaying = False
-                        continue
-                    self._accept_token(req, token_of[chunk.request_id], now)
+                    launched = self._launch(planned)
+                previous, self._in_flight = self._in_flight, launched
+                self._read_tokens(previous)              # of the step before, while the device runs this one
+                if not self.config.overlap_steps:
+                    self._collect()
             except Exception as ex:  # noqa: BLE001 - any executor failure faults the engine
                 self.fault = f"{type(ex).__name__}: {ex}"
+                self._in_flight = None
                 for req in list(self.all_requests.values()):
                     if req.state not in TERMINAL:
                         self._finish(req, State.FAILED, "error", self.fault)
@@ -291,18 +315,89 @@ class Engine:
                 })
             return True
 
-    def _accept_token(self, req: Request, token: int, now: float) -> None:
-        req.generated_ids.append(token)
+    def _launch(self, planned: list) -> _InFlight:
+        """Run the planned chunks and sample; nothing here waits for the device."""
+        before = self._in_flight
+        entries, sampled = [], []
+        for c in planned:
+            req = self.running[c.request_id]
+            ids, carry = c.input_ids, None
+            if ids[-1] == PENDING:                       # a decode step planned on a token that was on its way
+                last = req.generated_ids[-1]
+                if last == PENDING:
+                    ids, carry = [0], before.index[c.request_id]
+                else:
+                    ids = [last]                         # it has been read since
+            entries.append(StepEntry(c.request_id, ids, [len(ids) - 1] if c.wants_logits else [], carry))
+            if c.wants_logits:
+                sampled.append(req)
+        logits = self.runner.step(entries, before.tokens if before is not None else None)
+        tokens = None
+        if sampled:
+            tokens = self.sampler.sample_on_device(logits, [r.temperature for r in sampled], [r.top_k for r in sampled],
+                                                   [r.seed for r in sampled], [len(r.generated_ids) for r in sampled])
+        now = time.monotonic()
+        places = []
+        for chunk in planned:
+            req = self.running[chunk.request_id]
+            if req.first_scheduled_at is None:
+                req.first_scheduled_at = now
+            req.cached_tokens += len(chunk.input_ids)
+            if req.in_prefill:
+                continue
+            if req.replaying:
+                # the recomputed context already gave its token before the preemption
+                req.replaying = False
+                continue
+            req.generated_ids.append(PENDING)
+            places.append((req, len(req.generated_ids) - 1))
+        assert [r.request_id for r, _ in places] == [r.request_id for r in sampled]
+        record = _InFlight(places, tokens, index={r.request_id: i for i, (r, _) in enumerate(places)})
+        if tokens is not None and tokens.device.type == "cuda":
+            record.host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+            record.host.copy_(tokens, non_blocking=True)
+            record.event = torch.cuda.Event()
+            record.event.record()
+        return record
+
+    def drain(self) -> None:
+        """Wait for the step that was launched last and take its tokens in: afterwards no request
+        holds a token that the host has not read."""
+        with self.lock:
+            self._collect()
+
+    def _collect(self) -> None:
+        """Read the tokens that are on their way, if any."""
+        record, self._in_flight = self._in_flight, None
+        self._read_tokens(record)
+
+    def _read_tokens(self, record: _InFlight | None) -> None:
+        if record is None or not record.sampled:
+            return
+        if record.event is not None:
+            record.event.synchronize()
+            values = record.host.tolist()
+        else:
+            values = record.tokens.tolist()
+        now = time.monotonic()
+        for (req, place), token in zip(record.sampled, values):
+            if req.state in TERMINAL:
+                continue                                  # ended or cancelled meanwhile: one token too far
+            self._accept_token(req, place, int(token), now)
+
+    def _accept_token(self, req: Request, place: int, token: int, now: float) -> None:
+        req.generated_ids[place] = token
+        known = place + 1                                 # a later place may hold the next token on its way
         if req.first_token_at is None:
             req.first_token_at = now
         req.last_token_at = now
         req.token_times.append(now)
         self.output_tokens += 1
         if self.tokenizer is not None:
-            req.text = self.tokenizer.decode(req.generated_ids, skip_special_tokens=True,
+            req.text = self.tokenizer.decode(req.generated_ids[:known], skip_special_tokens=True,
                                              clean_up_tokenization_spaces=False)
             # a trailing replacement character may still be completed by the next tokens
-            stable = req.text.rstrip("�")
+            stable = req.text.rstrip("\ufffd")
             delta = stable[len(req.emitted_text):] if stable.startswith(req.emitted_text) else ""
             if delta:
                 req.emitted_text += delta
@@ -311,7 +406,7 @@ class Engine:
             req.events.put(Event("token", token_id=token))
         if token in self.eos_ids:
             self._finish(req, State.FINISHED, "stop")
-        elif len(req.generated_ids) >= req.max_tokens:
+        elif known >= req.max_tokens:
             self._finish(req, State.FINISHED, "length")
 
     # ---- the Python entry point ----------------------------------------------------------------------
@@ -338,6 +433,7 @@ class Engine:
                 raise RuntimeError("the engine made no progress: the page pool cannot hold any waiting request")
             if max_steps is not None and steps >= max_steps:
                 break
+        self.drain()
         return [GenerationOutput(r.request_id, r.prompt_ids, list(r.generated_ids), r.text, r.finish_reason)
                 for r in (requests[i] for i in sorted(requests))]
 

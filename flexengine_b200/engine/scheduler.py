@@ -60,6 +60,8 @@ class Scheduler:
         for req in self.ordered(requests):
             if budget <= 0:
                 break
+            if req.awaits_last_token:
+                continue
             if req.in_prefill:
                 length = min(budget, req.context_length - req.cached_tokens)
                 if self.policy == "adaptive":

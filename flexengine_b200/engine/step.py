@@ -24,6 +24,8 @@ class StepEntry:
     request_id: str
     tokens: list
     want: list = field(default_factory=list)     # places among ``tokens`` whose logits are wanted
+    carry: int | None = None                     # the one token is element ``carry`` of the tensor given to step()
+                                                 # as ``carried`` (on the device); ``tokens`` holds a placeholder
 
 
 class GroupView:
@@ -182,10 +184,12 @@ class ModelRunner:
         return [dev[o:o + s] for o, s in zip(offsets, sizes)]
 
     # ------------------------------------------------------------------------------------------
-    def _metadata(self, entries, pad_to: int = 0, max_pages: int = 0):
+    def _metadata(self, entries, pad_to: int = 0, max_pages: int = 0, carrying: bool = False):
         """The step's index arrays on the host.  ``pad_to`` > len(entries) appends padding requests of
         one token each (token 0 at position 0, no cache write, state slot -1, page 0) so that a
-        batch fits a fixed shape; ``max_pages`` fixes the width of the block tables."""
+        batch fits a fixed shape; ``max_pages`` fixes the width of the block tables.  ``carrying``
+        appends, for entries whose token is still on the device, the row to fill and where it comes
+        from (one pair per request with a fixed shape, row -1 where nothing is carried)."""
         cache = self.cache
         starts = [cache.tokens_of(e.request_id) for e in entries]
         lengths = [len(e.tokens) for e in entries]
@@ -226,6 +230,12 @@ class ModelRunner:
             bt[len(entries):, :] = 0
             arrays += [np.asarray(slots, dtype=np.int32), bt.reshape(-1)]
             widths.append(width)
+        if carrying:
+            carried = [(cu_q[r], e.carry) for r, e in enumerate(entries) if e.carry is not None]
+            if pad_to:
+                carried = [(cu_q[r], e.carry) if e.carry is not None else (-1, 0) for r, e in enumerate(entries)]
+                carried += [(-1, 0)] * pad
+            arrays += [np.asarray([c[0] for c in carried], dtype=np.int32), np.asarray([c[1] for c in carried], dtype=np.int32)]
         info = dict(T=len(token_ids), R=R, rows=len(logit_rows), starts=all_starts, lengths=all_lengths,
                     state_slots=state_slots, widths=widths, max_q_len=max(all_lengths), max_ctx_len=max(ctx_len),
                     request_ids=[e.request_id for e in entries])
@@ -253,9 +263,13 @@ class ModelRunner:
         ctx.host_state_slots, ctx.request_ids = info["state_slots"], info["request_ids"]
         return ctx
 
-    def build_context(self, entries) -> StepContext:
-        arrays, info = self._metadata(entries)
-        return self._context(self._upload(arrays), info)
+    def build_context(self, entries, carried=None) -> StepContext:
+        arrays, info = self._metadata(entries, carrying=carried is not None)
+        dev = self._upload(arrays)
+        ctx = self._context(dev, info)
+        if carried is not None:
+            self.ops.carry_tokens(ctx.token_ids, dev[-2], dev[-1], carried)
+        return ctx
 
     # ---- decode steps as CUDA graphs -----------------------------------------------------------------
     def enable_decode_graphs(self, max_batch: int, max_model_len: int) -> None:
@@ -298,23 +312,25 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx)
-        record = dict(graph=graph, static=static, logits=logits, total=total,
+        record = dict(graph=graph, static=static, logits=logits, total=total, views=dev,
                       launches=getattr(self.ops, "launches", 0) - launches_before)
         self._graphs[bucket] = record
         return record
 
-    def _graph_step(self, entries):
+    def _graph_step(self, entries, carried=None):
         """Replay the graph of the smallest bucket that holds the batch; None if none does."""
         bucket = next((b for b in self._graph_buckets if b >= len(entries)), None)
         if bucket is None:
             return None
         if max(self.cache.tokens_of(e.request_id) for e in entries) + 1 > self._graph_max_len:
             return None
-        arrays, info = self._metadata(entries, pad_to=bucket, max_pages=self._graph_max_pages)
+        # the carry arrays are always part of a bucket's buffer, so that its layout does not change
+        arrays, info = self._metadata(entries, pad_to=bucket, max_pages=self._graph_max_pages, carrying=True)
         fresh = bucket not in self._graphs
         record = self._graph_for(bucket, arrays, info)
-        if not fresh:
-            self._upload(arrays, into=record["static"])
+        dev = record["views"] if fresh else self._upload(arrays, into=record["static"])
+        if carried is not None:
+            self.ops.carry_tokens(dev[0], dev[-2], dev[-1], carried)
         record["graph"].replay()
         if hasattr(self.ops, "launches"):
             self.ops.launches += record["launches"]
@@ -322,19 +338,29 @@ class ModelRunner:
         return record["logits"][:len(entries)]
 
     @torch.inference_mode()
-    def step(self, entries):
+    def step(self, entries, carried=None):
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] in the order
         of the entries and of their ``want`` (None when nothing is wanted).  With decode graphs
-        on, the returned tensor of a decode step is overwritten by the next such step."""
+        on, the returned tensor of a decode step is overwritten by the next such step.
+        ``carried``: an int32 tensor on the device from which entries with ``carry`` take their token
+        (what the step before sampled, not yet read by the host)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._check(entries)
+        if any(e.carry is not None for e in entries):
+            if carried is None:
+                raise ValueError("an entry carries its token but no tensor of carried tokens was given")
+            for e in entries:
+                if e.carry is not None and (len(e.tokens) != 1 or not 0 <= e.carry < carried.numel()):
+                    raise ValueError(f"request {e.request_id!r}: a carried token is one token, inside the tensor given")
+        else:
+            carried = None
         self._reserve(entries)
         logits = None
         decode = self._graph_buckets and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         if decode:
-            logits = self._graph_step(entries)
+            logits = self._graph_step(entries, carried)
         if logits is None:
-            ctx = self.build_context(entries)
+            ctx = self.build_context(entries, carried)
             logits = self.model.forward(ctx)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))

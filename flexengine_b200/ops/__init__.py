@@ -88,6 +88,16 @@ def embedding(token_ids, table):
     return out
 
 
+def carry_tokens(token_ids, rows, sources, previous):
+    """token_ids[rows[i]] = previous[sources[i]] where rows[i] >= 0 (all int32, in place): what the
+    step before sampled becomes this step's input without a round trip through the host."""
+    _need_cuda(token_ids, rows, sources, previous)
+    if previous.dtype != torch.int32 or token_ids.dtype != torch.int32:
+        raise TypeError("carry_tokens: int32 tensors")
+    _run(_core(), "fe_carry_tokens", _ptr(token_ids), _ptr(rows), _ptr(sources), _ptr(previous), _c_int(rows.numel()),
+         _c_int(token_ids.numel()), _c_int(previous.numel()), _ptr(status_word(token_ids.device)), _stream())
+
+
 def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None):
     """Fused residual add + RMSNorm.  rows=None: residual += delta in place (all rows) and every row
     is normalised; rows given: only those rows are read (residual[rows] + delta[rows]), nothing is

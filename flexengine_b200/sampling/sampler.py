@@ -27,6 +27,10 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, temperatures, top_ks, seeds, draws) -> list:
         """logits float32 [R, V]; the other arguments are sequences of length R.  Returns R token ids."""
+        return self.sample_on_device(logits, temperatures, top_ks, seeds, draws).tolist()
+
+    def sample_on_device(self, logits: torch.Tensor, temperatures, top_ks, seeds, draws) -> torch.Tensor:
+        """As ``sample`` but the token ids stay where the logits are (int32 [R]); nothing waits for the device."""
         if logits.dim() != 2 or logits.shape[0] != len(temperatures):
             raise ValueError("Expected logits [requests, vocab]")
         for t, k in zip(temperatures, top_ks):
@@ -41,7 +45,7 @@ class Sampler:
                                     torch.zeros(n, dtype=torch.int32, device=dev),
                                     torch.zeros(n, dtype=torch.int64, device=dev))
             temperature, top_k, zero64 = self._zeros[key]
-            return self.ops.sample(logits, temperature, top_k, zero64, zero64).tolist()
+            return self.ops.sample(logits, temperature, top_k, zero64, zero64)
         # one host buffer, one copy: [temperature bits | top_k | seed lo, hi | draw lo, hi] as 64-bit words
         packed = torch.empty((4, n), dtype=torch.int64, pin_memory=dev.type == "cuda")
         packed[0] = torch.tensor(list(temperatures), dtype=torch.float32).view(torch.int32).to(torch.int64)
@@ -51,4 +55,4 @@ class Sampler:
         on_dev = packed.to(dev, non_blocking=True)
         temperature = on_dev[0].to(torch.int32).view(torch.float32)
         top_k = on_dev[1].to(torch.int32)
-        return self.ops.sample(logits, temperature, top_k, on_dev[2].contiguous(), on_dev[3].contiguous()).tolist()
+        return self.ops.sample(logits, temperature, top_k, on_dev[2].contiguous(), on_dev[3].contiguous())

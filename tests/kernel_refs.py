@@ -16,6 +16,11 @@ def embedding(token_ids, table):
     return table[token_ids.long()].float()
 
 
+def carry_tokens(token_ids, rows, sources, previous):
+    keep = rows >= 0
+    token_ids[rows[keep].long()] = previous[sources[keep].long()].to(token_ids.dtype)
+
+
 def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None):
     if rows is None:
         if delta is not None:

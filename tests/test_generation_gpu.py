@@ -156,15 +156,36 @@ def test_decode_graphs_give_the_same_logits(model_dirs, dtype):
     ops.check_status(DEV)
 
 
-def test_engine_with_decode_graphs_generates_the_same_tokens(model_dirs):
+@pytest.mark.parametrize("overlap", [True, False])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_engine_with_decode_graphs_and_overlapped_steps_generates_the_same_tokens(model_dirs, graphs, overlap):
+    """Tokens sampled by one step go into the next on the device (graphs replayed or not) while the host
+    reads them one step late: the same tokens as the plain implementation, greedy and sampled."""
     config, weights = plain_model.read_model_folder(model_dirs["A"], DEV)
     rng = random.Random(8)
     prompts = [helpers.random_prompt(rng, n, 256) for n in (5, 17, 33, 1, 40, 12)]
-    engine = engine_for(model_dirs["A"], "A", "float32", cuda_graph=True, max_num_seqs=4)
+    engine = engine_for(model_dirs["A"], "A", "float32", cuda_graph=graphs, max_num_seqs=4, overlap_steps=overlap)
     outputs = engine.generate(prompts, max_tokens=10)
     for prompt, out in zip(prompts, outputs):
         assert out.token_ids == plain_model.greedy_generate(config, weights, prompt, 10)
-    assert engine.runner.graph_replays > 0 and engine.cache.used_pages == 0
+    assert (engine.runner.graph_replays > 0) == graphs and engine.cache.used_pages == 0 and engine._in_flight is None
+    sampled = engine.generate(prompts, max_tokens=10, temperature=0.7, top_k=12, seed=5)
+    alone = [engine_for(model_dirs["A"], "A", "float32", overlap_steps=False).generate([p], max_tokens=10, temperature=0.7, top_k=12, seed=5 + i)[0].token_ids
+             for i, p in enumerate(prompts)]
+    assert [o.token_ids for o in sampled] == alone
+    from flexengine_b200 import ops
+    ops.check_status(DEV)
+
+
+def test_carry_tokens_kernel():
+    from flexengine_b200 import ops
+    token_ids = torch.arange(10, dtype=torch.int32, device=DEV)
+    previous = torch.tensor([70, 71, 72], dtype=torch.int32, device=DEV)
+    rows = torch.tensor([4, -1, 0, 9], dtype=torch.int32, device=DEV)
+    sources = torch.tensor([2, 0, 0, 1], dtype=torch.int32, device=DEV)
+    ops.carry_tokens(token_ids, rows, sources, previous)
+    assert token_ids.tolist() == [70, 1, 2, 3, 72, 5, 6, 7, 8, 71]
+    ops.check_status(DEV)
 
 
 def test_generate_command_line(model_dirs, capsys):

@@ -90,7 +90,7 @@ class CountingRunner:
         self.calls = []
         self.fail_at = fail_at
 
-    def step(self, entries):
+    def step(self, entries, carried=None):
         if self.fail_at is not None and len(self.calls) >= self.fail_at:
             raise RuntimeError("injected executor failure")
         self.calls.append([(e.request_id, len(e.tokens), list(e.want)) for e in entries])
@@ -99,9 +99,10 @@ class CountingRunner:
             start = self.cache.tokens_of(e.request_id)
             assert self.cache.reserved_tokens(e.request_id) >= start + len(e.tokens)
             self.cache.commit(e.request_id, len(e.tokens))
+            tokens = e.tokens if e.carry is None else [int(carried[e.carry])]     # a token the host has not read yet
             for w in e.want:
                 row = torch.full((32,), -100.0)
-                row[(e.tokens[w] + 1) % 32] = 10.0
+                row[(tokens[w] + 1) % 32] = 10.0
                 rows.append(row)
         return torch.stack(rows) if rows else None
 
@@ -173,6 +174,7 @@ def test_forced_preemption_keeps_outputs():
     a = e.submit([1, 2, 3, 4], max_tokens=7)
     for _ in range(4):
         e.step()
+    e.drain()                                   # the last step's token is read before it is compared
     before = list(a.generated_ids)
     assert before
     e._preempt(a)
@@ -278,3 +280,65 @@ def test_sampled_tokens_do_not_depend_on_batching_or_preemption(model_a):
     assert [o.token_ids for o in outs] == alone
     assert tight.preemption_count >= 1 and tight.cache.used_pages == 0
     assert len(set(map(tuple, alone))) > 1
+
+
+# ---- launching a step before the tokens of the one before have been read ------------------------------------
+def test_overlapped_steps_give_the_same_tokens_and_drop_the_token_run_too_far():
+    """Counting model, end-of-sequence token 0: a request that starts at 28 stops after 29, 30, 31, 0.  With
+    overlap it has been run one step further by the time the host sees the 0; that token is dropped."""
+    results = {}
+    for overlap in (False, True):
+        e = counting_engine(overlap_steps=overlap)
+        a, b, c = e.submit([1, 2, 28], max_tokens=9), e.submit([5], max_tokens=6), e.submit([30], max_tokens=9)
+        run_until_done(e, [a, b, c])
+        e.drain()
+        results[overlap] = [(r.generated_ids, r.finish_reason) for r in (a, b, c)]
+        assert e.cache.used_pages == 0 and not e.cache.requests and e._in_flight is None
+        e.cache.assert_invariants()
+        assert all(-1 not in r.generated_ids for r in (a, b, c))
+        steps_with_a = sum(1 for call in e.runner.calls if any(rid == a.request_id for rid, _, _ in call))
+        assert steps_with_a == (5 if overlap else 4)            # prompt, 29, 30, 31 (, and the 0 when overlapped)
+    assert results[True] == results[False]
+    assert results[True][0] == ([29, 30, 31, 0], "stop") and results[True][1] == ([6, 7, 8, 9, 10, 11], "length")
+    assert results[True][2] == ([31, 0], "stop")
+
+
+def test_a_request_at_its_last_token_is_not_run_again_and_cancel_meets_a_token_on_its_way():
+    e = counting_engine()
+    a = e.submit([3], max_tokens=2)
+    e.step()                                        # prompt -> first token on its way
+    e.step()                                        # first token (carried) -> second token on its way
+    assert a.generated_ids[-1] == -1 and a.awaits_last_token
+    assert e.scheduler.plan(list(e.running.values())) == []
+    assert e.step() is True and a.state is State.FINISHED and a.generated_ids == [4, 5]
+    assert e.step() is False and len(e.runner.calls) == 2
+    b = e.submit([7], max_tokens=5)
+    e.step()
+    e.step()
+    assert e.cancel(b.request_id) and b.state is State.CANCELLED and -1 not in b.generated_ids
+    assert e.step() is True and e.step() is False   # the token on its way finds its request gone
+    assert e.cache.used_pages == 0 and b.generated_ids == [8]
+    e.cache.assert_invariants()
+
+
+def test_carried_tokens_in_the_step_function(model_a):
+    """A decode step whose tokens come from a tensor (as the step before left them) gives the logits of the
+    same step with the tokens in hand; entries with and without a carried token side by side."""
+    from flexengine_b200.engine import StepEntry
+
+    def runner():
+        return Engine.from_model_dir(model_a, EngineConfig(model=model_a, device="cpu", dtype="float32", max_model_len=64,
+                                                           max_num_seqs=4, kv_block_size=16, kv_num_blocks=8),
+                                     ops=kernel_refs).runner
+    one, two = runner(), runner()
+    prompts = {"x": [3, 14, 15, 92], "y": [6, 5], "z": [9, 9, 9]}
+    for r in (one, two):
+        r.step([StepEntry(rid, ids, []) for rid, ids in prompts.items()])
+    want = one.step([StepEntry("x", [41], [0]), StepEntry("y", [7], [0]), StepEntry("z", [200, 11], [1])])
+    carried = torch.tensor([7, 99, 41], dtype=torch.int32)
+    got = two.step([StepEntry("x", [0], [0], carry=2), StepEntry("y", [0], [0], carry=0), StepEntry("z", [200, 11], [1])], carried)
+    torch.testing.assert_close(got, want, atol=0, rtol=0)
+    with pytest.raises(ValueError, match="carried"):
+        two.step([StepEntry("x", [0], [0], carry=5)], carried)
+    with pytest.raises(ValueError, match="carried"):
+        two.step([StepEntry("x", [0], [0], carry=0)])
