@@ -11,7 +11,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 from enum import Enum
-from queue import Queue
+from queue import SimpleQueue
 from time import monotonic, time
 
 
@@ -71,7 +71,7 @@ class Request:
     token_times: list = field(default_factory=list)
     error: str | None = None
     finish_reason: str | None = None
-    events: Queue = field(default_factory=Queue, repr=False)
+    events: SimpleQueue = field(default_factory=SimpleQueue, repr=False)
 
     def transition(self, new_state: State) -> None:
         if new_state == self.state:
@@ -86,7 +86,8 @@ class Request:
 
     @property
     def context_length(self) -> int:
-        return len(self.prompt_ids) + max(0, len(self.generated_ids) - 1)
+        n = len(self.generated_ids)
+        return len(self.prompt_ids) + (n - 1 if n else 0)
 
     @property
     def in_prefill(self) -> bool:

@@ -56,15 +56,17 @@ class Scheduler:
 
     def plan(self, requests: list) -> list:
         budget = self.token_budget
+        adaptive = self.policy == "adaptive"
         chunks = []
         for req in self.ordered(requests):
             if budget <= 0:
                 break
             if req.awaits_last_token:
                 continue
-            if req.in_prefill:
-                length = min(budget, req.context_length - req.cached_tokens)
-                if self.policy == "adaptive":
+            cached, context = req.cached_tokens, req.context_length
+            if cached < context:                          # still in its prompt (or recomputing)
+                length = min(budget, context - cached)
+                if adaptive:
                     length = min(length, self.prefill_chunk_size)
             elif req.generated_ids:
                 length = 1
@@ -73,9 +75,8 @@ class Scheduler:
             tokens = req.next_inputs(length)
             if not tokens:
                 continue
-            completes = req.cached_tokens + len(tokens) >= req.context_length
-            chunks.append(Chunk(req.request_id, tokens, req.cached_tokens,
-                                wants_logits=completes and not req.replaying))
+            completes = cached + len(tokens) >= context
+            chunks.append(Chunk(req.request_id, tokens, cached, wants_logits=completes and not req.replaying))
             budget -= len(tokens)
         assert sum(len(c.input_ids) for c in chunks) <= self.token_budget
         return chunks

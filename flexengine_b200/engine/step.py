@@ -111,8 +111,15 @@ class ModelRunner:
     def _reserve(self, entries) -> None:
         """Reserve for the whole batch or for none of it."""
         cache = self.cache
-        if all(e.request_id in cache.requests and
-               cache.reserved_tokens(e.request_id) >= cache.tokens_of(e.request_id) + len(e.tokens) for e in entries):
+        held, page_size, paged = cache.requests, cache.page_size, [gi for gi, _ in cache.paged]
+        for e in entries:
+            rc = held.get(e.request_id)
+            if rc is None:
+                break
+            need = rc.tokens + len(e.tokens)
+            if any(len(rc.tables[gi]) * page_size < need for gi in paged):
+                break
+        else:
             return                      # the scheduler reserved already
         made = []
         try:
@@ -191,20 +198,30 @@ class ModelRunner:
         appends, for entries whose token is still on the device, the row to fill and where it comes
         from (one pair per request with a fixed shape, row -1 where nothing is carried)."""
         cache = self.cache
-        starts = [cache.tokens_of(e.request_id) for e in entries]
+        held, ps = cache.requests, cache.page_size
+        caches = [held.get(e.request_id) for e in entries]
+        starts = [rc.tokens if rc else 0 for rc in caches]
         lengths = [len(e.tokens) for e in entries]
         pad = max(0, pad_to - len(entries))
-        token_ids = [t for e in entries for t in e.tokens] + [0] * pad
-        positions = [p for s, n in zip(starts, lengths) for p in range(s, s + n)] + [0] * pad
         all_lengths = lengths + [1] * pad
         all_starts = starts + [0] * pad
         R = len(all_lengths)
-        token_request = [r for r, n in enumerate(all_lengths) for _ in range(n)]
-        cu_q = [0]
-        for n in all_lengths:
-            cu_q.append(cu_q[-1] + n)
-        ctx_len = [s + n for s, n in zip(all_starts, all_lengths)]
-        state_slots = [cache.requests[e.request_id].state_slot for e in entries] + [-1] * pad
+        single = max(lengths) == 1                  # a decode step: one token a request
+        if single:
+            token_ids = [e.tokens[0] for e in entries] + [0] * pad
+            positions = all_starts
+            token_request = list(range(R))
+            cu_q = list(range(R + 1))
+            ctx_len = [s + 1 for s in all_starts]
+        else:
+            token_ids = [t for e in entries for t in e.tokens] + [0] * pad
+            positions = [p for s, n in zip(starts, lengths) for p in range(s, s + n)] + [0] * pad
+            token_request = [r for r, n in enumerate(all_lengths) for _ in range(n)]
+            cu_q = [0]
+            for n in all_lengths:
+                cu_q.append(cu_q[-1] + n)
+            ctx_len = [s + n for s, n in zip(all_starts, all_lengths)]
+        state_slots = [rc.state_slot for rc in caches] + [-1] * pad
         logit_rows = [cu_q[r] + w for r, e in enumerate(entries) for w in e.want]
         if pad_to:
             logit_rows = list(range(R))          # a fixed shape: every request's one row, padding too
@@ -217,14 +234,20 @@ class ModelRunner:
             if not isinstance(g, PagedGroup):
                 widths.append(0)
                 continue
+            refs = g.pool.refs
             slots = []
-            for e, s, n in zip(entries, starts, lengths):
-                slots.extend(cache.slot_mapping(e.request_id, gi, s, n))
+            for e, rc, s, n in zip(entries, caches, starts, lengths):
+                table = rc.tables[gi]
+                page = table[s // ps] if n == 1 and s < len(table) * ps else -1
+                if page >= 0 and refs[page] == 1:
+                    slots.append(page * ps + s % ps)       # the usual case, without a call
+                else:
+                    slots.extend(cache.slot_mapping(e.request_id, gi, s, n))      # checks and messages live there
             slots += [-1] * pad
-            width = max_pages or max(1, max(-(-c // cache.page_size) for c in ctx_len))
+            width = max_pages or max(1, max(-(-c // ps) for c in ctx_len))
             bt = np.full((R, width), -1, dtype=np.int32)
-            for r, e in enumerate(entries):
-                t = cache.table(e.request_id, gi)
+            for r, rc in enumerate(caches):
+                t = rc.tables[gi]
                 k = min(len(t), width)
                 bt[r, :k] = t[:k]
             bt[len(entries):, :] = 0
