@@ -366,6 +366,16 @@ def test_tcgen05_prefill_kernel_window_and_far_key(window, gen):
     ops().check_status(DEV)
 
 
+def test_tcgen05_prefill_kernel_long_contexts_go_round_its_rings(gen):
+    # dozens of key tiles per block: the four-stage key/value ring and both score buffers are used many times over;
+    # a portion far into its context, a long portion from position 0, and one under a window
+    got, want, _ = _attention_case(torch.bfloat16, 14, 2, 128, 16, [(2000, 700), (0, 1500)], 0, gen, tcgen05=True)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    got, want, _ = _attention_case(torch.bfloat16, 4, 1, 64, 32, [(3000, 333)], 1000, gen, tcgen05=True)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
+
+
 def test_tcgen05_prefill_kernel_moves_its_reference_point(gen):
     # scores that grow along the keys by far more than 2^8 make every row rescale its output in tensor memory
     nq, nkv, d, ps, n = 4, 2, 64, 16, 400

@@ -342,3 +342,23 @@ def test_carried_tokens_in_the_step_function(model_a):
         two.step([StepEntry("x", [0], [0], carry=5)], carried)
     with pytest.raises(ValueError, match="carried"):
         two.step([StepEntry("x", [0], [0], carry=0)])
+
+
+@pytest.mark.parametrize("overlap", [True, False])
+def test_end_of_sequence_with_the_real_model_under_tight_pages(model_a, overlap):
+    """An end-of-sequence id that greedy generation does produce: every request stops at its first
+    occurrence, whatever was launched beyond it, also when pages are so few that requests are preempted."""
+    config, weights = plain_model.read_model_folder(model_a)
+    prompts = [[3, 14, 15, 92, 65], list(range(40, 57)), [7, 200] * 16 + [1], [9], list(range(100, 130))]
+    plain = [plain_model.greedy_generate(config, weights, p, 10) for p in prompts]
+    eos = plain[1][4]
+    want = [t[:t.index(eos) + 1] if eos in t else t for t in plain]
+    assert any(len(w) < 10 for w in want)
+    for kw in (dict(), dict(pages=5, budget=48, max_num_seqs=3, max_model_len=64)):
+        base = real_engine(model_a, overlap_steps=overlap, **kw)
+        engine = Engine(base.config, base.runner, eos_token_ids=(eos,))
+        outs = engine.generate(prompts, max_tokens=10)
+        assert [o.token_ids for o in outs] == want
+        assert [o.finish_reason for o in outs] == ["stop" if w[-1] == eos else "length" for w in want]
+        assert engine.cache.used_pages == 0 and engine._in_flight is None
+        engine.cache.assert_invariants()
