@@ -327,7 +327,16 @@ constexpr int MAX_SPLITS_SHARED = 256;
 
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                       bf16* __restrict__ out, long long out_stride, const int* __restrict__ cu_q,
-                                      int nq, int d, int splits) {
+                                      int nq, int d, int splits, int requests, const void* __restrict__ upcoming,
+                                      long long upcoming_bytes) {
+    if ((int)blockIdx.y >= requests) {
+        // rows of blocks beyond the requests: the merge barely touches memory, so they start the matrix that the
+        // next kernel streams (the output projection) into L2
+        const long long workers = (long long)(gridDim.y - requests) * gridDim.x * blockDim.x;
+        prefetch_l2_share(upcoming, upcoming_bytes,
+                          ((long long)(blockIdx.y - requests) * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x, workers);
+        return;
+    }
     griddep_wait();
     griddep_launch_dependents();
     __shared__ float weight[MAX_SPLITS_SHARED];
@@ -510,11 +519,13 @@ extern "C" long long fe_paged_decode_scratch_bytes(int requests, int nq, int d, 
     return (long long)requests * nq * splits * (d + 1) * (long long)sizeof(float);
 }
 
-extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, void* scratch,
-                                   const void* kc, const void* vc, const int* block_table, int bt_stride,
-                                   const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
-                                   int num_pages, float scale, int window, int splits, int* status,
-                                   cudaStream_t stream) {
+// ``upcoming`` (may be null): memory that the kernel after this one will stream, ``upcoming_bytes`` of it; with more
+// than one split, extra blocks of the merge kernel ask for it to be brought into L2.
+extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, void* out, long long out_stride, void* scratch,
+                                            const void* kc, const void* vc, const int* block_table, int bt_stride,
+                                            const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
+                                            int num_pages, float scale, int window, int splits, const void* upcoming,
+                                            long long upcoming_bytes, int* status, cudaStream_t stream) {
     if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
     FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
     FE_REQUIRE(splits >= 1 && splits <= MAX_SPLITS_SHARED && requests >= 0,
@@ -539,11 +550,22 @@ extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out,
 #undef FE_DECODE
     if (fe_check_launch("paged_decode")) return 2;
     if (splits > 1) {
-        fe::launch(decode_combine_kernel, dim3(nq, requests), d >= 128 ? 128 : 64, 0, stream, 
-            part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits);
+        FE_REQUIRE(upcoming_bytes >= 0, "paged_decode: negative byte count");
+        const int extra = upcoming && upcoming_bytes > 0 ? 2 : 0;
+        fe::launch(decode_combine_kernel, dim3(nq, requests + extra), d >= 128 ? 128 : 64, 0, stream,
+            part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits, requests, upcoming, upcoming_bytes);
         return fe_check_launch("paged_decode combine");
     }
     return 0;
+}
+
+extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, void* scratch,
+                                   const void* kc, const void* vc, const int* block_table, int bt_stride,
+                                   const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
+                                   int num_pages, float scale, int window, int splits, int* status,
+                                   cudaStream_t stream) {
+    return fe_paged_decode_mma_upcoming(q, q_stride, out, out_stride, scratch, kc, vc, block_table, bt_stride, cu_q, q_start,
+                                        requests, nq, nkv, d, ps, num_pages, scale, window, splits, nullptr, 0, status, stream);
 }
 
 extern "C" int fe_paged_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride,

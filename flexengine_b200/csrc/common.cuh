@@ -103,6 +103,16 @@ template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float* v
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Worker ``w`` of ``workers`` threads asks for its share of the 128-byte lines of [base, base + bytes) to be brought
+// into L2.  Used by kernels that leave the memory system idle (a norm over a few rows, decode attention) to start
+// the weight matrix that the NEXT kernel streams: blocks beyond their own grid do nothing else.  A prefetch changes
+// no data, so it needs no ordering with other kernels.
+__device__ __forceinline__ void prefetch_l2_share(const void* base, long long bytes, long long w, long long workers) {
+    const char* p = static_cast<const char*>(base);
+    for (long long off = w * 128; off < bytes; off += workers * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off));
+}
+
 }  // namespace fe
 
 // Host side: the last error message of this thread, and a checked launch epilogue.

@@ -75,7 +75,13 @@ extern "C" int fe_carry_tokens(int* token_ids, const int* rows, const int* sourc
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const float* __restrict__ weight, float eps, T* __restrict__ out,
-                                   const int* __restrict__ rows, int H, int n_rows_total) {
+                                   const int* __restrict__ rows, int H, int n_rows_total, int n_out,
+                                   const void* __restrict__ upcoming, long long upcoming_bytes) {
+    if ((int)blockIdx.x >= n_out) {         // blocks beyond the rows: start the next kernel's weights into L2
+        prefetch_l2_share(upcoming, upcoming_bytes, (long long)(blockIdx.x - n_out) * blockDim.x + threadIdx.x,
+                          (long long)(gridDim.x - n_out) * blockDim.x);
+        return;
+    }
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float row[];
@@ -123,7 +129,13 @@ template <> struct Vec4<bf16> {
 template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const float* __restrict__ weight, float eps, T* __restrict__ out,
-                                       const int* __restrict__ rows, int H, int n_rows_total) {
+                                       const int* __restrict__ rows, int H, int n_rows_total, int n_out,
+                                       const void* __restrict__ upcoming, long long upcoming_bytes) {
+    if ((int)blockIdx.x >= n_out) {         // blocks beyond the rows: start the next kernel's weights into L2
+        prefetch_l2_share(upcoming, upcoming_bytes, (long long)(blockIdx.x - n_out) * blockDim.x + threadIdx.x,
+                          (long long)(gridDim.x - n_out) * blockDim.x);
+        return;
+    }
     griddep_wait();
     griddep_launch_dependents();
     extern __shared__ float row[];
@@ -154,9 +166,13 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
     }
 }
 
+constexpr int PREFETCH_BLOCKS = 64;
+
 template <typename T>
 static int launch_add_rmsnorm(float* residual, const void* delta, const float* weight, float eps, void* out,
-                              const int* rows, int n_out, int H, int n_rows_total, cudaStream_t stream) {
+                              const int* rows, int n_out, int H, int n_rows_total, const void* upcoming,
+                              long long upcoming_bytes, cudaStream_t stream) {
+    const int grid = n_out + (upcoming && upcoming_bytes > 0 ? PREFETCH_BLOCKS : 0);
     const size_t smem = (size_t)H * sizeof(float);
     const bool vec = H % 4 == 0;
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
@@ -165,28 +181,31 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const float* w
         if (smem > 48 * 1024)
             err = cudaFuncSetAttribute(add_rmsnorm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
-        fe::launch(add_rmsnorm_vec_kernel<T>, n_out, threads, smem, stream, residual, (const T*)delta, weight, eps, (T*)out,
-                                                                    rows, H, n_rows_total);
+        fe::launch(add_rmsnorm_vec_kernel<T>, grid, threads, smem, stream, residual, (const T*)delta, weight, eps, (T*)out,
+                   rows, H, n_rows_total, n_out, upcoming, upcoming_bytes);
     } else {
         if (smem > 48 * 1024)
             err = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         FE_REQUIRE(err == cudaSuccess, "add_rmsnorm: %s", cudaGetErrorString(err));
-        fe::launch(add_rmsnorm_kernel<T>, n_out, threads, smem, stream, residual, (const T*)delta, weight, eps, (T*)out, rows,
-                                                                H, n_rows_total);
+        fe::launch(add_rmsnorm_kernel<T>, grid, threads, smem, stream, residual, (const T*)delta, weight, eps, (T*)out, rows,
+                   H, n_rows_total, n_out, upcoming, upcoming_bytes);
     }
     return fe_check_launch("add_rmsnorm");
 }
 
+// ``upcoming`` (may be null): memory that the next kernel will stream, ``upcoming_bytes`` of it; extra blocks ask for
+// it to be brought into L2 while this kernel, which barely touches memory, runs.
 extern "C" int fe_add_rmsnorm(float* residual, const void* delta, const float* weight, float eps, void* out,
-                              const int* rows, int n_out, int H, int n_rows_total, int dtype, cudaStream_t stream) {
-    FE_REQUIRE(n_out >= 0 && H > 0, "add_rmsnorm: bad sizes n=%d H=%d", n_out, H);
+                              const int* rows, int n_out, int H, int n_rows_total, int dtype, const void* upcoming,
+                              long long upcoming_bytes, cudaStream_t stream) {
+    FE_REQUIRE(n_out >= 0 && H > 0 && upcoming_bytes >= 0, "add_rmsnorm: bad sizes n=%d H=%d", n_out, H);
     if (n_out == 0) return 0;
     FE_REQUIRE((size_t)H * sizeof(float) <= 200 * 1024,
                "add_rmsnorm: hidden size %d needs %zu bytes of shared memory (limit 204800)", H, (size_t)H * sizeof(float));
     if (dtype == FE_F32)
-        return launch_add_rmsnorm<float>(residual, delta, weight, eps, out, rows, n_out, H, n_rows_total, stream);
+        return launch_add_rmsnorm<float>(residual, delta, weight, eps, out, rows, n_out, H, n_rows_total, upcoming, upcoming_bytes, stream);
     if (dtype == FE_BF16)
-        return launch_add_rmsnorm<bf16>(residual, delta, weight, eps, out, rows, n_out, H, n_rows_total, stream);
+        return launch_add_rmsnorm<bf16>(residual, delta, weight, eps, out, rows, n_out, H, n_rows_total, upcoming, upcoming_bytes, stream);
     FE_REQUIRE(false, "add_rmsnorm: unknown dtype %d", dtype);
 }
 

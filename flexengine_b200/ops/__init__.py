@@ -104,10 +104,24 @@ def carry_tokens(token_ids, rows, sources, previous):
          _c_int(token_ids.numel()), _c_int(previous.numel()), _ptr(status_word(token_ids.device)), _stream())
 
 
-def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None):
+UPCOMING_MAX_ROWS = 16            # a step of this many tokens or fewer leaves the memory system idle between products
+UPCOMING_BYTES_MERGE = 16 << 20   # the same for the merge kernel of decode attention, ahead of the output projection
+UPCOMING_BYTES = 10 << 20         # how much of the next weight matrix a norm asks into L2 ahead of its product: what the
+                                  # memory system delivers while the norm runs (8-12 MB measured best on the 7B shape)
+
+
+def _upcoming(tensor, rows: int, limit: int = UPCOMING_BYTES):
+    """(pointer, bytes) of the start of ``tensor`` for a kernel's prefetching blocks; nothing for large steps."""
+    if tensor is None or rows > UPCOMING_MAX_ROWS or not tensor.is_cuda:
+        return _c_void_p(0), _c_ll(0)
+    return _ptr(tensor), _c_ll(min(tensor.numel() * tensor.element_size(), limit))
+
+
+def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=None):
     """Fused residual add + RMSNorm.  rows=None: residual += delta in place (all rows) and every row
     is normalised; rows given: only those rows are read (residual[rows] + delta[rows]), nothing is
-    written back."""
+    written back.  ``upcoming``: the weight matrix that the next kernel streams; in a decode step extra
+    blocks of this kernel, which barely touches memory, ask for its start to be brought into L2."""
     _need_cuda(residual, delta, weight, rows)
     T, H = residual.shape
     if residual.dtype != torch.float32 or weight.dtype != torch.float32:
@@ -117,7 +131,7 @@ def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None):
     n_out = T if rows is None else rows.numel()
     out = torch.empty((n_out, H), dtype=out_dtype, device=residual.device)
     _run(_core(), "fe_add_rmsnorm", _ptr(residual), _ptr(delta), _ptr(weight), _c_float(eps), _ptr(out), _ptr(rows),
-         _c_int(n_out), _c_int(H), _c_int(T), _c_int(_code(out_dtype)), _stream())
+         _c_int(n_out), _c_int(H), _c_int(T), _c_int(_code(out_dtype)), *_upcoming(upcoming, T), _stream())
     return out
 
 
@@ -333,18 +347,21 @@ def decode_splits(requests: int, nkv: int, max_ctx_len: int) -> int:
 
 
 def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
-                     scale, window, splits, out=None):
-    """Tensor-core decode attention (one token per request), keys split ``splits`` ways."""
+                     scale, window, splits, out=None, upcoming=None):
+    """Tensor-core decode attention (one token per request), keys split ``splits`` ways.  ``upcoming``: the
+    matrix that the next kernel streams (the output projection); extra blocks of the merge kernel ask for its
+    start to be brought into L2."""
     if out is None:
         out = torch.empty((requests, nq * d), dtype=torch.bfloat16, device=k_cache.device)
     lib = _bf16()
     lib.fe_paged_decode_scratch_bytes.restype = _c_ll
     need = lib.fe_paged_decode_scratch_bytes(_c_int(requests), _c_int(nq), _c_int(d), _c_int(splits))
     work = scratch(k_cache.device, need) if need else None
-    _run(lib, "fe_paged_decode_mma", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(work),
+    _run(lib, "fe_paged_decode_mma_upcoming", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(work),
          _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start),
          _c_int(requests), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _c_int(splits), _ptr(status_word(k_cache.device)), _stream())
+         _c_float(scale), _c_int(window), _c_int(splits), *_upcoming(upcoming, requests, UPCOMING_BYTES_MERGE),
+         _ptr(status_word(k_cache.device)), _stream())
     return out
 
 
@@ -376,7 +393,7 @@ def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_st
     return out
 
 
-def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window):
+def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None):
     """Causal grouped-query attention of the step's tokens over their requests' pages.
     qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d].
     float32 runs on CUDA cores (true 32-bit); bfloat16 on tensor cores: the split-KV decode
@@ -393,7 +410,7 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     if ctx.max_q_len == 1 and nq // nkv <= 16:
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
         return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
-                                nq, nkv, d, page_size, scale, window, splits)
+                                nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming)
     prefill = paged_prefill_tcgen05 if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d) else paged_prefill_mma
     return prefill(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
                    ctx.max_q_len, nq, nkv, d, page_size, scale, window)

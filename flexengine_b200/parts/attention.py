@@ -52,6 +52,9 @@ class AttentionMixer(Mixer):
         self.qkv_bias_ = tensors.get("qkv.bias")
         self.out_bias_ = tensors.get("out.bias")
 
+    def reads_first(self):
+        return self.qkv_weight
+
     def cache_need(self):
         return {"kind": "window" if self.window > 0 else "full", "kv_heads": self.num_kv_heads,
                 "head_dim": self.head_dim, "window": self.window}
@@ -76,7 +79,8 @@ class AttentionMixer(Mixer):
             qkv = ops.qkv_projection(h, self.qkv_weight, self.qkv_bias_, ctx.positions, inv_freq, rot, slot_mapping,
                                      k_cache, v_cache, nq, nkv, d, group.page_size)
         out = ops.paged_attention(qkv, k_cache, v_cache, group.block_table, ctx, self.num_heads,
-                                  self.num_kv_heads, self.head_dim, group.page_size, self.scale, self.window)
+                                  self.num_kv_heads, self.head_dim, group.page_size, self.scale, self.window,
+                                  upcoming=self.out_weight)
         return ops.linear(out, self.out_weight, self.out_bias_)
 
 

@@ -90,6 +90,11 @@ class Part:
                 raise ValueError(f"{type(self).__name__}.{name}: shape {tuple(tensors[name].shape)}, want {tuple(shape)}")
             setattr(self, name.replace(".", "_"), tensors[name])
 
+    def reads_first(self):
+        """The weight matrix this part streams first, or None.  A small kernel that runs before the part in
+        a decode step may ask for its start to be brought into L2 (``upcoming`` of the ops)."""
+        return None
+
 
 class Mixer(Part):
     def cache_need(self):

@@ -7,6 +7,8 @@ as ``pending`` and added inside the next norm kernel (fused residual add + norm)
 """
 from __future__ import annotations
 
+import inspect
+
 from .base import build_part, register_block
 
 
@@ -23,10 +25,21 @@ class PreNormBlock:
         return {name: getattr(self, name) for name in self.part_names}
 
     def forward(self, ctx, residual, pending, entry):
-        h = self.input_norm.forward(ctx, residual, pending)
+        # each norm is told which matrix comes next: in a decode step it starts that matrix into L2 meanwhile
+        h = _norm(self.input_norm, ctx, residual, pending, self.mixer.reads_first())
         mixed = self.mixer.forward(ctx, h, entry)
-        h = self.post_mixer_norm.forward(ctx, residual, mixed)
+        h = _norm(self.post_mixer_norm, ctx, residual, mixed, self.feed_forward.reads_first())
         return self.feed_forward.forward(ctx, h)
+
+
+def _norm(norm, ctx, residual, delta, upcoming):
+    """A norm of another kind need not know the hint: it is passed only to a ``forward`` that names it."""
+    takes = getattr(norm, "_takes_upcoming", None)
+    if takes is None:
+        takes = norm._takes_upcoming = "upcoming" in inspect.signature(norm.forward).parameters
+    if takes and upcoming is not None:
+        return norm.forward(ctx, residual, delta, upcoming=upcoming)
+    return norm.forward(ctx, residual, delta)
 
 
 register_block("prenorm", PreNormBlock)

@@ -20,6 +20,9 @@ class SwiGLU(FeedForward):
         h, i = self.hidden_size, self.intermediate_size
         return {"gate_up.weight": ((2 * i, h), "matrix"), "down.weight": ((h, i), "matrix")}
 
+    def reads_first(self):
+        return self.gate_up_weight
+
     def forward(self, ctx, h):
         act = ctx.ops.linear_swiglu(h, self.gate_up_weight, self.intermediate_size)
         return ctx.ops.linear(act, self.down_weight)

@@ -19,8 +19,8 @@ class RMSNorm(Norm):
     def parameter_shapes(self) -> dict:
         return {"weight": ((self.hidden_size,), "vector")}
 
-    def forward(self, ctx, residual, delta, rows=None):
-        return ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.dtype, rows)
+    def forward(self, ctx, residual, delta, rows=None, upcoming=None):
+        return ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.dtype, rows, upcoming=upcoming)
 
 
 register_norm("rmsnorm", RMSNorm)

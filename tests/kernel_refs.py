@@ -21,7 +21,7 @@ def carry_tokens(token_ids, rows, sources, previous):
     token_ids[rows[keep].long()] = previous[sources[keep].long()].to(token_ids.dtype)
 
 
-def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None):
+def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=None):
     if rows is None:
         if delta is not None:
             residual += delta.float()
@@ -81,7 +81,7 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
     return qkv
 
 
-def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window):
+def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_size, scale, window, upcoming=None):
     T = qkv.shape[0]
     out = torch.zeros(T, nq * d, dtype=qkv.dtype, device=qkv.device)
     q_all = qkv[:, :nq * d].float().view(T, nq, d)

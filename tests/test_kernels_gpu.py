@@ -65,6 +65,12 @@ def test_add_rmsnorm(dtype, T, H, gen):
         want_rows = kernel_refs.add_rmsnorm(r2, delta, weight, eps, dtype, rows)
         torch.testing.assert_close(got_rows.float(), want_rows.float(), **bar(dtype))
         torch.testing.assert_close(r1, keep, atol=0, rtol=0)             # rows mode leaves the residual alone
+        # the hint at the matrix that comes next changes nothing but what lies in L2 (odd sizes: the last line is partial)
+        nxt = rand((333, 77), torch.bfloat16, gen)
+        r3, r4 = residual.clone(), residual.clone()
+        hinted = ops().add_rmsnorm(r3, delta, weight, eps, dtype, upcoming=nxt)
+        torch.testing.assert_close(hinted, ops().add_rmsnorm(r4, delta, weight, eps, dtype), atol=0, rtol=0)
+        torch.testing.assert_close(r3, r4, atol=0, rtol=0)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 7, 5), (33, 130, 70), (64, 64, 16), (100, 301, 257), (3, 1000, 3584)])
