@@ -25,14 +25,14 @@ class AttentionMixer(Mixer):
             raise ValueError(f"head_dim={head_dim}: the attention kernels take head sizes in steps of 16 from 16 to 256")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = \
             int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
-        self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)
+        self.has_qkv_bias, self.has_out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         if position is None:
             position = PartSpec("none")
         if isinstance(position, dict):
             position = PartSpec(position["kind"], position.get("params", {}))
         self.position = build_part("position", position)
-        self.qkv_weight = self.qkv_bias_ = self.out_weight = self.out_bias_ = None
+        self.qkv_weight = self.qkv_bias = self.out_weight = self.out_bias = None      # bound by local name
 
     @property
     def qkv_width(self) -> int:
@@ -41,16 +41,11 @@ class AttentionMixer(Mixer):
     def parameter_shapes(self) -> dict:
         shapes = {"qkv.weight": ((self.qkv_width, self.hidden_size), "matrix"),
                   "out.weight": ((self.hidden_size, self.num_heads * self.head_dim), "matrix")}
-        if self.qkv_bias:
+        if self.has_qkv_bias:
             shapes["qkv.bias"] = ((self.qkv_width,), "vector")
-        if self.out_bias:
+        if self.has_out_bias:
             shapes["out.bias"] = ((self.hidden_size,), "vector")
         return shapes
-
-    def bind(self, tensors: dict) -> None:
-        super().bind(tensors)
-        self.qkv_bias_ = tensors.get("qkv.bias")
-        self.out_bias_ = tensors.get("out.bias")
 
     def reads_first(self):
         return self.qkv_weight
@@ -68,7 +63,7 @@ class AttentionMixer(Mixer):
         if self.position.applies_itself:
             # an encoding of its own: projection and bias, the encoding on the query and key heads in place,
             # then the keys and values to their cache slots
-            qkv = ops.linear(h, self.qkv_weight, self.qkv_bias_)
+            qkv = ops.linear(h, self.qkv_weight, self.qkv_bias)
             self.position.apply(ctx, qkv[:, :nq * d].view(-1, nq, d), qkv[:, nq * d:(nq + nkv) * d].view(-1, nkv, d))
             ops.qkv_bias_rope_cache(qkv, None, ctx.positions, None, 0, slot_mapping, k_cache, v_cache, nq, nkv, d,
                                     group.page_size)
@@ -76,12 +71,12 @@ class AttentionMixer(Mixer):
             # projection, bias, rotation and the cache write are one operation (one kernel in decode); a
             # run entry that only reads another entry's cache passes no slot mapping, so nothing is written
             inv_freq, rot = self.position.rotary_table(h.device) or (None, 0)
-            qkv = ops.qkv_projection(h, self.qkv_weight, self.qkv_bias_, ctx.positions, inv_freq, rot, slot_mapping,
+            qkv = ops.qkv_projection(h, self.qkv_weight, self.qkv_bias, ctx.positions, inv_freq, rot, slot_mapping,
                                      k_cache, v_cache, nq, nkv, d, group.page_size)
         out = ops.paged_attention(qkv, k_cache, v_cache, group.block_table, ctx, self.num_heads,
                                   self.num_kv_heads, self.head_dim, group.page_size, self.scale, self.window,
                                   upcoming=self.out_weight)
-        return ops.linear(out, self.out_weight, self.out_bias_)
+        return ops.linear(out, self.out_weight, self.out_bias)
 
 
 register_mixer("attention", AttentionMixer)

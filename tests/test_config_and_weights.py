@@ -129,7 +129,9 @@ def test_load_binds_by_name_and_keeps_precisions(folder):
     cfg, plan, model = load_model(folder, "bfloat16", "cpu")
     mixer = model.blocks[0].mixer
     assert mixer.qkv_weight.dtype == torch.bfloat16 and tuple(mixer.qkv_weight.shape) == (4 * 16 + 2 * 2 * 16, 64)
-    assert mixer.qkv_bias_.dtype == torch.float32                       # vectors are held in float32
+    assert mixer.qkv_bias.dtype == torch.float32                       # vectors are held in float32
+    assert mixer.has_qkv_bias and "qkv.bias" in mixer.parameter_shapes()  # the flag survives the binding of the tensor
+    assert model.weight_bytes() > 0
     assert model.lm_head.data_ptr() == model.embedding.data_ptr()        # tied
     reader = CheckpointReader(folder)
     q = reader.read("model.layers.0.self_attn.q_proj.weight")
