@@ -320,6 +320,7 @@ def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_sta
 
 
 _scratch: dict = {}
+_scratch_kept: list = []     # every scratch buffer ever handed out (see scratch())
 SM_COUNT = 148
 
 
@@ -328,12 +329,16 @@ def _bf16():
 
 
 def scratch(device, nbytes: int) -> torch.Tensor:
-    """Scratch memory of at least ``nbytes`` bytes on ``device`` (grown on demand, then kept)."""
+    """Scratch memory of at least ``nbytes`` bytes on ``device``, grown on demand.  A buffer that has been
+    handed out is never freed: a CUDA graph captured with it keeps its address, and replays it long after a
+    larger buffer has taken its place for new calls."""
     key = str(device)
     have = _scratch.get(key)
     if have is None or have.numel() < nbytes:
         with torch.inference_mode(False):
-            _scratch[key] = have = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            have = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch_kept.append(have)
+        _scratch[key] = have
     return have
 
 

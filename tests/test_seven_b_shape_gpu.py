@@ -64,6 +64,34 @@ def test_bfloat16_prefill_on_tcgen05_then_graph_decode(plain_weights):
         helpers.assert_logits_close(torch.cat(rows[j]), want[len(ids) - 31:], "bfloat16", f"7B-shape short request {j}")
 
 
+def test_a_graph_keeps_its_scratch_when_a_later_bucket_needs_more(plain_weights):
+    """The one-request graph is captured first; the eight-request graph then needs a larger scratch buffer for
+    the attention splits.  The first graph must still own valid memory when it is replayed afterwards, also
+    after the allocator has given every unused block back to the driver."""
+    from flexengine_b200 import ops
+    rng = random.Random(3)
+    ids = [helpers.random_prompt(rng, 70, SHAPE["vocab_size"]) for _ in range(8)]
+    runner = runner_for("bfloat16", 8 * 5 + 2, max_requests=8)
+    runner.enable_decode_graphs(8, 4096)
+    for j in range(8):
+        runner.step([StepEntry(f"r{j}", ids[j][:60], [])])
+    first = runner.step([StepEntry("r0", ids[0][60:61], [0])]).clone()                       # captures the graph of one request
+    small = ops.scratch(torch.device(DEV), 1)
+    all_eight = runner.step([StepEntry(f"r{j}", ids[j][60 + (j == 0):61 + (j == 0)], [0]) for j in range(8)]).clone()
+    assert ops.scratch(torch.device(DEV), 1).data_ptr() != small.data_ptr(), "this shape was chosen so that the scratch grows"
+    del small
+    torch.cuda.empty_cache()
+    junk = [torch.full((1 << 20,), 7, dtype=torch.uint8, device=DEV) for _ in range(8)]       # takes freed blocks, if any
+    again = runner.step([StepEntry("r0", ids[0][62:63], [0])]).clone()                       # replays the first graph
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+    assert runner.graph_replays == 3 and sorted(runner._graphs) == [1, 8]
+    want = plain_model.forward_logits(SHAPE, plain_weights, ids[0][:63]).cpu()
+    got = torch.cat([first, all_eight[0:1], again])
+    helpers.assert_logits_close(got, want[[60, 61, 62]], "bfloat16", "graph replayed after the scratch grew")
+    del junk
+
+
 def test_float32_path_at_the_seven_b_widths(plain_weights):
     rng = random.Random(2)
     ids = helpers.random_prompt(rng, 150, SHAPE["vocab_size"])
