@@ -203,3 +203,43 @@ def test_generate_command_line(model_dirs, capsys):
           "--temperature", "0.7", "--top-k", "10", "--seed", "5", "--num-blocks", "16", "--max-model-len", "128", "--cuda-graph"])
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert len(out["token_ids"]) == 4 and out["finish_reason"] in ("length", "stop")
+
+
+@pytest.mark.parametrize("policy", ["fcfs", "adaptive"])
+def test_engine_under_churn_matches_the_plain_implementation(model_dirs, policy):
+    """Requests arrive while others run, some are cancelled on the way, pages are so few that requests are
+    preempted and recomputed, batches shrink and grow across the graph buckets, steps overlap: every request that
+    finishes has the plain implementation's greedy tokens, every cancelled one a prefix of them."""
+    config, weights = plain_model.read_model_folder(model_dirs["A"], DEV)
+    rng = random.Random(21)
+    engine = engine_for(model_dirs["A"], "A", "float32", cuda_graph=True, max_num_seqs=6, pages=7, budget=40,
+                        max_model_len=96, scheduler_policy=policy, prefill_chunk_size=16)
+    todo = [(helpers.random_prompt(rng, rng.choice([1, 3, 9, 17, 30, 44]), 256), rng.randint(1, 12)) for _ in range(30)]
+    live, done, cancelled = [], [], []
+    while todo or live:
+        for _ in range(rng.randint(0, 2)):
+            if todo and len(engine.waiting) < 8:
+                prompt, n = todo.pop()
+                live.append((engine.submit(prompt, max_tokens=n), prompt, n))
+        if live and rng.random() < 0.08:
+            victim = live.pop(rng.randrange(len(live)))
+            engine.cancel(victim[0].request_id)
+            cancelled.append(victim)
+        progressed = engine.step()
+        assert engine.fault is None
+        still = []
+        for item in live:
+            (done if item[0].state.value == "finished" else still).append(item)
+        live = still
+        assert progressed or todo or not live
+    engine.drain()
+    assert engine.cache.used_pages == 0 and engine.preemption_count > 0 and len(done) >= 20
+    assert len(engine.runner._graphs) >= 3
+    for req, prompt, n in done:
+        assert req.generated_ids == plain_model.greedy_generate(config, weights, prompt, n)
+    for req, prompt, n in cancelled:
+        assert -1 not in req.generated_ids
+        assert req.generated_ids == plain_model.greedy_generate(config, weights, prompt, n)[:len(req.generated_ids)]
+    from flexengine_b200 import ops
+    ops.check_status(DEV)
+    engine.cache.assert_invariants()

@@ -362,3 +362,40 @@ def test_end_of_sequence_with_the_real_model_under_tight_pages(model_a, overlap)
         assert [o.finish_reason for o in outs] == ["stop" if w[-1] == eos else "length" for w in want]
         assert engine.cache.used_pages == 0 and engine._in_flight is None
         engine.cache.assert_invariants()
+
+
+@pytest.mark.parametrize("policy", ["fcfs", "decode_first"])
+def test_engine_under_churn_on_the_cpu(model_a, policy):
+    """Arrivals, cancellations and so few pages that requests are preempted, with steps overlapped: finished
+    requests have the plain implementation's greedy tokens, cancelled ones a prefix of them."""
+    import random
+    import helpers
+    config, weights = plain_model.read_model_folder(model_a)
+    rng = random.Random(21)
+    engine = real_engine(model_a, max_num_seqs=6, pages=7, budget=40, max_model_len=96, scheduler_policy=policy,
+                         prefill_chunk_size=16)
+    todo = [(helpers.random_prompt(rng, rng.choice([1, 3, 9, 17, 30, 44]), 256), rng.randint(1, 12)) for _ in range(24)]
+    live, done, cancelled = [], [], []
+    for _ in range(3000):
+        if not (todo or live):
+            break
+        for _ in range(rng.randint(0, 2)):
+            if todo and len(engine.waiting) < 8:
+                prompt, n = todo.pop()
+                live.append((engine.submit(prompt, max_tokens=n), prompt, n))
+        if live and rng.random() < 0.08:
+            victim = live.pop(rng.randrange(len(live)))
+            engine.cancel(victim[0].request_id)
+            cancelled.append(victim)
+        engine.step()
+        assert engine.fault is None
+        done += [item for item in live if item[0].state is State.FINISHED]
+        live = [item for item in live if item[0].state is not State.FINISHED]
+    engine.drain()
+    assert not todo and not live and engine.cache.used_pages == 0 and engine.preemption_count > 0 and cancelled
+    engine.cache.assert_invariants()
+    for req, prompt, n in done:
+        assert req.generated_ids == plain_model.greedy_generate(config, weights, prompt, n)
+    for req, prompt, n in cancelled:
+        assert -1 not in req.generated_ids
+        assert req.generated_ids == plain_model.greedy_generate(config, weights, prompt, n)[:len(req.generated_ids)]
