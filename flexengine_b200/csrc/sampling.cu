@@ -125,18 +125,34 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
             __syncthreads();
             const unsigned int prefix = s_prefix;
             const unsigned int mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i0 = (tid & ~31); i0 < V; i0 += RADIX_LOADS * THREADS) {
-                float v[RADIX_LOADS];
+            auto count = [&](float raw) {
+                const unsigned int key = ordered_key(sanitize(raw));
+                if ((key & mask) == prefix) atomicAdd(&warp_hist[tid >> 5][(key >> shift) & 0xffu], 1u);
+            };
+            if ((V & 3) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
+                // the order does not matter here: four logits per load, four loads on their way per thread
+                const float4* x4 = reinterpret_cast<const float4*>(x);
+                const int n4 = V >> 2;
+                for (int i = tid; i < n4; i += 4 * THREADS) {
+                    float4 part[4];
+                    bool in[4];
 #pragma unroll
-                for (int u = 0; u < RADIX_LOADS; ++u) {
-                    const int i = i0 + u * THREADS + (tid & 31);
-                    v[u] = i < V ? x[i] : 0.f;
+                    for (int u = 0; u < 4; ++u) {
+                        in[u] = i + u * THREADS < n4;
+                        part[u] = in[u] ? x4[i + u * THREADS] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (in[u]) { count(part[u].x); count(part[u].y); count(part[u].z); count(part[u].w); }
                 }
+            } else {
+                for (int i0 = tid; i0 < V; i0 += RADIX_LOADS * THREADS) {
+                    float v[RADIX_LOADS];
 #pragma unroll
-                for (int u = 0; u < RADIX_LOADS; ++u) {
-                    const unsigned int key = ordered_key(sanitize(v[u]));
-                    const bool hit = i0 + u * THREADS + (tid & 31) < V && (key & mask) == prefix;
-                    if (hit) atomicAdd(&warp_hist[tid >> 5][(key >> shift) & 0xffu], 1u);
+                    for (int u = 0; u < RADIX_LOADS; ++u) v[u] = i0 + u * THREADS < V ? x[i0 + u * THREADS] : 0.f;
+#pragma unroll
+                    for (int u = 0; u < RADIX_LOADS; ++u)
+                        if (i0 + u * THREADS < V) count(v[u]);
                 }
             }
             __syncthreads();
