@@ -13,6 +13,7 @@ COMMANDS = {
     "replay": ("flexengine_b200.engine.replay", "main", "Replay token ids step by step and write logits"),
     "random-model": ("flexengine_b200.cli.random_model", "main", "Write a model folder with seeded random weights"),
     "build": ("flexengine_b200.cli.build", "main", "Compile the CUDA kernel libraries"),
+    "bench": ("flexengine_b200.cli.bench", "main", "Decode and prefill throughput on the Qwen2.5-7B shape (one JSON line)"),
 }
 
 
