@@ -26,8 +26,13 @@ TINY_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden
               num_attention_heads=6, num_key_value_heads=3, head_dim=48, intermediate_size=112, vocab_size=301,
               rope_theta=50000.0, rms_norm_eps=3e-6, max_position_embeddings=1024, tie_word_embeddings=False,
               use_sliding_window=False, hidden_act="silu")
-PAGE_SIZE = {"A": 16, "B": 32, "C": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# head size 64 with long enough prompts: portions of 64 queries and more take the tcgen05 attention kernel in bfloat16
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=96,
+              num_attention_heads=8, num_key_value_heads=2, head_dim=64, intermediate_size=176, vocab_size=333,
+              rope_theta=200000.0, rms_norm_eps=2e-6, max_position_embeddings=2048, tie_word_embeddings=True,
+              use_sliding_window=False, hidden_act="silu")
+PAGE_SIZE = {"A": 16, "B": 32, "C": 16, "D": 8}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_dir(tmp_path_factory, name: str, seed: int = 7, stored: str = "bfloat16") -> str:

@@ -12,7 +12,7 @@ import torch
 import helpers
 import kernel_refs
 
-LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 40, 77, 130], "C": [3, 50, 64]}
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 40, 77, 130], "C": [3, 50, 64], "D": [300, 70, 150]}
 
 
 @pytest.fixture(scope="module")
@@ -63,7 +63,7 @@ def _run(model_dir, name, kind, dtype, device, ops):
 
 
 @pytest.mark.parametrize("kind", ["whole", "last_decoded", "portions", "mixed"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_step_on_cpu_with_reference_kernels(model_dirs, name, kind):
     _run(model_dirs[name], name, kind, "float32", "cpu", kernel_refs)
 
@@ -71,7 +71,7 @@ def test_step_on_cpu_with_reference_kernels(model_dirs, name, kind):
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("kind", ["whole", "last_decoded", "portions", "mixed"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_step_on_gpu(model_dirs, name, kind, dtype):
     _run(model_dirs[name], name, kind, dtype, "cuda:0", None)
 
