@@ -167,6 +167,7 @@ def linear(x, w, bias=None, out_float32=False):
 
 
 SKINNY_MAX_ROWS = 8          # beyond this the library product is as fast or faster
+SKINNY_QKV_MAX_ROWS = 8      # the fused projection + bias + rotation + cache write takes one 8-row tile of tokens
 EPI_BF16, EPI_F32, EPI_SWIGLU = 0, 1, 2
 
 
@@ -295,7 +296,8 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
     rotated this is ONE kernel (csrc/gemm_skinny.cu); otherwise the product and the fused
     bias/rotation/cache-write kernel."""
     _need_cuda(h, w, bias, positions, inv_freq, slot_mapping, k_cache, v_cache)
-    if (skinny_ok(h, w) and inv_freq is not None and rot == d and d % 16 == 0 and k_cache.dtype == torch.bfloat16
+    if (skinny_ok(h, w) and h.shape[0] <= SKINNY_QKV_MAX_ROWS and inv_freq is not None and rot == d and d % 16 == 0
+            and k_cache.dtype == torch.bfloat16
             and w.shape[0] == (nq + 2 * nkv) * d and (bias is None or bias.dtype == torch.float32)):
         T = h.shape[0]
         out = torch.empty((T, w.shape[0]), dtype=torch.bfloat16, device=h.device)
