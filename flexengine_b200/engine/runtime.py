@@ -110,6 +110,7 @@ class Engine:
         runner = ModelRunner(model, cache, ops=ops)
         if config.cuda_graph:
             runner.enable_decode_graphs(config.max_num_seqs, config.max_model_len)
+            runner.capture_decode_graphs()         # at start-up, not in the path of the first requests
         return cls(config, runner, tokenizer=tokenizer, eos_token_ids=plan.eos_token_ids)
 
     # ---- worker thread (a server would use it; generate() steps inline) --------------------------

@@ -312,6 +312,30 @@ class ModelRunner:
         self._graph_max_pages = -(-max_model_len // self.cache.page_size)
         self._graph_max_len = max_model_len
         self._graphs = {}
+        self._graph_pool = torch.cuda.graph_pool_handle()
+
+    def capture_decode_graphs(self) -> int:
+        """Capture every bucket now, with stand-in requests of one token, instead of at the first step that
+        needs it (a capture takes tens of milliseconds).  Buckets for which the pool has no pages to spare are
+        left for later.  Returns how many graphs exist afterwards."""
+        from ..cache.page_pool import CacheExhausted
+        replays = self.graph_replays
+        for bucket in self._graph_buckets:
+            if bucket in self._graphs:
+                continue
+            names = [f"__graph_capture_{i}" for i in range(bucket)]
+            try:
+                for name in names:
+                    self.cache.reserve(name, 1)
+                self._graph_step([StepEntry(name, [0], [0]) for name in names])
+            except CacheExhausted:
+                pass
+            finally:
+                for name in names:
+                    self.cache.free(name)
+        torch.cuda.synchronize(self.device)
+        self.graph_replays = replays               # the stand-in steps are not part of anyone's count
+        return len(self._graphs)
 
     def _graph_for(self, bucket: int, arrays: list, info: dict):
         """Capture the forward pass for ``bucket`` requests of one token (first use only)."""
@@ -332,9 +356,18 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(self.device)
         launches_before = getattr(self.ops, "launches", 0)
+        # Captured by hand on a stream of its own: the context manager of the library would also collect garbage
+        # and hand every cached block back to the driver at each capture (a tenth of a second, and slow allocations
+        # afterwards).  All buckets share one memory pool: only one of them runs at a time.
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph.capture_begin(pool=self._graph_pool, capture_error_mode="thread_local")
+            try:
+                logits = self.model.forward(ctx)
+            finally:
+                graph.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
         record = dict(graph=graph, static=static, logits=logits, total=total, views=dev,
                       launches=getattr(self.ops, "launches", 0) - launches_before)
         self._graphs[bucket] = record
