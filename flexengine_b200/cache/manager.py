@@ -72,6 +72,7 @@ class CacheManager:
         self.requests: dict[str, RequestCache] = {}
         self.free_state_slots = list(range(self.max_requests - 1, -1, -1))
         self._paged = [(gi, g) for gi, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
+        self._windowed = [(gi, g) for gi, g in self._paged if g.spec.kind == "window" and g.spec.window > 0]
 
     # --- sizes -----------------------------------------------------------------------------
     @property
@@ -151,13 +152,13 @@ class CacheManager:
         """``count`` more tokens of the request are now in the cache; pages that a window has
         passed are given back."""
         rc = self.requests[request_id]
-        if rc.tokens + count > self.reserved_tokens(request_id):
-            raise IndexError("KV slots not reserved")
-        rc.tokens += count
-        for gi, g in self.paged:
+        target = rc.tokens + count
+        for gi, _ in self._paged:
+            if len(rc.tables[gi]) * self.page_size < target:
+                raise IndexError("KV slots not reserved")
+        rc.tokens = target
+        for gi, g in self._windowed:
             w = g.spec.window
-            if g.spec.kind != "window" or w <= 0:
-                continue
             # the next query sits at position >= rc.tokens and sees keys t > position - w
             first_needed = rc.tokens - w + 1
             table = rc.tables[gi]

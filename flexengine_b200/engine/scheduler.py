@@ -14,7 +14,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from time import monotonic
 
-from .request import Request
+from .request import PENDING, Request
 
 
 @dataclass
@@ -61,22 +61,26 @@ class Scheduler:
         for req in self.ordered(requests):
             if budget <= 0:
                 break
-            if req.awaits_last_token:
-                continue
-            cached, context = req.cached_tokens, req.context_length
+            # the request's properties, spelled out: this loop runs for every running request at every step
+            generated = req.generated_ids
+            produced = len(generated)
+            if produced and generated[-1] == PENDING and produced >= req.max_tokens:
+                continue                                  # its last token is on its way
+            cached = req.cached_tokens
+            context = len(req.prompt_ids) + (produced - 1 if produced else 0)
             if cached < context:                          # still in its prompt (or recomputing)
                 length = min(budget, context - cached)
                 if adaptive:
                     length = min(length, self.prefill_chunk_size)
-            elif req.generated_ids:
-                length = 1
+                tokens = req.next_inputs(length)
+            elif produced:
+                tokens = [generated[-1]]
             else:
                 continue
-            tokens = req.next_inputs(length)
             if not tokens:
                 continue
             completes = cached + len(tokens) >= context
-            chunks.append(Chunk(req.request_id, tokens, cached, wants_logits=completes and not req.replaying))
+            chunks.append(Chunk(req.request_id, tokens, cached, completes and not req.replaying))
             budget -= len(tokens)
         assert sum(len(c.input_ids) for c in chunks) <= self.token_budget
         return chunks
