@@ -90,6 +90,8 @@ class Engine:
         self.preemption_count = 0
         self.output_tokens = 0
         self._in_flight: _InFlight | None = None
+        self._pinned: list = []
+        self._pinned_at = 0
         self.trace = TraceWriter(config.trace_dir)
         self.trace.metadata(config)
 
@@ -355,7 +357,13 @@ class Engine:
         assert [r.request_id for r, _ in places] == [r.request_id for r in sampled]
         record = _InFlight(places, tokens, index={r.request_id: i for i, (r, _) in enumerate(places)})
         if tokens is not None and tokens.device.type == "cuda":
-            record.host = torch.empty(tokens.shape, dtype=tokens.dtype, pin_memory=True)
+            # one of a few pinned buffers kept for good (two records are alive at most): allocating pinned memory
+            # at every step costs a call into the driver now and then
+            if not self._pinned or self._pinned[0].numel() < tokens.numel():
+                self._pinned = [torch.empty(max(tokens.numel(), self.config.max_num_seqs), dtype=tokens.dtype, pin_memory=True)
+                                for _ in range(4)]
+            self._pinned_at = (self._pinned_at + 1) % len(self._pinned)
+            record.host = self._pinned[self._pinned_at][:tokens.numel()]
             record.host.copy_(tokens, non_blocking=True)
             record.event = torch.cuda.Event()
             record.event.record()
