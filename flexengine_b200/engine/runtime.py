@@ -354,6 +354,12 @@ class Engine:
                 continue
             req.generated_ids.append(PENDING)
             places.append((req, len(req.generated_ids) - 1))
+            if len(req.generated_ids) >= req.max_tokens:
+                # the token on its way is its last whatever it is: its seat and its pages serve others from the next
+                # step on (what that step writes there comes after this one on the stream); the request itself ends
+                # when the token has been read
+                self.cache.free(req.request_id)
+                self.running.pop(req.request_id, None)
         assert [r.request_id for r, _ in places] == [r.request_id for r in sampled]
         record = _InFlight(places, tokens, index={r.request_id: i for i, (r, _) in enumerate(places)})
         if tokens is not None and tokens.device.type == "cuda":

@@ -399,3 +399,18 @@ def test_engine_under_churn_on_the_cpu(model_a, policy):
     for req, prompt, n in cancelled:
         assert -1 not in req.generated_ids
         assert req.generated_ids == plain_model.greedy_generate(config, weights, prompt, n)[:len(req.generated_ids)]
+
+
+def test_overlapped_steps_plan_the_same_batches_when_requests_end_by_length():
+    """A request whose last token is on its way gives up its seat and its pages at once, so that requests which
+    wait are admitted in the same step as without overlap: the same batches, step for step."""
+    calls = {}
+    for overlap in (False, True):
+        e = counting_engine(overlap_steps=overlap, max_num_seqs=2)
+        requests = [e.submit([1 + i], max_tokens=2 + i % 3) for i in range(7)]       # tokens stay below the end-of-sequence id
+        run_until_done(e, requests)
+        e.drain()
+        calls[overlap] = [[(n, w) for _, n, w in call] for call in e.runner.calls]
+        assert e.cache.used_pages == 0 and [r.finish_reason for r in requests] == ["length"] * 7
+        e.cache.assert_invariants()
+    assert calls[True] == calls[False]
