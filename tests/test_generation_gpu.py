@@ -205,6 +205,27 @@ def test_generate_command_line(model_dirs, capsys):
     assert len(out["token_ids"]) == 4 and out["finish_reason"] in ("length", "stop")
 
 
+def test_generate_command_line_with_text_prompts(model_dirs, tmp_path, capsys):
+    """A folder with ``tokenizer.json``: text in, text out; the words of this tokenizer are ``<id>``."""
+    import json
+    import shutil
+    tokenizers = pytest.importorskip("tokenizers")
+    from flexengine_b200.cli import main
+    folder = tmp_path / "with_tokenizer"
+    shutil.copytree(model_dirs["A"], folder)
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel({f"<{t}>": t for t in range(256)}, unk_token="<0>"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.WhitespaceSplit()
+    tok.decoder = tokenizers.decoders.Fuse()
+    tok.save(str(folder / "tokenizer.json"))
+    main(["generate", "--model", str(folder), "--prompt", "<3> <14> <15> <92> <65>", "--max-tokens", "6", "--dtype", "float32",
+          "--num-blocks", "16", "--max-model-len", "128"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    config, weights = plain_model.read_model_folder(model_dirs["A"], DEV)
+    want = plain_model.greedy_generate(config, weights, [3, 14, 15, 92, 65], 6)
+    assert out["token_ids"] == want and out["prompt_tokens"] == 5
+    assert out["text"].replace(" ", "") == "".join(f"<{t}>" for t in want if t != 255)
+
+
 @pytest.mark.parametrize("policy", ["fcfs", "adaptive"])
 def test_engine_under_churn_matches_the_plain_implementation(model_dirs, policy):
     """Requests arrive while others run, some are cancelled on the way, pages are so few that requests are
