@@ -107,19 +107,19 @@ __device__ __forceinline__ void copy_rows(bf16* ks, bf16* vs, const KvSource& sr
     }
 }
 
-// One warp, 32 keys: s = Q K^T, mask (only where ``masked``), online softmax in float with the
-// running maximum kept in log2 units, o += P V.  ``ks``/``vs`` point at the first of the 32 rows.
+// One warp, KEYS keys (32, or 16 when two warps share a tile): s = Q K^T, mask (only where ``masked``), online
+// softmax in float with the running maximum kept in log2 units, o += P V.  ``ks``/``vs`` point at the first row.
 // pos0/pos1 and lo0/lo1: last and first visible key of the queries in rows g and g + 8.
 // UPPER = false: rows 8..15 of the tile are padding and their softmax is skipped.
-template <int DMAX, bool UPPER>
+template <int DMAX, bool UPPER, int KEYS = TK>
 __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, const unsigned (*qfrag)[4],
                                              float (*o)[4], float* m, float* l, int first_key, int d,
                                              float scale_log2, int pos0, int pos1, int lo0, int lo1, bool masked) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     const int mat = lane >> 3, mrow = lane & 7;
-    float s[TK / 8][4];
+    float s[KEYS / 8][4];
 #pragma unroll
-    for (int j = 0; j < TK / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int j = 0; j < KEYS / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     {
         // row = jp*16 + (mat>>1)*8 + mrow, 16-byte chunk = ksx*2 + (mat&1)
         const bf16* kbase = ks + ((mat >> 1) * 8 + mrow) * pitch<DMAX>() + (mat & 1) * 8;
@@ -127,7 +127,7 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
         for (int ksx = 0; ksx < DMAX / 16; ++ksx) {
             if (ksx * 16 < d) {
 #pragma unroll
-                for (int jp = 0; jp < TK / 16; ++jp) {
+                for (int jp = 0; jp < KEYS / 16; ++jp) {
                     unsigned r0, r1, r2, r3;
                     ldmatrix_x4(r0, r1, r2, r3, kbase + jp * 16 * pitch<DMAX>() + ksx * 16);
                     mma16816(s[jp * 2], qfrag[ksx], r0, r1);
@@ -138,7 +138,7 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
     }
     if (masked) {
 #pragma unroll
-        for (int j = 0; j < TK / 8; ++j) {
+        for (int j = 0; j < KEYS / 8; ++j) {
 #pragma unroll
             for (int e = 0; e < (UPPER ? 4 : 2); ++e) {
                 const int key = first_key + j * 8 + 2 * t + (e & 1);
@@ -149,7 +149,7 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
     }
     float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
 #pragma unroll
-    for (int j = 0; j < TK / 8; ++j) {
+    for (int j = 0; j < KEYS / 8; ++j) {
         mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
         if (UPPER) mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
     }
@@ -171,7 +171,7 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
     }
     float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-    for (int j = 0; j < TK / 8; ++j) {
+    for (int j = 0; j < KEYS / 8; ++j) {
         s[j][0] = ex2(fmaf(s[j][0], scale_log2, -ms0)); s[j][1] = ex2(fmaf(s[j][1], scale_log2, -ms0));
         sum0 += s[j][0] + s[j][1];
         if (UPPER) {
@@ -184,7 +184,7 @@ __device__ __forceinline__ void compute_tile(const bf16* ks, const bf16* vs, con
         // row = kk*16 + (mat&1)*8 + mrow, 16-byte chunk = np*2 + (mat>>1)
         const bf16* vbase = vs + ((mat & 1) * 8 + mrow) * pitch<DMAX>() + (mat >> 1) * 8;
 #pragma unroll
-        for (int kk = 0; kk < TK / 16; ++kk) {
+        for (int kk = 0; kk < KEYS / 16; ++kk) {
             unsigned a[4];
             a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
             a[1] = UPPER ? pack_bf16(s[2 * kk][2], s[2 * kk][3]) : 0u;
@@ -221,12 +221,17 @@ __device__ __forceinline__ void load_q(unsigned (*qfrag)[4], const bf16* src0, c
 }
 
 // ---------------------------------------------------------------------------------------------
-// decode: grid (splits, nkv, requests), one warp, a ring of 32-key stages.  Every request brings
-// exactly one token.
+// decode: grid (splits, nkv, requests), two warps, a ring of 32-key stages.  Every request brings
+// exactly one token.  A warp's stream of dependent instructions, not memory, bounds what one warp
+// gets through, and shared memory bounds how many blocks fit an SM: so the two warps of a block
+// share every stage they load, each takes 16 of its 32 keys with running statistics of its own,
+// and the two results are merged once at the end.
 constexpr int DECODE_STAGES = 2;
+constexpr int DECODE_WARPS = 2;
+constexpr int DECODE_KEYS = TK / DECODE_WARPS;   // keys of a stage per warp
 
 template <int DMAX, bool UPPER>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(DECODE_WARPS * 32)
 paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                     float* __restrict__ part_o, float* __restrict__ part_lse, const bf16* __restrict__ kc,
                     const bf16* __restrict__ vc, const int* __restrict__ block_table, int bt_stride,
@@ -238,8 +243,9 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     __shared__ long long offs[TK];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     constexpr int TILE = TK * pitch<DMAX>();         // elements per K (or V) stage
+    constexpr int THREADS = DECODE_WARPS * 32;
     const int split = blockIdx.x, splits = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int lane = threadIdx.x, g = lane >> 2, t = lane & 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = nq / nkv;
     const int tok = cu_q[b];
     const int pos = q_start[b];
@@ -251,11 +257,11 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
 
     KvSource src{kc, vc, block_table + (size_t)b * bt_stride, nkv, kvh, d, ps, (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1,
                  num_pages};
-    // lane r looks up key r of a tile; then the warp copies the 32 rows
+    // thread r < 32 looks up key r of a tile; then the block copies the 32 rows
     if (n_tiles > 0) {
-        offs[lane] = row_offset(src, t_begin * TK + lane, lo, pos, status);
-        __syncwarp();
-        copy_rows<DMAX, 32, TK>(smem, smem + TILE, src, offs);
+        if (threadIdx.x < TK) offs[threadIdx.x] = row_offset(src, t_begin * TK + threadIdx.x, lo, pos, status);
+        __syncthreads();
+        copy_rows<DMAX, THREADS, TK>(smem, smem + TILE, src, offs);
     }
     cp_async_commit();
 
@@ -269,29 +275,55 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
 
     for (int it = 0; it < n_tiles; ++it) {
-        // the other stage is free (the warp finished tile it - 1): start tile it + 1 into it
+        // the other stage is free (both warps finished tile it - 1): start tile it + 1 into it
         long long next = -1;
-        if (it + 1 < n_tiles) next = row_offset(src, (t_begin + it + 1) * TK + lane, lo, pos, status);
-        cp_async_wait<0>();                          // tile ``it`` has landed
-        __syncwarp();
+        if (it + 1 < n_tiles && threadIdx.x < TK) next = row_offset(src, (t_begin + it + 1) * TK + threadIdx.x, lo, pos, status);
+        cp_async_wait<0>();                          // this thread's part of tile ``it`` has landed
+        __syncthreads();                             // ... and everyone else's; the offsets of tile ``it`` have been read
         if (it + 1 < n_tiles) {
-            offs[lane] = next;
-            __syncwarp();
+            if (threadIdx.x < TK) offs[threadIdx.x] = next;
+            __syncthreads();
             bf16* st = smem + ((it + 1) & 1) * 2 * TILE;
-            copy_rows<DMAX, 32, TK>(st, st + TILE, src, offs);
+            copy_rows<DMAX, THREADS, TK>(st, st + TILE, src, offs);
         }
         cp_async_commit();
-        const bf16* sp = smem + (it & 1) * 2 * TILE;
-        const int first = (t_begin + it) * TK;
-        compute_tile<DMAX, UPPER>(sp, sp + TILE, qfrag, o, m, l, first, d, scale_log2, pos, pos, lo, lo,
-                                  first + TK - 1 > pos || first < lo);
-        __syncwarp();
+        const bf16* sp = smem + (it & 1) * 2 * TILE + warp * DECODE_KEYS * pitch<DMAX>();
+        const int first = (t_begin + it) * TK + warp * DECODE_KEYS;
+        compute_tile<DMAX, UPPER, DECODE_KEYS>(sp, sp + TILE, qfrag, o, m, l, first, d, scale_log2, pos, pos, lo, lo,
+                                               first + DECODE_KEYS - 1 > pos || first < lo);
     }
     cp_async_wait<0>();
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+    // the second warp hands its running statistics and output to the first through the stages' memory (free now),
+    // thread to thread: both hold the same rows and columns
+    __syncthreads();
+    float* hand = reinterpret_cast<float*>(smem_raw);                 // [DMAX / 2 + 4][32] floats
+    if (warp == 1) {
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) hand[(n * 4 + e) * 32 + lane] = o[n][e];
+        hand[(DMAX / 2) * 32 + lane] = m[0]; hand[(DMAX / 2 + 1) * 32 + lane] = m[1];
+        hand[(DMAX / 2 + 2) * 32 + lane] = l[0]; hand[(DMAX / 2 + 3) * 32 + lane] = l[1];
+    }
+    __syncthreads();
+    if (warp == 1) return;
+#pragma unroll
+    for (int i = 0; i < (UPPER ? 2 : 1); ++i) {
+        const float m1 = hand[(DMAX / 2 + i) * 32 + lane], l1 = hand[(DMAX / 2 + 2 + i) * 32 + lane];
+        const float mn = fmaxf(m[i], m1);
+        const float a0 = mn == -CUDART_INF_F ? 0.f : ex2(m[i] - mn), a1 = mn == -CUDART_INF_F ? 0.f : ex2(m1 - mn);
+        l[i] = l[i] * a0 + l1 * a1;
+        m[i] = mn;
+#pragma unroll
+        for (int n = 0; n < DMAX / 8; ++n) {
+            o[n][2 * i] = o[n][2 * i] * a0 + hand[(n * 4 + 2 * i) * 32 + lane] * a1;
+            o[n][2 * i + 1] = o[n][2 * i + 1] * a0 + hand[(n * 4 + 2 * i + 1) * 32 + lane] * a1;
+        }
     }
 #pragma unroll
     for (int i = 0; i < (UPPER ? 2 : 1); ++i) {
@@ -539,7 +571,7 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
 #define FE_DECODE(DMAX, UPPER)                                                                                    \
     do {                                                                                                          \
         if (allow_smem(paged_decode_kernel<DMAX, UPPER>, decode_smem<DMAX>(), "paged_decode")) return 1;          \
-        fe::launch(paged_decode_kernel<DMAX, UPPER>, grid, 32, decode_smem<DMAX>(), stream,                               \
+        fe::launch(paged_decode_kernel<DMAX, UPPER>, grid, DECODE_WARPS * 32, decode_smem<DMAX>(), stream,                               \
             (const bf16*)q, q_stride, (bf16*)out, out_stride, part_o, part_lse, (const bf16*)kc, (const bf16*)vc, \
             block_table, bt_stride, cu_q, q_start, nq, nkv, d, ps, num_pages, scale_log2, window, status);        \
     } while (0)
