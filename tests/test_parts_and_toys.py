@@ -469,3 +469,111 @@ def test_routed_toy_with_its_own_feed_forward_position_encoding_and_norm(routed_
     h = torch.randn(50, ROUTED["width"], device=device)
     chosen = (h @ block.feed_forward.router_weight.float().T).topk(2, dim=-1).indices.sort(-1).values
     assert len({tuple(c) for c in chosen.tolist()}) > 1
+
+
+# ---- a third toy: full attention in one layer, a sliding window in the other, each with pages of its own ----------
+@dataclass(frozen=True)
+class WindowedConfig:
+    vocab_size: int
+    hidden_size: int
+    window: int
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(int(data["vocab_size"]), int(data["hidden_size"]), int(data["window"]))
+
+
+WINDOWED = {"architectures": ["ToyWindowedForCausalLM"], "vocab_size": 211, "hidden_size": 128, "window": 70}
+WQ, WKV, WD, WI = 8, 2, 64, 192           # head size 64 and group 4: portions of 64 queries take the tcgen05 kernel
+
+
+def build_windowed_plan(cfg: WindowedConfig) -> ModelPlan:
+    h, v = cfg.hidden_size, cfg.vocab_size
+    norm = PartSpec("rmsnorm", {"hidden_size": h, "eps": 1e-5})
+    position = PartSpec("rope_half_split", {"head_dim": WD, "theta": 30000.0})
+    def attention(window):
+        return PartSpec("attention", {"hidden_size": h, "num_heads": WQ, "num_kv_heads": WKV, "head_dim": WD,
+                                      "window": window, "position": position})
+    ffn = PartSpec("swiglu", {"hidden_size": h, "intermediate_size": WI})
+    layers = [LayerSpec(attention(0), ffn, norm), LayerSpec(attention(cfg.window), ffn, norm)]
+    run = [RunEntry(0, 0, 0, True), RunEntry(1, 1, 0, True)]
+    groups = [CacheGroupSpec("all_keys", "full", slots=1, kv_heads=WKV, head_dim=WD),
+              CacheGroupSpec("recent_keys", "window", slots=1, kv_heads=WKV, head_dim=WD, window=cfg.window)]
+    def src(name, *shape):
+        return WeightSource(name, tuple(shape))
+    bindings = [WeightBinding(("embedding", "weight"), (src("embed.weight", v, h),)),
+                WeightBinding(("lm_head", "weight"), alias_of=("embedding", "weight")),
+                WeightBinding(("final_norm", "weight"), (src("norm.weight", h),), kind="vector")]
+    for l in range(2):
+        p = f"layers.{l}."
+        bindings += [WeightBinding(("layer", l, "input_norm", "weight"), (src(p + "norm1.weight", h),), kind="vector"),
+                     WeightBinding(("layer", l, "post_mixer_norm", "weight"), (src(p + "norm2.weight", h),), kind="vector"),
+                     WeightBinding(("layer", l, "feed_forward", "gate_up.weight"), (src(p + "gate.weight", WI, h), src(p + "up.weight", WI, h))),
+                     WeightBinding(("layer", l, "feed_forward", "down.weight"), (src(p + "down.weight", h, WI),)),
+                     WeightBinding(("layer", l, "mixer", "qkv.weight"), (src(p + "q.weight", WQ * WD, h), src(p + "k.weight", WKV * WD, h), src(p + "v.weight", WKV * WD, h))),
+                     WeightBinding(("layer", l, "mixer", "qkv.bias"), (src(p + "q.bias", WQ * WD), src(p + "k.bias", WKV * WD), src(p + "v.bias", WKV * WD)), kind="vector"),
+                     WeightBinding(("layer", l, "mixer", "out.weight"), (src(p + "o.weight", h, WQ * WD),))]
+    init = {"default": ("normal", 0.0, 0.08), "suffix": {"norm1.weight": ("normal", 1.0, 0.05), "norm2.weight": ("normal", 1.0, 0.05),
+                                                           "norm.weight": ("normal", 1.0, 0.05)}}
+    return ModelPlan("ToyWindowedForCausalLM", v, h, layers, run, groups, norm, bindings, init=init)
+
+
+register_architecture("ToyWindowedForCausalLM", WindowedConfig, build_windowed_plan)
+
+
+def windowed_reference(w: dict, ids) -> torch.Tensor:
+    T = len(ids)
+    pos = torch.arange(T)
+    inv = plain_model.rope_inverse_frequencies(WD, 30000.0, "cpu")
+    x = w["embed.weight"].float()[torch.tensor(ids)]
+    for l, window in enumerate((0, WINDOWED["window"])):
+        p = f"layers.{l}."
+        names = {"q_proj.weight": w[p + "q.weight"], "k_proj.weight": w[p + "k.weight"], "v_proj.weight": w[p + "v.weight"],
+                 "q_proj.bias": w[p + "q.bias"], "k_proj.bias": w[p + "k.bias"], "v_proj.bias": w[p + "v.bias"],
+                 "o_proj.weight": w[p + "o.weight"]}
+        x = x + plain_model.attention_block(plain_model.rms_norm(x, w[p + "norm1.weight"].float(), 1e-5), names, "", pos, WQ, WKV, WD, inv, window)
+        x = x + plain_model.swiglu_mlp(plain_model.rms_norm(x, w[p + "norm2.weight"].float(), 1e-5), w[p + "gate.weight"].float(),
+                                       w[p + "up.weight"].float(), w[p + "down.weight"].float())
+    return plain_model.rms_norm(x, w["norm.weight"].float(), 1e-5) @ w["embed.weight"].float().T
+
+
+@pytest.mark.parametrize("device,dtype", [pytest.param("cpu", "float32", id="cpu"),
+                                          pytest.param("cuda:0", "float32", id="gpu-float32", marks=pytest.mark.gpu),
+                                          pytest.param("cuda:0", "bfloat16", id="gpu-bfloat16", marks=pytest.mark.gpu)])
+def test_windowed_toy_gives_pages_back_and_matches_the_plain_implementation(tmp_path_factory, device, dtype):
+    """Long prompts in portions (some of 64 queries and more: the tcgen05 kernel in bfloat16), decoded tails, mixed
+    batches; the window group holds only the pages its window still reaches."""
+    folder = str(tmp_path_factory.mktemp("windowed"))
+    write_random_model(WINDOWED, folder, seed=6, dtype="bfloat16")
+    _cfg, plan, model = load_model(folder, dtype, device)
+    _, w = plain_model.read_model_folder(folder)
+    rng = random.Random(4)
+    requests = {f"w{i}": helpers.random_prompt(rng, n, WINDOWED["vocab_size"]) for i, n in enumerate([330, 90, 201])}
+    steps = helpers.steps_mixed(requests, rng, live=3, decode_tail=5)
+    torch_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    cache = CacheManager(plan.cache_groups, helpers.peak_pages(steps, 8), 8, 3, torch_dtype, device)
+    runner = ModelRunner(model, cache, ops=provider(device))
+    window_pool = cache.groups[1].pool
+    most_window_pages = 0
+    results = {}
+    for entries, ended in steps:
+        out = runner.step([StepEntry(rid, toks, want) for rid, toks, want in entries])
+        row = 0
+        for rid, toks, want in entries:
+            start = cache.tokens_of(rid) - len(toks)
+            for place in want:
+                results[(rid, start + place)] = out[row].float().cpu()
+                row += 1
+        most_window_pages = max(most_window_pages, window_pool.used_pages)
+        for rid in ended:
+            runner.finish(rid)
+    assert cache.used_pages == 0
+    # three live requests never hold more than their windows' worth (and the portion in flight) in the window group
+    assert most_window_pages < helpers.peak_pages(steps, 8)
+    for rid, ids in requests.items():
+        want = windowed_reference(w, ids)
+        got = torch.stack([results[(rid, p)] for p in range(len(ids))])
+        helpers.assert_logits_close(got, want, dtype, f"windowed {rid}")
+    if device != "cpu":
+        from flexengine_b200 import ops
+        ops.check_status(device)
