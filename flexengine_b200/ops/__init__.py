@@ -345,11 +345,15 @@ def scratch(device, nbytes: int) -> torch.Tensor:
 
 
 def decode_splits(requests: int, nkv: int, max_ctx_len: int) -> int:
-    """How many ways the keys of a request are split in decode: about one round of resident blocks
-    (six one-warp blocks fit an SM), but no split shorter than two tiles of 32 keys."""
+    """How many ways the keys of a request are split in decode.  Between half a round and one round of resident
+    blocks (six blocks fit an SM): towards the full round when a split still has eight tiles of 32 keys or more to
+    walk (long contexts), towards the half when splits would get short and the merge dominate; never a split
+    shorter than two tiles."""
     tiles = max(1, -(-max_ctx_len // 32))
     pairs = max(1, requests * nkv)
-    want = max(1, (6 * SM_COUNT + pairs // 2) // pairs)
+    most = max(1, (6 * SM_COUNT + pairs // 2) // pairs)
+    least = max(1, (3 * SM_COUNT + pairs // 2) // pairs)
+    want = min(most, max(least, tiles // 8))
     return int(max(1, min(want, tiles // 2)))
 
 
