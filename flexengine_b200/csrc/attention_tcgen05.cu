@@ -233,7 +233,8 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
                              const bf16* __restrict__ kc, const bf16* __restrict__ vc,
                              const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
                              const int* __restrict__ q_start, int nq, int nkv, int ps, int num_pages, float scale_log2,
-                             int window, int* __restrict__ status) {
+                             int window, int splits, float* __restrict__ part_o, float* __restrict__ part_lse,
+                             int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long kv_full[KV_STAGES], kv_empty[KV_STAGES], s_ready[2][2], p_ready[2][2], pv_done[2], o_final[2];
     __shared__ long long offs[KEYS];
@@ -254,7 +255,9 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     const int G = nq / nkv;
     const int tok0 = cu_q[r], n_q = cu_q[r + 1] - tok0;
     const int rows = n_q * G;
-    const int m_pair = (gridDim.x - 1 - blockIdx.x) * 2 * ROWS;     // the rows with the most keys first
+    // blockIdx.x = (pair of row tiles, split of its keys); the rows with the most keys first
+    const int split = blockIdx.x % splits;
+    const int m_pair = (gridDim.x / splits - 1 - blockIdx.x / splits) * 2 * ROWS;
     if (m_pair >= rows) return;
     const bool two = m_pair + ROWS < rows;                          // else the second row tile is empty and left out
     const int start = q_start[r];
@@ -262,7 +265,16 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
     const int qi_first = m_pair / G, qi_last = min(n_q - 1, (m_pair + (two ? 2 : 1) * ROWS - 1) / G);
     const int hi = start + qi_last;
     const int lo = window > 0 ? max(0, start + qi_first - window + 1) : 0;
-    const int t_begin = lo / KEYS, n_tiles = hi / KEYS - t_begin + 1;
+    // this block's share of the key tiles; with one split, all of them
+    const int all_tiles = hi / KEYS - lo / KEYS + 1, per_split = (all_tiles + splits - 1) / splits;
+    const int t_begin = lo / KEYS + split * per_split, n_tiles = min(per_split, all_tiles - split * per_split);
+    if (n_tiles <= 0) {
+        // nothing left for this split: its rows say so, and the merge reads nothing more of them
+        const int m = m_pair + tid;
+        if (tid < 2 * ROWS && m < rows)
+            part_lse[((size_t)(tok0 + m / G) * nq + kvh * G + m % G) * splits + split] = -CUDART_INF_F;
+        return;
+    }
 
     if (tid == 0) {
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 128); mbar_init(&kv_empty[s], two ? 2 : 1); }
@@ -447,7 +459,9 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
             mbar_arrive(&p_ready[ti][j & 1]);
         }
         if (ok) ok = __all_sync(FULL, mbar_wait(&o_final[ti], 0, &give_up));
-        if (ok) {
+        // partial results are staged where keys and values lay: the other row tile must have read its last ones
+        if (ok && splits > 1 && two) ok = __all_sync(FULL, mbar_wait(&o_final[ti ^ 1], 0, &give_up));
+        if (ok && splits == 1) {
             tc_fence_after();
             const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
             // O through shared memory (this row tile's Q is no longer read), so that the warp writes whole rows:
@@ -472,6 +486,32 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
                 const uint4 v = *reinterpret_cast<const uint4*>(stage + row_in_warp * (2 * D) + ((c ^ (row_in_warp & 7)) << 4));
                 if (to >= 0) *reinterpret_cast<uint4*>(out + to + c * 8) = v;
             }
+        } else if (ok) {
+            // this split's share of the row: O / sum in float32 and the logarithm of the sum, for the merge
+            tc_fence_after();
+            const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
+            const long long slot = valid ? ((long long)(tok0 + qi) * nq + head) * splits + split : -1;
+            if (valid) part_lse[slot] = row_sum > 0.f ? m_ref + log2f(row_sum) : -CUDART_INF_F;
+            float* stage = reinterpret_cast<float*>(kv_s + (size_t)ti * (ROWS * 4 * D) + (warp & 3) * (32 * 4 * D));
+#pragma unroll 1
+            for (int c = 0; c < D; c += 32) {
+                float v[32];
+                tmem_load32(o_addr + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(stage + lane * D + ((((c + i) >> 2) ^ (lane & 7)) << 2)) =
+                        make_float4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
+            }
+            __syncwarp();
+            constexpr int CPR4 = D / 4, RPI4 = 32 / CPR4;       // 16-byte chunks of a float32 row; rows per instruction
+            const int c = lane % CPR4;
+#pragma unroll 4
+            for (int k = 0; k < CPR4; ++k) {
+                const int row_in_warp = k * RPI4 + lane / CPR4;
+                const long long to = __shfl_sync(FULL, slot, row_in_warp);
+                const float4 v = *reinterpret_cast<const float4*>(stage + row_in_warp * D + ((c ^ (row_in_warp & 7)) << 2));
+                if (to >= 0) *reinterpret_cast<float4*>(part_o + to * D + c * 4) = v;
+            }
         }
     }
     tc_fence_before();
@@ -481,40 +521,98 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
 }
 
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int MAX_SPLITS = 32;                       // the merge keeps one split's weight per lane
+
+// One warp per (token, head): the splits' shares of the row, weighted by what each split saw of the softmax sum.
+template <int D>
+__global__ void __launch_bounds__(128)
+prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
+                     long long out_stride, int nq, int splits, long long items) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int lane = threadIdx.x & 31;
+    const long long token = item / nq;
+    const int head = (int)(item % nq);
+    const float lse = lane < splits ? part_lse[item * splits + lane] : -CUDART_INF_F;
+    const float mx = warp_max(lse);
+    const float w = mx == -CUDART_INF_F ? 0.f : exp2f(lse - mx);       // 0 for a split that saw no key of this row
+    const float total = warp_sum(w);
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    constexpr int CHUNKS = D / 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+        const float ws = __shfl_sync(0xffffffffu, w, s);
+        if (ws == 0.f || lane >= CHUNKS) continue;                     // such a split's share was never written
+        const float4 v = *reinterpret_cast<const float4*>(part_o + (item * splits + s) * D + lane * 4);
+        acc.x += ws * v.x; acc.y += ws * v.y; acc.z += ws * v.z; acc.w += ws * v.w;
+    }
+    if (lane < CHUNKS) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const unsigned*>(&lo);
+        packed.y = *reinterpret_cast<const unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(out + token * out_stride + (long long)head * D + lane * 4) = packed;
+    }
+}
 
 template <int D>
 int launch(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
            const int* block_table, int bt_stride, const int* cu_q, const int* q_start, int requests, int max_q_len, int nq,
-           int nkv, int ps, int num_pages, float scale, int window, int* status, cudaStream_t stream) {
+           int nkv, int ps, int num_pages, float scale, int window, int splits, float* scratch, long long total_tokens,
+           int* status, cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * (2 * Q_BLOCK + 2 * KV_STAGES * KV_BLOCK) + 1024;
     const cudaError_t err = cudaFuncSetAttribute(paged_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FE_REQUIRE(err == cudaSuccess, "paged_prefill_tcgen05: %s", cudaGetErrorString(err));
     const long long rows = (long long)max_q_len * (nq / nkv);
-    const long long tiles = (rows + 2 * ROWS - 1) / (2 * ROWS);
+    const long long tiles = (rows + 2 * ROWS - 1) / (2 * ROWS) * splits;
     FE_REQUIRE(tiles <= 2147483647LL && nkv <= 65535 && requests <= 65535, "paged_prefill_tcgen05: grid too large");
+    // partial results: [token, head, split, D] float32, then [token, head, split] logarithms of the sums
+    float* part_o = splits > 1 ? scratch : nullptr;
+    float* part_lse = splits > 1 ? scratch + (size_t)total_tokens * nq * splits * D : nullptr;
     fe::launch(paged_prefill_tcgen05_kernel<D>, dim3((unsigned)tiles, nkv, requests), THREADS, smem, stream, (const bf16*)q, q_stride,
                (bf16*)out, out_stride, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, nq, nkv, ps,
-               num_pages, scale * LOG2E, window, status);
-    return fe_check_launch("paged_prefill_tcgen05");
+               num_pages, scale * LOG2E, window, splits, part_o, part_lse, status);
+    if (fe_check_launch("paged_prefill_tcgen05")) return 1;
+    if (splits > 1) {
+        const long long items = total_tokens * nq;
+        FE_REQUIRE((items + 3) / 4 <= 2147483647LL, "paged_prefill_tcgen05: merge grid too large");
+        fe::launch(prefill_merge_kernel<D>, dim3((unsigned)((items + 3) / 4)), 128, 0, stream, (const float*)part_o,
+                   (const float*)part_lse, (bf16*)out, out_stride, nq, splits, items);
+        return fe_check_launch("paged_prefill_tcgen05 merge");
+    }
+    return 0;
 }
 
 }  // namespace
 
-// Head sizes 64 and 128, bfloat16.  Other arguments as fe_paged_prefill_mma.
+// Head sizes 64 and 128, bfloat16.  Other arguments as fe_paged_prefill_mma.  With ``splits`` > 1 (at most 32) the key
+// tiles of every pair of row tiles are shared out over that many blocks, whose results a second kernel merges:
+// for short portions late in a long context, which alone would keep few blocks busy.  ``scratch`` then holds
+// ``fe_paged_prefill_tcgen05_scratch_floats`` floats; ``total_tokens`` is the number of rows of q.
+extern "C" long long fe_paged_prefill_tcgen05_scratch_floats(long long total_tokens, int nq, int d, int splits) {
+    return splits > 1 ? total_tokens * nq * splits * (d + 1) : 0;
+}
+
 extern "C" int fe_paged_prefill_tcgen05(const void* q, long long q_stride, void* out, long long out_stride, const void* kc,
                                         const void* vc, const int* block_table, int bt_stride, const int* cu_q,
                                         const int* q_start, int requests, int max_q_len, int nq, int nkv, int d, int ps,
-                                        int num_pages, float scale, int window, int* status, cudaStream_t stream) {
+                                        int num_pages, float scale, int window, int splits, void* scratch,
+                                        long long total_tokens, int* status, cudaStream_t stream) {
     FE_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "paged_prefill_tcgen05: bad head counts %d/%d", nq, nkv);
     FE_REQUIRE(d == 64 || d == 128, "paged_prefill_tcgen05: head size %d; this kernel takes 64 and 128", d);
     FE_REQUIRE(ps > 0 && num_pages > 0 && window >= 0, "paged_prefill_tcgen05: bad page size, page count or window");
     FE_REQUIRE(q_stride % 8 == 0 && out_stride % 8 == 0 && (((size_t)q | (size_t)out | (size_t)kc | (size_t)vc) & 15) == 0,
                "paged_prefill_tcgen05: rows must start on 16-byte boundaries");
     FE_REQUIRE(requests >= 0 && max_q_len >= 0, "paged_prefill_tcgen05: bad request count or length");
+    FE_REQUIRE(splits >= 1 && splits <= MAX_SPLITS, "paged_prefill_tcgen05: %d splits; 1 to %d", splits, MAX_SPLITS);
+    FE_REQUIRE(splits == 1 || (scratch != nullptr && ((size_t)scratch & 15) == 0 && total_tokens > 0),
+               "paged_prefill_tcgen05: splits need scratch memory on a 16-byte boundary and the number of tokens");
     if (requests == 0 || max_q_len == 0) return 0;
     if (d == 64)
         return launch<64>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start, requests, max_q_len, nq, nkv,
-                          ps, num_pages, scale, window, status, stream);
+                          ps, num_pages, scale, window, splits, (float*)scratch, total_tokens, status, stream);
     return launch<128>(q, q_stride, out, out_stride, kc, vc, block_table, bt_stride, cu_q, q_start, requests, max_q_len, nq, nkv, ps,
-                       num_pages, scale, window, status, stream);
+                       num_pages, scale, window, splits, (float*)scratch, total_tokens, status, stream);
 }

@@ -388,19 +388,41 @@ def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start,
 
 
 def tcgen05_attention_ok(max_q_len, nq, nkv, d):
-    """The tcgen05 prefill kernel takes head sizes 64 and 128 and pays off once the longest portion fills
-    a block's 256 (query, head) rows; shorter portions go to the mma.sync kernel with its 64-row blocks."""
-    return d in (64, 128) and max_q_len * (nq // nkv) >= 256
+    """The tcgen05 prefill kernel takes head sizes 64 and 128, portions of any length: measured against the
+    mma.sync kernel it is level on portions of a few tokens and ahead everywhere else, the more the longer the
+    context.  Other head sizes go to the mma.sync kernel."""
+    return d in (64, 128)
+
+
+PREFILL_MAX_SPLITS = 32
+PREFILL_TILES_PER_SPLIT = 4      # a split walks at least this many tiles of 64 keys
+PREFILL_SPLIT_FROM_TILES = 16    # shorter walks are over before a second kernel could merge them
+
+
+def prefill_splits(lengths, starts, nq, nkv, window=0) -> int:
+    """Into how many blocks the tcgen05 prefill kernel shares out the keys of each pair of row tiles.  One block
+    a multiprocessor is resident; a short portion late in a long context fills few of them, and each walks the whole
+    context, so its keys are split until the blocks about cover the device."""
+    group = nq // nkv
+    blocks = nkv * sum(-(-n * group // 256) for n in lengths)
+    longest = max(min(s + n, window + n) if window > 0 else s + n for s, n in zip(starts, lengths))
+    tiles = -(-longest // 64)
+    if tiles < PREFILL_SPLIT_FROM_TILES:
+        return 1
+    return int(max(1, min(SM_COUNT // max(1, blocks), tiles // PREFILL_TILES_PER_SPLIT, PREFILL_MAX_SPLITS)))
 
 
 def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
-                          page_size, scale, window):
-    """Prefill attention on tcgen05 tensor cores: 128 (query, head) rows a block, head sizes 64 and 128."""
+                          page_size, scale, window, splits=1):
+    """Prefill attention on tcgen05 tensor cores: 128 (query, head) rows a block, head sizes 64 and 128.
+    ``splits`` > 1 shares the keys of each pair of row tiles out over that many blocks and merges their results."""
     out = torch.empty((T, nq * d), dtype=torch.bfloat16, device=k_cache.device)
+    part = scratch(k_cache.device, 4 * T * nq * splits * (d + 1)) if splits > 1 else None
     _run(_bf16(), "fe_paged_prefill_tcgen05", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _ptr(status_word(k_cache.device)), _stream())
+         _c_float(scale), _c_int(window), _c_int(splits), _ptr(part) if part is not None else ctypes.c_void_p(0),
+         _c_ll(T), _ptr(status_word(k_cache.device)), _stream())
     return out
 
 
@@ -422,9 +444,13 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
         return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
                                 nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming)
-    prefill = paged_prefill_tcgen05 if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d) else paged_prefill_mma
-    return prefill(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
-                   ctx.max_q_len, nq, nkv, d, page_size, scale, window)
+    if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d):
+        lengths = getattr(ctx, "host_lengths", None)
+        splits = prefill_splits(lengths, ctx.host_starts, nq, nkv, window) if lengths else 1
+        return paged_prefill_tcgen05(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
+                                     ctx.max_q_len, nq, nkv, d, page_size, scale, window, splits)
+    return paged_prefill_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
+                             ctx.max_q_len, nq, nkv, d, page_size, scale, window)
 
 
 def sample(logits, temperature, top_k, seed, draw):

@@ -274,6 +274,7 @@ def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered
         cu.append(cu[-1] + n)
     ctx = types.SimpleNamespace(
         max_q_len=max(n for _, n in chunks), max_ctx_len=max(lens),
+        host_starts=[s for s, _ in chunks], host_lengths=[n for _, n in chunks],
         cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
         q_start=torch.tensor([s for s, _ in chunks], dtype=torch.int32, device=DEV),
         token_request=torch.tensor([r for r, (_, n) in enumerate(chunks) for _ in range(n)], dtype=torch.int32, device=DEV))
@@ -283,9 +284,9 @@ def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered
     if splits is not None:            # the split-KV decode kernel, asked for by name
         got = ops().paged_decode_mma(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, R, nq, nkv, d, ps, scale,
                                      window, splits)
-    elif tcgen05:                     # the tcgen05 prefill kernel, asked for by name
+    elif tcgen05:                     # the tcgen05 prefill kernel, asked for by name; an integer > 1 splits the keys
         got = ops().paged_prefill_tcgen05(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, T, R, ctx.max_q_len, nq,
-                                          nkv, d, ps, scale, window)
+                                          nkv, d, ps, scale, window, splits=int(tcgen05))
     elif simt:
         got = ops().paged_attention_simt(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, ctx.token_request, T,
                                          nq, nkv, d, ps, scale, window)
@@ -391,11 +392,52 @@ def test_tcgen05_prefill_kernel_moves_its_reference_point(gen):
         _attention_case(torch.bfloat16, 4, 2, 32, 16, [(0, 300)], 0, gen, tcgen05=True)
 
 
-def test_dispatch_takes_the_tcgen05_kernel_for_long_portions(gen):
-    assert ops().tcgen05_attention_ok(300, 4, 2, 128) and not ops().tcgen05_attention_ok(100, 4, 2, 128)
+@pytest.mark.parametrize("splits", [2, 3, 8, 32])
+def test_tcgen05_prefill_kernel_with_split_keys(splits, gen):
+    # the keys of every pair of row tiles shared out over several blocks and merged: splits that get nothing (short
+    # contexts), that lie wholly behind a row's position, and a decisive key in the first, a middle and the last split
+    chunks = [(0, 1), (1000, 3), (0, 300), (2000, 70), (63, 2), (500, 129)]
+    for nq, nkv, d, ps in [(28, 4, 128, 16), (5, 1, 64, 8)]:
+        got, want, _ = _attention_case(torch.bfloat16, nq, nkv, d, ps, chunks, 0, gen, tcgen05=splits)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    for far in (0, 63, 64, 1027, 2040, 2100):
+        got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(2048, 60), (3, 2)], 0, gen, boost=far, tcgen05=splits)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+        assert float((got[59].float() - 10.0).abs().max()) < 0.5
+    for window in (1, 65, 700):
+        got, want, _ = _attention_case(torch.bfloat16, 8, 2, 128, 16, [(1500, 40), (10, 5)], window, gen, tcgen05=splits)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    # each split moves its own reference point, and the merge weighs splits whose sums differ by hundreds of powers of two
+    got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(900, 100), (37, 200)], 0, gen, tcgen05=splits, ramp=0.6)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
+    with pytest.raises(RuntimeError, match="splits"):
+        _attention_case(torch.bfloat16, 4, 2, 64, 16, [(0, 300)], 0, gen, tcgen05=33)
+
+
+def test_prefill_splits_follow_the_work():
+    split = ops().prefill_splits
+    assert split([2048], [0], 28, 4) == 1                      # a whole prompt fills the device by itself
+    assert split([64], [2048], 28, 4) == 8                     # 33 tiles: no split shorter than four
+    assert split([64], [8192], 28, 4) == 18                    # eight blocks without splits; one round of the device
+    assert split([2], [100000], 28, 4) == 32                   # never more than the merge takes
+    assert split([64], [0], 28, 4) == 1 and split([40, 1, 1], [10, 20, 30], 4, 2) == 1
+    assert split([16], [900], 28, 4) == 1 and split([16], [1010], 28, 4) == 4      # from sixteen tiles on
+    assert split([64], [8192], 28, 4, window=256) == 1         # a window bounds what any row walks
+    assert split([1] * 4 + [128], [500] * 4 + [4000], 28, 4) == 4      # decoded tokens beside a portion
+
+
+def test_dispatch_takes_the_tcgen05_kernel_for_its_head_sizes(gen):
+    assert ops().tcgen05_attention_ok(300, 4, 2, 128) and ops().tcgen05_attention_ok(2, 4, 2, 64)
     assert not ops().tcgen05_attention_ok(4096, 4, 2, 96)
     got, want, _ = _attention_case(torch.bfloat16, 4, 2, 128, 16, [(0, 300), (100, 1), (7, 2)], 0, gen)
     torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    # a short portion late in a long context beside decoded tokens: the dispatch splits its keys
+    chunks = [(3000, 48), (700, 1), (0, 2)]
+    assert ops().prefill_splits([n for _, n in chunks], [s for s, _ in chunks], 14, 2) > 1
+    got, want, _ = _attention_case(torch.bfloat16, 14, 2, 128, 16, chunks, 0, gen)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
 
 
 def test_bfloat16_on_cuda_cores_for_shapes_the_tensor_core_kernels_refuse(gen):

@@ -78,6 +78,38 @@ def test_step_on_gpu(model_dirs, name, kind, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_portions_late_in_a_long_context(model_dirs, dtype):
+    """A prompt of 1,700 tokens in portions of 2 to 90 while a second request decodes beside it: from 1,024 keys on
+    the bfloat16 prefill attention shares the keys of a portion out over several blocks and merges them, with the
+    decoded token as a one-row portion in the same launch."""
+    rng = random.Random(9)
+    vocab = helpers.CONFIGS["D"]["vocab_size"]
+    long_ids, side_ids = helpers.random_prompt(rng, 1700, vocab), helpers.random_prompt(rng, 1150, vocab)
+    steps = [([("side", side_ids[:1090], [1089])], [])]
+    at, side_at = 0, 1090
+    while at < len(long_ids):
+        n = min(rng.choice((2, 17, 48, 64, 90)), len(long_ids) - at)
+        entries = [("long", long_ids[at:at + n], list(range(n)))]
+        if side_at < len(side_ids):
+            entries.append(("side", side_ids[side_at:side_at + 1], [0]))
+            side_at += 1
+        steps.append((entries, []))
+        at += n
+    steps[-1] = (steps[-1][0], ["long", "side"])
+    page = helpers.PAGE_SIZE["D"]
+    runner = helpers.make_runner(model_dirs["D"], dtype, "cuda:0", helpers.peak_pages(steps, page) + 1, page)
+    results = helpers.run_steps(runner, steps)
+    assert runner.cache.used_pages == 0
+    for rid, ids, first in (("long", long_ids, 0), ("side", side_ids[:side_at], 1089)):
+        want = helpers.plain_logits(model_dirs["D"], ids, "cuda:0")
+        got = torch.stack([results[(rid, p)] for p in range(first, len(ids))])
+        helpers.assert_logits_close(got, want[first:], dtype, f"long context, {rid}, {dtype}")
+    from flexengine_b200 import ops as cuda_ops
+    cuda_ops.check_status("cuda:0")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_weights_stored_in_32_bit(tmp_path_factory, dtype):
     """A checkpoint stored in float32: in bfloat16 mode its matrices stay 32-bit (their products run
     through the float32 GEMM), activations and cache are bfloat16; both modes match the plain implementation."""
