@@ -210,7 +210,45 @@ def run_ours(args):
             runner.finish(rid)
         return ms, launches, ctx
 
+    # ---- a mixed step: a portion of a prompt late in its context beside decoded tokens ----------------
+    MIXED_PORTION, MIXED_AFTER, MIXED_DECODERS = 128, 3072, 7
+
+    def mixed(count, hook=None):
+        """``count`` timed steps of 128 prompt tokens after 3,072 cached ones beside seven decoded tokens at 2,048.
+        The cache holds zeros for what came before: the step's time does not depend on values."""
+        rids = [f"m{i}" for i in range(MIXED_DECODERS)]
+        for rid in rids:
+            cache.reserve(rid, PROMPT_LEN)
+            cache.commit(rid, PROMPT_LEN)
+        portion = torch.randint(0, vocab, (MIXED_PORTION,), generator=gen).tolist()
+
+        def one(i):
+            cache.reserve("long", MIXED_AFTER)
+            cache.commit("long", MIXED_AFTER)
+            entries = [StepEntry("long", portion, [])] + [StepEntry(rid, [i + 1], [0]) for rid in rids]
+            greedy(runner.step(entries))
+            runner.finish("long")
+        for w in range(3):
+            one(w)
+        if hook:
+            return hook(one)
+        ms, _ = timed(one, count)
+        for rid in rids:
+            runner.finish(rid)
+        return ms
+
     warmup = max(args.warmup, 3)
+    if args.profile == "mixed":
+        def capture(one):
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            one(5)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        mixed(0, capture)
+        sampler.stop()
+        print(json.dumps({"profiled": args.profile}))
+        return 0
     if args.profile:
         # for a profiler started with --profile-from-start off: only this region is captured
         if args.profile == "prefill":
@@ -241,6 +279,8 @@ def run_ours(args):
         for b in (1, 64):
             pms, _, _ = decode(b, max(4, args.steps // 2), 3)
             points[f"decode_b{b}"] = b / (pms / 1e3)
+        # tokens a second of a step that brings 128 prompt tokens after 3,072 beside seven decoded tokens
+        points["mixed_128_after_3072_plus_7"] = (MIXED_PORTION + MIXED_DECODERS) / (mixed(8) / 1e3)
 
     # ---- the same through the Python entry point: host tokens in, sampled tokens out, every step -----
     del runner, cache
@@ -312,8 +352,8 @@ def main():
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     p.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
-    p.add_argument("--profile", choices=["decode", "prefill"], default=None,
-                   help="run one decode step or one prefill between cudaProfilerStart/Stop and exit")
+    p.add_argument("--profile", choices=["decode", "prefill", "mixed"], default=None,
+                   help="run one decode step, one prefill or one mixed step between cudaProfilerStart/Stop and exit")
     p.add_argument("--cuda-graph", action=argparse.BooleanOptionalAction, default=True)
     args = p.parse_args()
     if args.gpus != 1:

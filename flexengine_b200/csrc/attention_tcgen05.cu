@@ -78,6 +78,9 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.com
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void loader_barrier() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
 // Shared-memory descriptors, 128-byte swizzle.  K-major: rows 128 bytes apart, 8-row groups 1024
@@ -237,7 +240,7 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
                              int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long kv_full[KV_STAGES], kv_empty[KV_STAGES], s_ready[2][2], p_ready[2][2], pv_done[2], o_final[2];
-    __shared__ long long offs[KEYS];
+    __shared__ long long offs[2][KEYS];
     __shared__ unsigned tmem_holder;
     __shared__ volatile int give_up;
     constexpr int DB = D / 64;                       // 64-element blocks per row
@@ -328,41 +331,51 @@ paged_prefill_tcgen05_kernel(const bf16* __restrict__ q, long long q_stride, bf1
         const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
         constexpr int ROW_STEP = 128 / CPR;                        // 8 (head size 128) or 16 (head size 64) rows per pass
         const int chunk = lt % CPR, row0 = lt / CPR, smem_off0 = swizzled(row0, chunk, KV_BLOCK);
-        for (int j = 0; j < n_tiles; ++j) {
-            const int s = j % KV_STAGES;
-            mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, &give_up);     // free from the start
-            if (lt < KEYS) {
-                const int key = (t_begin + j) * KEYS + lt;
-                long long off = -1;
-                if (key >= lo && key <= hi) {
-                    const int page = block_table[(size_t)r * bt_stride + (ps_shift >= 0 ? key >> ps_shift : key / ps)];
-                    if (page < 0 || page >= num_pages) {
-                        if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
-                    } else {
-                        const int within = ps_shift >= 0 ? key & (ps - 1) : key % ps;
-                        off = (((long long)page * nkv + kvh) * ps + within) * D;
+        // A tile is handed over LOADS_AHEAD iterations after its copies were started, before the wait for the next free
+        // stage: two tiles are on their way from memory at a time (a cold miss takes about as long as a tile's softmax),
+        // and tile t is handed over once the products of tile t - 3 are done, a full tile before its scores are wanted.
+        constexpr int LOADS_AHEAD = 2;
+        for (int j = 0; j < n_tiles + LOADS_AHEAD; ++j) {
+            if (j >= LOADS_AHEAD) {
+                cp_async_wait_but<LOADS_AHEAD - 1>();              // tile j - LOADS_AHEAD has arrived
+                fence_proxy_async();
+                mbar_arrive(&kv_full[(j - LOADS_AHEAD) % KV_STAGES]);
+            }
+            if (j < n_tiles) {
+                const int s = j % KV_STAGES;
+                mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, &give_up);     // free from the start
+                long long* tile_offs = offs[j & 1];
+                if (lt < KEYS) {
+                    const int key = (t_begin + j) * KEYS + lt;
+                    long long off = -1;
+                    if (key >= lo && key <= hi) {
+                        const int page = block_table[(size_t)r * bt_stride + (ps_shift >= 0 ? key >> ps_shift : key / ps)];
+                        if (page < 0 || page >= num_pages) {
+                            if (status) atomicOr(status, FE_STATUS_BAD_PAGE);
+                        } else {
+                            const int within = ps_shift >= 0 ? key & (ps - 1) : key % ps;
+                            off = (((long long)page * nkv + kvh) * ps + within) * D;
+                        }
                     }
+                    tile_offs[lt] = off;
                 }
-                offs[lt] = off;
-            }
-            loader_barrier();
-            if (give_up) break;                                    // the same for all loaders after the barrier
-            unsigned char* k_s = kv_s + s * 2 * KV_BYTES;
-            unsigned char* v_s = k_s + KV_BYTES;
-            // this thread's chunk of a row is always the same; its rows are ROW_STEP apart, which keeps row & 7
+                loader_barrier();                                  // the other buffer of offs is read by no one by now
+                if (give_up) break;                                // the same for all loaders after the barrier
+                unsigned char* k_s = kv_s + s * 2 * KV_BYTES;
+                unsigned char* v_s = k_s + KV_BYTES;
+                // this thread's chunk of a row is always the same; its rows are ROW_STEP apart, which keeps row & 7
 #pragma unroll
-            for (int k = 0; k < KEYS / ROW_STEP; ++k) {
-                const long long ro = offs[row0 + k * ROW_STEP];
-                const bool ok = ro >= 0;
-                const long long from = ok ? ro + chunk * 8 : 0;
-                cp_async16(k_s + smem_off0 + k * ROW_STEP * 128, kc + from, ok ? 16 : 0);     // keys out of range read as zeros
-                cp_async16(v_s + smem_off0 + k * ROW_STEP * 128, vc + from, ok ? 16 : 0);
+                for (int k = 0; k < KEYS / ROW_STEP; ++k) {
+                    const long long ro = tile_offs[row0 + k * ROW_STEP];
+                    const bool ok = ro >= 0;
+                    const long long from = ok ? ro + chunk * 8 : 0;
+                    cp_async16(k_s + smem_off0 + k * ROW_STEP * 128, kc + from, ok ? 16 : 0);     // keys out of range read as zeros
+                    cp_async16(v_s + smem_off0 + k * ROW_STEP * 128, vc + from, ok ? 16 : 0);
+                }
             }
-            cp_async_wait_all();
-            fence_proxy_async();
-            mbar_arrive(&kv_full[s]);
-            loader_barrier();                                      // offs may be rewritten
+            cp_async_commit();                                     // one group an iteration, empty ones at the end
         }
+        cp_async_wait_all();
     } else if (warp >= 12) {
         // ---- lane 0 of warp 12 + i issues the products of row tile i; the tensor cores keep each thread's order ----
         const int i = warp - 12;
