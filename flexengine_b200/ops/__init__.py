@@ -430,7 +430,7 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     """Causal grouped-query attention of the step's tokens over their requests' pages.
     qkv [T, >= nq d] holds the (rotated) queries in its first nq d columns; returns [T, nq d].
     float32 runs on CUDA cores (true 32-bit); bfloat16 on tensor cores: the split-KV decode
-    kernel when every request brings one token, else a prefill kernel (tcgen05 for long portions of
+    kernel when every request brings one token, else a prefill kernel (tcgen05 for portions of
     head size 64 or 128, mma.sync otherwise)."""
     _need_cuda(qkv, k_cache, v_cache, block_table)
     T = qkv.shape[0]

@@ -26,7 +26,7 @@ TINY_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden
               num_attention_heads=6, num_key_value_heads=3, head_dim=48, intermediate_size=112, vocab_size=301,
               rope_theta=50000.0, rms_norm_eps=3e-6, max_position_embeddings=1024, tie_word_embeddings=False,
               use_sliding_window=False, hidden_act="silu")
-# head size 64 with long enough prompts: portions of 64 queries and more take the tcgen05 attention kernel in bfloat16
+# head size 64: in bfloat16 its portions take the tcgen05 attention kernel (the others' head sizes take the mma.sync one)
 TINY_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=96,
               num_attention_heads=8, num_key_value_heads=2, head_dim=64, intermediate_size=176, vocab_size=333,
               rope_theta=200000.0, rms_norm_eps=2e-6, max_position_embeddings=2048, tie_word_embeddings=True,
