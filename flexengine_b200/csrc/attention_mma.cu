@@ -356,11 +356,12 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
 // splits are computed once per block; the sums run four splits at a time so that their loads
 // overlap (the order of the additions is fixed all the same).
 constexpr int MAX_SPLITS_SHARED = 256;
+constexpr int COMBINE_MAX_GROUPS = 8;        // sets of threads that share the splits of one (request, head) in the merge
 
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                       bf16* __restrict__ out, long long out_stride, const int* __restrict__ cu_q,
-                                      int nq, int d, int splits, int requests, const void* __restrict__ upcoming,
-                                      long long upcoming_bytes) {
+                                      int nq, int d, int splits, int groups, int requests,
+                                      const void* __restrict__ upcoming, long long upcoming_bytes) {
     if ((int)blockIdx.y >= requests) {
         // rows of blocks beyond the requests: the merge barely touches memory, so they start the matrix that the
         // next kernel streams (the output projection) into L2
@@ -372,35 +373,60 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
     griddep_wait();
     griddep_launch_dependents();
     __shared__ float weight[MAX_SPLITS_SHARED];
+    __shared__ float sums[COMBINE_MAX_GROUPS][128];
     __shared__ float inv_total;
     const int head = blockIdx.x, b = blockIdx.y;
     const size_t base = ((size_t)b * nq + head) * splits;
     if (threadIdx.x < 32) {
+        // all of a lane's logarithms are asked for at once: one trip to memory, not one per 32 splits
+        float lse[MAX_SPLITS_SHARED / 32];
         float mx = -CUDART_INF_F;
-        for (int s = threadIdx.x; s < splits; s += 32) mx = fmaxf(mx, part_lse[base + s]);
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS_SHARED / 32; ++i) {
+            const int s = threadIdx.x + 32 * i;
+            lse[i] = s < splits ? part_lse[base + s] : -CUDART_INF_F;
+            mx = fmaxf(mx, lse[i]);
+        }
         mx = warp_max(mx);
         float sum = 0.f;
-        for (int s = threadIdx.x; s < splits; s += 32) {
-            const float w = mx == -CUDART_INF_F ? 0.f : exp2f(part_lse[base + s] - mx);
-            if (s < MAX_SPLITS_SHARED) weight[s] = w;
-            sum += w;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS_SHARED / 32; ++i) {
+            const int s = threadIdx.x + 32 * i;
+            const float w = mx == -CUDART_INF_F ? 0.f : exp2f(lse[i] - mx);
+            if (s < splits) weight[s] = w;
+            sum += s < splits ? w : 0.f;
         }
         sum = warp_sum(sum);
         if (threadIdx.x == 0) inv_total = sum > 0.f ? 1.f / sum : 0.f;
     }
     __syncthreads();
+    // ``groups`` sets of threads share the splits out among them (split s goes to set s % groups), so that a
+    // long list of splits is a few trips to memory deep; their sums are added in a fixed order
+    const int cols = blockDim.x / groups, grp = threadIdx.x / cols, col = threadIdx.x - grp * cols;
     bf16* op = out + (size_t)cu_q[b] * out_stride + (size_t)head * d;
     const float* po = part_o + base * d;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+    for (int j0 = 0; j0 < d; j0 += cols) {
+        const int j = j0 + col;
         float acc = 0.f;
-        int s = 0;
-        for (; s + 4 <= splits; s += 4) {
-            const float v0 = po[(size_t)s * d + j], v1 = po[(size_t)(s + 1) * d + j];
-            const float v2 = po[(size_t)(s + 2) * d + j], v3 = po[(size_t)(s + 3) * d + j];
-            acc += weight[s] * v0; acc += weight[s + 1] * v1; acc += weight[s + 2] * v2; acc += weight[s + 3] * v3;
+        if (j < d) {
+            int s = grp;
+            for (; s + 3 * groups < splits; s += 4 * groups) {
+                const float v0 = po[(size_t)s * d + j], v1 = po[(size_t)(s + groups) * d + j];
+                const float v2 = po[(size_t)(s + 2 * groups) * d + j], v3 = po[(size_t)(s + 3 * groups) * d + j];
+                acc += weight[s] * v0; acc += weight[s + groups] * v1;
+                acc += weight[s + 2 * groups] * v2; acc += weight[s + 3 * groups] * v3;
+            }
+            for (; s < splits; s += groups) acc += weight[s] * po[(size_t)s * d + j];
         }
-        for (; s < splits; ++s) acc += weight[s] * po[(size_t)s * d + j];
-        op[j] = __float2bfloat16_rn(acc * inv_total);
+        if (groups > 1) {
+            sums[grp][col] = acc;
+            __syncthreads();
+            if (grp == 0) {
+                for (int g = 1; g < groups; ++g) acc += sums[g][col];
+            }
+            __syncthreads();                         // before the next round of columns overwrites the sums
+        }
+        if (grp == 0 && j < d) op[j] = __float2bfloat16_rn(acc * inv_total);
     }
 }
 
@@ -584,8 +610,10 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
     if (splits > 1) {
         FE_REQUIRE(upcoming_bytes >= 0, "paged_decode: negative byte count");
         const int extra = upcoming && upcoming_bytes > 0 ? 2 : 0;
-        fe::launch(decode_combine_kernel, dim3(nq, requests + extra), d >= 128 ? 128 : 64, 0, stream,
-            part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits, requests, upcoming, upcoming_bytes);
+        const int cols = d >= 128 ? 128 : 64;
+        const int groups = splits >= 64 ? 8 : splits >= 32 ? 4 : splits >= 16 ? 2 : 1;
+        fe::launch(decode_combine_kernel, dim3(nq, requests + extra), cols * groups, 0, stream,
+            part_o, part_lse, (bf16*)out, out_stride, cu_q, nq, d, splits, groups, requests, upcoming, upcoming_bytes);
         return fe_check_launch("paged_decode combine");
     }
     return 0;

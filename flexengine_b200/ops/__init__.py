@@ -346,14 +346,14 @@ def scratch(device, nbytes: int) -> torch.Tensor:
 
 def decode_splits(requests: int, nkv: int, max_ctx_len: int) -> int:
     """How many ways the keys of a request are split in decode.  Between half a round and one round of resident
-    blocks (six blocks fit an SM): towards the full round when a split still has eight tiles of 32 keys or more to
-    walk (long contexts), towards the half when splits would get short and the merge dominate; never a split
-    shorter than two tiles."""
+    blocks (six blocks fit an SM; never more than a round: a few blocks over it would run alone after it): towards
+    the full round when a split still has six tiles of 32 keys or more to walk, towards the half when splits
+    would get short and the merge dominate; never a split shorter than two tiles."""
     tiles = max(1, -(-max_ctx_len // 32))
     pairs = max(1, requests * nkv)
-    most = max(1, (6 * SM_COUNT + pairs // 2) // pairs)
+    most = max(1, 6 * SM_COUNT // pairs)          # rounded down: a few blocks over the round would run alone after it
     least = max(1, (3 * SM_COUNT + pairs // 2) // pairs)
-    want = min(most, max(least, tiles // 8))
+    want = min(most, max(least, tiles // 6))
     return int(max(1, min(want, tiles // 2)))
 
 
