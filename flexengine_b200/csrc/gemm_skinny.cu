@@ -245,9 +245,11 @@ template <int EPI>
 int launch(const void* x, const void* W, void* out, int M, int N, int K, int I, cudaStream_t stream,
            const QkvEpilogue& qkv = QkvEpilogue{}) {
     const int tiles = EPI == EPI_SWIGLU ? (I + 7) / 8 : (N + 15) / 16;
-    // a wide matrix: two tiles per block; a narrow one (all its blocks are resident at once): every
-    // warp sends twice as many loads ahead, which halves the number of round trips to memory
-    const bool wide = EPI != EPI_QKV && tiles >= 4 * 148;
+    // Three one-tile blocks are resident on an SM (80 registers a thread), two of the others (120 to 128).  A matrix
+    // with more tiles than one round of one-tile blocks takes two tiles a block: a few blocks over the round would
+    // run alone after it (448 tiles: 15.9 -> 13.6 us).  A narrow one, whose blocks are all resident at once even two
+    // to an SM: every warp sends twice as many loads ahead, which halves the number of round trips to memory.
+    const bool wide = EPI != EPI_QKV && tiles > 3 * 148;
     const bool deep = !wide && tiles <= 2 * 148;
     const int blocks = wide ? (tiles + 1) / 2 : tiles;
 #define FE_SKINNY(NT, RT, PF) \

@@ -102,8 +102,9 @@ def test_linear_bf16(M, N, K, gen):
 
 
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(301, 64), (24, 192), (768, 384), (4608, 3584), (16, 18944)])
+@pytest.mark.parametrize("N,K", [(301, 64), (24, 192), (768, 384), (4608, 3584), (16, 18944), (7184, 128), (9624, 64)])
 def test_skinny_gemm(M, N, K, gen):
+    # the last two: more 16-row tiles than one round of resident blocks (two tiles a block), one with a ragged end
     x, w = rand((M, K), torch.bfloat16, gen), rand((N, K), torch.bfloat16, gen, 0.05)
     want = x.float() @ w.float().T
     torch.testing.assert_close(ops().skinny_gemm(x, w, ops().EPI_F32), want, atol=1e-3, rtol=1e-3)
