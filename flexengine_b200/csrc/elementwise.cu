@@ -272,6 +272,12 @@ __global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __r
 // The same for head sizes and rotary widths that are multiples of 16: one block per token; sine
 // and cosine of the token's angles are computed once (they do not depend on the head) and
 // every thread moves eight elements of each half at a time.
+// eight consecutive floats from a 16-byte aligned address (bias, the table of cosines and sines)
+__device__ __forceinline__ void load8f(const float* p, float* v) {
+    const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+}
+
 template <typename T>
 __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
                                                const int* __restrict__ positions, const float* __restrict__ inv_freq,
@@ -280,7 +286,7 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
                                                long long num_slots, int* __restrict__ status) {
     griddep_wait();
     griddep_launch_dependents();
-    extern __shared__ float trig[];                  // cos [rot/2], sin [rot/2]
+    extern __shared__ __align__(16) float trig[];    // cos [rot/2], sin [rot/2]
     const int t = blockIdx.x;
     const int half = rot / 2;
     const bool rotary = inv_freq != nullptr && rot > 0;
@@ -316,13 +322,20 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
             load8<T>(hx + j, a);
             load8<T>(hx + j + half, c);
             float ra[8], rc[8];
+            float cs[8], sn[8];
+            load8f(trig + j, cs);
+            load8f(trig + half + j, sn);
+            if (hb) {
+                float ba[8], bc[8];
+                load8f(hb + j, ba);
+                load8f(hb + j + half, bc);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { a[e] += ba[e]; c[e] += bc[e]; }
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                float av = a[e], cv = c[e];
-                if (hb) { av += hb[j + e]; cv += hb[j + half + e]; }
-                const float cs = trig[j + e], sn = trig[half + j + e];
-                ra[e] = av * cs - cv * sn;
-                rc[e] = cv * cs + av * sn;
+                ra[e] = a[e] * cs[e] - c[e] * sn[e];
+                rc[e] = c[e] * cs[e] + a[e] * sn[e];
             }
             store8<T>(hx + j, ra);
             store8<T>(hx + j + half, rc);
@@ -335,8 +348,12 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
             for (int rep = 0; rep < ((k < rot_units) ? 2 : 1); ++rep, j += half) {
                 float a[8];
                 load8<T>(hx + j, a);
+                if (hb) {
+                    float ba[8];
+                    load8f(hb + j, ba);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) if (hb) a[e] += hb[j + e];
+                    for (int e = 0; e < 8; ++e) a[e] += ba[e];
+                }
                 store8<T>(hx + j, a);
                 if (dst) store8<T>(dst + j, a);
             }
@@ -348,9 +365,11 @@ template <typename T>
 static int launch_rope(void* qkv, const float* bias, const int* positions, const float* inv_freq, int rot,
                        const int* slot_mapping, void* kc, void* vc, int T_tokens, int nq, int nkv, int d, int ps,
                        long long num_slots, int* status, cudaStream_t stream) {
-    if (d % 16 == 0 && rot % 16 == 0) {
+    if (d % 16 == 0 && rot % 16 == 0 && ((size_t)bias & 15) == 0) {
         const int units = (nq + 2 * nkv) * (d / 8 - (inv_freq && rot ? rot / 16 : 0));
-        const int threads = units >= 256 ? 256 : (units >= 128 ? 128 : 64);
+        // as few passes over the units as 256 threads need, and then only as many threads as fill every pass
+        const int passes = (units + 255) / 256;
+        const int threads = max(64, ((units + passes - 1) / passes + 31) / 32 * 32);
         fe::launch(qkv_bias_rope_cache_vec_kernel<T>, T_tokens, threads, (size_t)rot * sizeof(float), stream, 
             (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
     } else {

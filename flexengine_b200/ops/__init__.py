@@ -224,13 +224,16 @@ def stream_gemm(x, w, epilogue: int = EPI_BF16):
     return out
 
 
+TCGEN05_MIN_K = 1024
 TCGEN05_MIN_ROWS = 1024      # measured: from about this many rows the fused kernel matches the library + activation
 
 
 def tcgen05_ok(x, w) -> bool:
-    """Whether the tcgen05 kernel is used for this product: bfloat16, many rows (prefill), K a multiple of 8."""
+    """Whether the tcgen05 kernel is used for this product: bfloat16, many rows (prefill), K a multiple of 8 and
+    long enough for the products of a tile to cover its epilogue (at K = 896 the library + activation is 10 % ahead,
+    from K = 1,536 on the fused kernel is)."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] >= TCGEN05_MIN_ROWS
-            and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+            and x.shape[1] >= TCGEN05_MIN_K and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
