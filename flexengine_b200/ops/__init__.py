@@ -390,11 +390,22 @@ def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start,
     return out
 
 
-def tcgen05_attention_ok(max_q_len, nq, nkv, d):
+def tcgen05_attention_ok(max_q_len, nq, nkv, d, lengths=None, starts=None):
     """The tcgen05 prefill kernel takes head sizes 64 and 128, portions of any length: measured against the
     mma.sync kernel it is level on portions of a few tokens and ahead everywhere else, the more the longer the
-    context.  Other head sizes go to the mma.sync kernel."""
-    return d in (64, 128)
+    context.  Other head sizes go to the mma.sync kernel, and so does a step of many requests that bring a few
+    tokens each to short contexts (``lengths`` and ``starts`` given): one tcgen05 block is resident on an SM and
+    costs a few microseconds before its first tile, where several of the lighter blocks share an SM."""
+    if d not in (64, 128):
+        return False
+    if lengths:
+        group = nq // nkv
+        blocks = nkv * sum(-(-n * group // 256) for n in lengths)
+        rows = nkv * group * sum(lengths)
+        longest = max(s + n for s, n in zip(starts, lengths))
+        if blocks > SM_COUNT and rows < 96 * blocks and longest <= 1024:
+            return False
+    return True
 
 
 PREFILL_MAX_SPLITS = 32
@@ -447,8 +458,8 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
         return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
                                 nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming)
-    if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d):
-        lengths = getattr(ctx, "host_lengths", None)
+    lengths = getattr(ctx, "host_lengths", None)
+    if tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d, lengths, getattr(ctx, "host_starts", None)):
         splits = prefill_splits(lengths, ctx.host_starts, nq, nkv, window) if lengths else 1
         return paged_prefill_tcgen05(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, T, requests,
                                      ctx.max_q_len, nq, nkv, d, page_size, scale, window, splits)

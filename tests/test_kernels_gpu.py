@@ -431,6 +431,12 @@ def test_prefill_splits_follow_the_work():
 def test_dispatch_takes_the_tcgen05_kernel_for_its_head_sizes(gen):
     assert ops().tcgen05_attention_ok(300, 4, 2, 128) and ops().tcgen05_attention_ok(2, 4, 2, 64)
     assert not ops().tcgen05_attention_ok(4096, 4, 2, 96)
+    # very many requests with a few tokens each at short contexts: the lighter blocks of the mma.sync kernel
+    ok = ops().tcgen05_attention_ok
+    assert not ok(8, 28, 4, 128, [8] * 256, [0] * 256) and not ok(64, 28, 4, 128, [1] * 60 + [64], [200] * 60 + [0])
+    assert ok(32, 28, 4, 128, [32] * 64, [0] * 64) and ok(500, 28, 4, 128, [1] * 30 + [500], [2000] * 30 + [0])
+    got, want, _ = _attention_case(torch.bfloat16, 8, 2, 128, 16, [(50, 1)] * 100 + [(0, 40)], 0, gen)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
     got, want, _ = _attention_case(torch.bfloat16, 4, 2, 128, 16, [(0, 300), (100, 1), (7, 2)], 0, gen)
     torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
     # a short portion late in a long context beside decoded tokens: the dispatch splits its keys
