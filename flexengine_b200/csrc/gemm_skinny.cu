@@ -18,7 +18,7 @@ using namespace fe;
 
 namespace {
 
-constexpr int WARPS = 8;
+constexpr int WARPS_USUAL = 8, WARPS_NARROW = 16;
 constexpr int KSTEP = 64;       // k elements per warp step (4 MMAs)
 
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
@@ -76,7 +76,9 @@ __device__ __forceinline__ void mma16816(float* c, unsigned a0, unsigned a1, uns
 // RT: 16-row tiles of W per block (2 for wide matrices: fewer, longer-lived blocks that fill the
 //     GPU in whole rounds, and the activations are read once for both tiles)
 // PF: k steps whose loads go out together before their math (bytes in flight per lane = RT * PF * 64)
-template <int NT, int EPI, int RT, int PF>
+// WARPS: warps that split K (8; 16 for a narrow matrix with a long K, whose few blocks leave SMs empty: the blocks
+//     it has then keep twice as many loads in flight)
+template <int NT, int EPI, int RT, int PF, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
                    int I, const QkvEpilogue qkv) {
@@ -242,7 +244,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 }
 
 template <int EPI>
-int launch(const void* x, const void* W, void* out, int M, int N, int K, int I, cudaStream_t stream,
+int launch(const void* x, const void* W_, void* out, int M, int N, int K, int I, cudaStream_t stream,
            const QkvEpilogue& qkv = QkvEpilogue{}) {
     const int tiles = EPI == EPI_SWIGLU ? (I + 7) / 8 : (N + 15) / 16;
     // Three one-tile blocks are resident on an SM (80 registers a thread), two of the others (120 to 128).  A matrix
@@ -252,10 +254,13 @@ int launch(const void* x, const void* W, void* out, int M, int N, int K, int I, 
     const bool wide = EPI != EPI_QKV && tiles > 3 * 148;
     const bool deep = !wide && tiles <= 2 * 148;
     const int blocks = wide ? (tiles + 1) / 2 : tiles;
-#define FE_SKINNY(NT, RT, PF) \
-    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF>, blocks, WARPS * 32, 0, stream, (const bf16*)x, (const bf16*)W, out, M, N, K, I, qkv)
-    if (M <= 8) { if (wide) FE_SKINNY(1, 2, 2); else if (deep) FE_SKINNY(1, 1, 4); else FE_SKINNY(1, 1, 2); }
-    else { if (wide) FE_SKINNY(2, 2, 2); else if (deep) FE_SKINNY(2, 1, 4); else FE_SKINNY(2, 1, 2); }
+    // fewer blocks than SMs, and at least one round of loads (four steps) for each of sixteen warps
+    const bool narrow = (EPI == EPI_BF16 || EPI == EPI_F32) && M <= 8 && tiles <= 148 && K / KSTEP >= 4 * WARPS_NARROW;
+#define FE_SKINNY(NT, RT, PF, W) \
+    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF, W>, blocks, W * 32, 0, stream, (const bf16*)x, (const bf16*)W_, out, M, N, K, I, qkv)
+    if (narrow) FE_SKINNY(1, 1, 4, WARPS_NARROW);
+    else if (M <= 8) { if (wide) FE_SKINNY(1, 2, 2, WARPS_USUAL); else if (deep) FE_SKINNY(1, 1, 4, WARPS_USUAL); else FE_SKINNY(1, 1, 2, WARPS_USUAL); }
+    else { if (wide) FE_SKINNY(2, 2, 2, WARPS_USUAL); else if (deep) FE_SKINNY(2, 1, 4, WARPS_USUAL); else FE_SKINNY(2, 1, 2, WARPS_USUAL); }
 #undef FE_SKINNY
     return fe_check_launch("skinny_gemm");
 }

@@ -104,7 +104,8 @@ def test_linear_bf16(M, N, K, gen):
 @pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(301, 64), (24, 192), (768, 384), (4608, 3584), (16, 18944), (7184, 128), (9624, 64)])
 def test_skinny_gemm(M, N, K, gen):
-    # the last two: more 16-row tiles than one round of resident blocks (two tiles a block), one with a ragged end
+    # (7184, 128), (9624, 64): more 16-row tiles than one round of resident blocks (two tiles a block), one with a
+    # ragged end; (16, 18944): one tile and a long K (sixteen warps split K)
     x, w = rand((M, K), torch.bfloat16, gen), rand((N, K), torch.bfloat16, gen, 0.05)
     want = x.float() @ w.float().T
     torch.testing.assert_close(ops().skinny_gemm(x, w, ops().EPI_F32), want, atol=1e-3, rtol=1e-3)
@@ -154,6 +155,17 @@ def test_stream_gemm_tcgen05(M, N, K, gen):
 def test_gemm_tcgen05_refuses_what_it_cannot_take(gen):
     with pytest.raises(RuntimeError, match="multiple of 8"):
         ops().gemm_tcgen05(rand((4, 60), torch.bfloat16, gen), rand((32, 60), torch.bfloat16, gen))
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("N,K", [(301, 4224), (1536, 8960), (40, 4096)])
+def test_skinny_gemm_narrow_matrix_long_k(M, N, K, gen):
+    """Fewer 16-row tiles than SMs and a long K: sixteen warps a block split K (66 steps leave the last warps less)."""
+    x, w = rand((M, K), torch.bfloat16, gen), rand((N, K), torch.bfloat16, gen, 0.05)
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(ops().skinny_gemm(x, w, ops().EPI_F32), want, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(ops().linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
+    assert torch.equal(ops().skinny_gemm(x, w, ops().EPI_F32), ops().skinny_gemm(x, w, ops().EPI_F32))
 
 
 def test_skinny_gemm_refuses_what_it_cannot_take(gen):
