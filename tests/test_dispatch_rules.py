@@ -1,0 +1,51 @@
+"""The host-side rules that choose a kernel and its launch shape: pure functions of sizes, checked without a GPU."""
+from flexengine_b200 import ops
+
+SLOTS = 6 * ops.SM_COUNT        # decode attention blocks resident at once
+
+
+def test_decode_splits_stay_within_one_resident_round():
+    for requests in (1, 2, 3, 5, 8, 13, 16, 31, 32, 64, 100, 256):
+        for nkv in (1, 2, 4, 8):
+            for ctx in (1, 31, 64, 500, 2048, 8192, 32768, 131072):
+                splits = ops.decode_splits(requests, nkv, ctx)
+                tiles = -(-ctx // 32)
+                assert splits >= 1
+                assert splits == 1 or splits * 2 <= tiles, "a split walks at least two tiles"
+                if requests * nkv <= SLOTS:
+                    assert splits * requests * nkv <= SLOTS, (requests, nkv, ctx, splits)
+    # the case that showed the fault: 28 splits of 32 pairs were 8 blocks more than fit
+    assert ops.decode_splits(8, 4, 32768) == 27
+    assert ops.decode_splits(8, 4, 2048) == 14 and ops.decode_splits(64, 4, 2048) == 3 and ops.decode_splits(1, 4, 2048) == 32
+
+
+def test_prefill_splits_follow_the_work():
+    split = ops.prefill_splits
+    assert split([2048], [0], 28, 4) == 1                      # a whole prompt fills the device by itself
+    assert split([64], [2048], 28, 4) == 8                     # 33 tiles: no split shorter than four
+    assert split([64], [8192], 28, 4) == 18                    # eight blocks without splits; one round of the device
+    assert split([2], [100000], 28, 4) == 32                   # never more than the merge takes
+    assert split([64], [0], 28, 4) == 1 and split([40, 1, 1], [10, 20, 30], 4, 2) == 1
+    assert split([16], [900], 28, 4) == 1 and split([16], [1010], 28, 4) == 4      # from sixteen tiles on
+    assert split([64], [8192], 28, 4, window=256) == 1         # a window bounds what any row walks
+    assert split([1] * 4 + [128], [500] * 4 + [4000], 28, 4) == 4      # decoded tokens beside a portion
+    for lengths, starts in (([1], [0]), ([5, 700], [3, 9000]), ([128] * 4, [64000] * 4)):
+        s = split(lengths, starts, 12, 2)
+        assert 1 <= s <= ops.PREFILL_MAX_SPLITS
+
+
+def test_attention_kernel_choice():
+    ok = ops.tcgen05_attention_ok
+    assert ok(300, 4, 2, 128) and ok(2, 4, 2, 64) and not ok(4096, 4, 2, 96) and not ok(4096, 4, 2, 256)
+    # very many requests with a few tokens each at short contexts: the lighter blocks of the mma.sync kernel
+    assert not ok(8, 28, 4, 128, [8] * 256, [0] * 256) and not ok(64, 28, 4, 128, [1] * 60 + [64], [200] * 60 + [0])
+    assert ok(32, 28, 4, 128, [32] * 64, [0] * 64) and ok(500, 28, 4, 128, [1] * 30 + [500], [2000] * 30 + [0])
+
+
+def test_upcoming_hint_only_for_small_steps():
+    import torch
+    w = torch.zeros(4, 4)
+    ptr, nbytes = ops._upcoming(w, 8)
+    assert nbytes.value == 0            # not a CUDA tensor: nothing to ask for
+    ptr, nbytes = ops._upcoming(None, 8)
+    assert ptr.value in (None, 0) and nbytes.value == 0

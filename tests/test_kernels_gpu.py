@@ -428,18 +428,6 @@ def test_tcgen05_prefill_kernel_with_split_keys(splits, gen):
         _attention_case(torch.bfloat16, 4, 2, 64, 16, [(0, 300)], 0, gen, tcgen05=33)
 
 
-def test_prefill_splits_follow_the_work():
-    split = ops().prefill_splits
-    assert split([2048], [0], 28, 4) == 1                      # a whole prompt fills the device by itself
-    assert split([64], [2048], 28, 4) == 8                     # 33 tiles: no split shorter than four
-    assert split([64], [8192], 28, 4) == 18                    # eight blocks without splits; one round of the device
-    assert split([2], [100000], 28, 4) == 32                   # never more than the merge takes
-    assert split([64], [0], 28, 4) == 1 and split([40, 1, 1], [10, 20, 30], 4, 2) == 1
-    assert split([16], [900], 28, 4) == 1 and split([16], [1010], 28, 4) == 4      # from sixteen tiles on
-    assert split([64], [8192], 28, 4, window=256) == 1         # a window bounds what any row walks
-    assert split([1] * 4 + [128], [500] * 4 + [4000], 28, 4) == 4      # decoded tokens beside a portion
-
-
 def test_dispatch_takes_the_tcgen05_kernel_for_its_head_sizes(gen):
     assert ops().tcgen05_attention_ok(300, 4, 2, 128) and ops().tcgen05_attention_ok(2, 4, 2, 64)
     assert not ops().tcgen05_attention_ok(4096, 4, 2, 96)
