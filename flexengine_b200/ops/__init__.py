@@ -11,13 +11,14 @@ norm weights, biases and logits are float32; index tensors are int32.
 """
 from __future__ import annotations
 
-import ctypes
-
 import torch
 
 from . import library
 
-_c_void_p, _c_int, _c_float, _c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+# Arguments go to the entry points as plain Python values: the loader has given every entry point the parameter
+# types of its C declaration (ops/library.py), so ctypes converts them itself, and refuses a call whose number of
+# arguments or kinds of values do not fit.  These names say which C type a value is meant for.
+_c_int, _c_ll, _c_float = int, int, float
 
 _status: dict = {}
 launches = 0          # kernels of this package launched so far (library matrix products not counted)
@@ -28,7 +29,7 @@ def _core():
 
 
 def _ptr(t):
-    return _c_void_p(t.data_ptr()) if t is not None else _c_void_p(0)
+    return t.data_ptr() if t is not None else None
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -37,8 +38,8 @@ _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 def _stream():
     """The current stream's handle; asked for at every launch, so by the shortest way there is."""
     if _raw_stream is not None:
-        return _c_void_p(_raw_stream(torch.cuda.current_device()))
-    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _code(dtype) -> int:
@@ -113,7 +114,7 @@ UPCOMING_BYTES = 10 << 20         # how much of the next weight matrix a norm as
 def _upcoming(tensor, rows: int, limit: int = UPCOMING_BYTES):
     """(pointer, bytes) of the start of ``tensor`` for a kernel's prefetching blocks; nothing for large steps."""
     if tensor is None or rows > UPCOMING_MAX_ROWS or not tensor.is_cuda:
-        return _c_void_p(0), _c_ll(0)
+        return None, 0
     return _ptr(tensor), _c_ll(min(tensor.numel() * tensor.element_size(), limit))
 
 
@@ -368,7 +369,6 @@ def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, 
     if out is None:
         out = torch.empty((requests, nq * d), dtype=torch.bfloat16, device=k_cache.device)
     lib = _bf16()
-    lib.fe_paged_decode_scratch_bytes.restype = _c_ll
     need = lib.fe_paged_decode_scratch_bytes(_c_int(requests), _c_int(nq), _c_int(d), _c_int(splits))
     work = scratch(k_cache.device, need) if need else None
     _run(lib, "fe_paged_decode_mma_upcoming", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(work),
@@ -435,7 +435,7 @@ def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_st
     _run(_bf16(), "fe_paged_prefill_tcgen05", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(nq * d), _ptr(k_cache),
          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
          _c_int(max_q_len), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]),
-         _c_float(scale), _c_int(window), _c_int(splits), _ptr(part) if part is not None else ctypes.c_void_p(0),
+         _c_float(scale), _c_int(window), _c_int(splits), _ptr(part),
          _c_ll(T), _ptr(status_word(k_cache.device)), _stream())
     return out
 

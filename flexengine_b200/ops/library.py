@@ -12,6 +12,7 @@ import ctypes
 import fcntl
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -159,6 +160,40 @@ def _prune(root: str, group: str, keep: str) -> None:
             shutil.rmtree(os.path.join(root, name), ignore_errors=True)
 
 
+_PROTOTYPE = re.compile(r'extern\s+"C"\s+((?:const\s+)?[\w ]+?\s*\*?)\s*(fe_\w+)\s*\(([^)]*)\)', re.S)
+
+
+def _ctype(decl: str, what: str):
+    """The ctypes type of one C parameter or return declaration of an entry point."""
+    text = decl.replace("const", " ").replace("__restrict__", " ").strip()
+    if "*" in text:
+        return ctypes.c_char_p if what == "return" and "char" in text else ctypes.c_void_p
+    words = text.split()
+    if what == "parameter" and len(words) > 1:
+        words = words[:-1]                       # the parameter's name
+    kind = " ".join(words)
+    table = {"int": ctypes.c_int, "long long": ctypes.c_longlong, "float": ctypes.c_float,
+             "cudaStream_t": ctypes.c_void_p, "void": None}
+    if kind not in table:
+        raise KernelLibraryError(f"entry point declares a type this loader does not know: '{decl.strip()}'")
+    return table[kind]
+
+
+def prototypes(group: str) -> dict:
+    """{entry point: (return type, [parameter types])} read from the ``extern "C"`` declarations of the group's
+    sources, so that the types ctypes converts to are the ones the C side declares (and a call with the wrong
+    number of arguments is refused before it reaches the device)."""
+    found = {}
+    for name in GROUPS[group]:
+        with open(os.path.join(CSRC, name)) as f:
+            text = f.read()
+        for ret, fn, params in _PROTOTYPE.findall(text):
+            params = params.strip()
+            args = [] if params in ("", "void") else [_ctype(a, "parameter") for a in params.split(",")]
+            found[fn] = (_ctype(ret, "return"), args)
+    return found
+
+
 def load(group: str) -> ctypes.CDLL:
     """The loaded library ``group``; builds it first when needed.  Raises when it cannot be had."""
     with _lock:
@@ -169,7 +204,9 @@ def load(group: str) -> ctypes.CDLL:
             lib = ctypes.CDLL(path)
         except OSError as ex:
             raise KernelLibraryError(f"cannot load {path}: {ex}") from ex
-        lib.fe_last_error.restype = ctypes.c_char_p
+        for fn, (restype, argtypes) in prototypes(group).items():
+            entry = getattr(lib, fn)
+            entry.restype, entry.argtypes = restype, argtypes
         # programmatic dependent launch (a kernel's preamble overlaps the tail of the one before):
         # measured to bring nothing inside CUDA graphs, so it is off unless FLEXENGINE_PDL=1
         lib.fe_set_pdl(ctypes.c_int(1 if os.environ.get("FLEXENGINE_PDL", "0") == "1" else 0))

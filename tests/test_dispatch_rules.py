@@ -44,8 +44,24 @@ def test_attention_kernel_choice():
 
 def test_upcoming_hint_only_for_small_steps():
     import torch
-    w = torch.zeros(4, 4)
-    ptr, nbytes = ops._upcoming(w, 8)
-    assert nbytes.value == 0            # not a CUDA tensor: nothing to ask for
-    ptr, nbytes = ops._upcoming(None, 8)
-    assert ptr.value in (None, 0) and nbytes.value == 0
+    assert ops._upcoming(torch.zeros(4, 4), 8) == (None, 0)            # not a CUDA tensor: nothing to ask for
+    assert ops._upcoming(None, 8) == (None, 0)
+
+
+def test_entry_points_take_the_types_their_c_declarations_name():
+    """The loader reads every ``extern "C"`` declaration of the sources; each entry point the Python side calls is
+    among them, with one ctypes type per parameter, pointers as pointers and 64-bit integers as such."""
+    import ctypes
+    import re
+    from flexengine_b200.ops import library
+    declared = {}
+    for group in library.GROUPS:
+        declared.update(library.prototypes(group))
+    with open(ops.__file__) as f:
+        called = set(re.findall(r"\bfe_\w+", f.read()))
+    assert called and called <= set(declared), called - set(declared)
+    restype, args = declared["fe_paged_prefill_tcgen05"]
+    assert restype is ctypes.c_int and len(args) == 24
+    assert args[0] is ctypes.c_void_p and args[1] is ctypes.c_longlong and args[17] is ctypes.c_float
+    assert declared["fe_static_scratch_bytes"] == (ctypes.c_longlong, [])
+    assert declared["fe_last_error"][0] is ctypes.c_char_p and declared["fe_set_pdl"] == (None, [ctypes.c_int])
