@@ -154,3 +154,50 @@ def test_random_orders_lose_nothing(seed):
     m.assert_invariants()
     assert m.groups[0].pool.free_pages == 12 and m.groups[1].pool.free_pages == 6
     assert len(m.free_state_slots) == 4 and done > 10
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_orders_with_shared_prefixes(seed):
+    """Requests that start on a donor's complete pages, in random order with growth and release: a shared page is
+    counted once per holder, comes back only when its last holder lets go, and is never among a holder's writable slots."""
+    rng = random.Random(100 + seed)
+    m = manager(groups=(FULL, STATE), pages=14, page_size=4, max_requests=5)
+    live, counter, shared_seen = {}, 0, 0
+    for _ in range(500):
+        action = rng.random()
+        if action < 0.15 and len(live) < 5:
+            rid = f"r{counter}"; counter += 1
+            donors = [d for d, n in live.items() if n >= 4]
+            if donors and rng.random() < 0.7:
+                donor = rng.choice(donors)
+                tokens = rng.randrange(4, live[donor] + 1)
+                m.share_prefix(donor, rid, tokens)
+                live[rid] = (tokens // 4) * 4
+                assert m.tokens_of(rid) == live[rid] and m.table(rid, 0) == m.table(donor, 0)[:live[rid] // 4]
+                shared_seen += 1
+            else:
+                m.admit(rid); live[rid] = 0
+        elif action < 0.8 and live:
+            rid = rng.choice(list(live))
+            n = rng.choice((1, 2, 5))
+            try:
+                m.reserve(rid, live[rid] + n)
+            except CacheExhausted:
+                victim = rng.choice(list(live))
+                m.free(victim); del live[victim]
+            else:
+                # what this request may write lies past every page it shares
+                slots = m.slot_mapping(rid, 0, live[rid], n)
+                refs = m.groups[0].pool.refs
+                assert all(refs[s // 4] == 1 for s in slots)
+                m.commit(rid, n); live[rid] += n
+        elif live:
+            rid = rng.choice(list(live))
+            m.free(rid); del live[rid]
+        m.assert_invariants()
+        held = set(p for rc in m.requests.values() for p in rc.tables[0])
+        assert m.groups[0].pool.used_pages == len(held)
+    for rid in list(live):
+        m.free(rid)
+    m.assert_invariants()
+    assert m.used_pages == 0 and len(m.free_state_slots) == 5 and shared_seen > 5
