@@ -66,11 +66,14 @@ def _run(lib, name: str, *args) -> None:
 
 def status_word(device) -> torch.Tensor:
     """The device word in which kernels record a guarded fault (bad token, page or slot)."""
-    key = str(device)
-    if key not in _status:
-        with torch.inference_mode(False):          # a plain tensor, writable from any mode
-            _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status[key]
+    word = _status.get(device)                     # asked for at every launch: the device object itself is the key
+    if word is None:
+        key = str(torch.device(device))
+        if key not in _status:
+            with torch.inference_mode(False):      # a plain tensor, writable from any mode
+                _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+        word = _status[device] = _status[key]
+    return word
 
 
 def check_status(device) -> None:
@@ -338,13 +341,17 @@ def scratch(device, nbytes: int) -> torch.Tensor:
     """Scratch memory of at least ``nbytes`` bytes on ``device``, grown on demand.  A buffer that has been
     handed out is never freed: a CUDA graph captured with it keeps its address, and replays it long after a
     larger buffer has taken its place for new calls."""
-    key = str(device)
-    have = _scratch.get(key)
+    have = _scratch.get(device)
     if have is None or have.numel() < nbytes:
-        with torch.inference_mode(False):
-            have = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _scratch_kept.append(have)
-        _scratch[key] = have
+        key = str(torch.device(device))            # "cuda:0" and torch.device("cuda:0") share one buffer
+        have = _scratch.get(key)
+        if have is None or have.numel() < nbytes:
+            with torch.inference_mode(False):
+                have = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            _scratch_kept.append(have)
+        for k in [k for k in _scratch if str(torch.device(k)) == key]:
+            _scratch[k] = have
+        _scratch[key] = _scratch[device] = have
     return have
 
 
