@@ -1,23 +1,31 @@
-"""Makes ``reference_logits.npz``: last-token logits computed by the reference's OWN model code.
+"""Makes ``reference_logits.npz``: outputs of the reference's OWN code on tiny models.
 
 Run once, on the CPU, where the reference checkout is available:
 
     python tests/golden/make_golden.py /path/to/reference
 
-It writes tiny random Qwen2.5 models with ``write_random_model`` (seeded), wraps their tensors
-in a module tree of the shape the reference's ``Qwen2Adapter`` walks
-(src/flexengine/inference/models/qwen2.py:94-135), runs the adapter with the reference's
-``PagedKVCache`` and both of its CPU attention backends, whole and as a mixed batch
-(a prefill portion beside a decoded token), and stores the logits together with a checksum
-of the weights, so that the test can tell whether it regenerated the same model.  The
-RMSNorm and SwiGLU modules of the wrapper are not the reference's code (it calls Hugging
-Face modules there); they follow src/flexengine/inference/kernels/rmsnorm.py:24-32 and
-tests/unit/test_synthetic_qwen.py:30-36.  ``transformers`` is not imported.
+Three kinds of record, each computed by code imported from the reference checkout:
+
+* ``<config>/<backend>/...``: last-token logits of ``Qwen2Adapter`` + ``PagedKVCache``
+  (src/flexengine/inference/models/qwen2.py:79-136, src/flexengine/engine/kv_cache/allocator.py)
+  over the tiny configurations of the tests, with both CPU attention backends, whole prompts and a
+  mixed batch (a prefill portion beside a decoded token).  The module tree that the adapter walks
+  is built here; its norm and feed-forward modules are restatements (the adapter calls Hugging
+  Face modules there), which is why the next two records exist.
+* ``parts/rms/*`` and ``parts/mlp/*``: the reference's own ``FakeRMS`` and ``FakeMLP`` modules
+  (tests/unit/test_synthetic_qwen.py:19-36) run on fixed inputs (the feed-forward's biases zeroed:
+  Qwen2.5 has none).  The plain implementation's ``rms_norm`` and ``swiglu_mlp`` are held to them.
+* ``fake/*``: the reference's whole ``FakeQwen`` (tests/unit/test_synthetic_qwen.py:39-61: its own
+  norm, feed-forward and layer modules) with fixed weights, the biases that Qwen2.5 lacks zeroed,
+  through the adapter: whole, in portions and beside another request.
+
+Weights come from ``fixed_weights``: an integer hash per element, twelve uniforms summed, scaled and
+rounded to bfloat16.  Integer and basic IEEE arithmetic only, so every machine makes the same model
+and the test never has to skip; the checksum in the file guards it.  ``transformers`` is not imported.
 """
 import hashlib
 import os
 import sys
-import tempfile
 import types
 
 import numpy as np
@@ -25,14 +33,66 @@ import torch
 from torch import nn
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))      # helpers imports the package for other tests
 sys.path.insert(0, os.path.dirname(HERE))
 
 import helpers  # noqa: E402
-from flexengine_b200.weights import write_random_model  # noqa: E402
 
 SEED = 2024
-PROMPTS = {"A": [5, 17, 33], "B": [1, 40, 77], "C": [3, 50]}
+PROMPTS = {"A": [5, 17, 33], "B": [1, 40, 77], "C": [3, 50], "D": [4, 70]}
+FAKE_CONFIG = dict(model_type="qwen2", num_hidden_layers=2, hidden_size=32, num_attention_heads=4,
+                   num_key_value_heads=2, head_dim=8, intermediate_size=64, vocab_size=50, rope_theta=1000000.0,
+                   rms_norm_eps=1e-6, tie_word_embeddings=False)
+FAKE_PROMPTS = [[2, 5, 3, 8, 9, 4, 7, 12, 10], [16, 8, 9, 2]]
+
+
+# ---- weights that every machine draws alike ----------------------------------------------------------
+def _mix(z: np.ndarray) -> np.ndarray:
+    """splitmix64's output function on uint64 arrays (wrapping arithmetic)."""
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return z ^ (z >> np.uint64(31))
+
+
+def fixed_tensor(name: str, shape, seed: int, mean: float, std: float) -> torch.Tensor:
+    """About N(mean, std^2): twelve uniforms from an integer hash of (seed, name, element, k), summed, minus six;
+    float32, then rounded to bfloat16 and widened again (exactly representable in both)."""
+    count = int(np.prod(shape)) if len(shape) else 1
+    key = int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little")
+    with np.errstate(over="ignore"):
+        base = np.uint64(key) + np.arange(count, dtype=np.uint64) * np.uint64(0x9E3779B97F4A7C15)
+        total = np.zeros(count, dtype=np.float64)
+        for k in range(12):
+            bits = _mix(base + np.uint64(k + 1) * np.uint64(0xD1B54A32D192ED03))
+            total += (bits >> np.uint64(11)).astype(np.float64) * (1.0 / (1 << 53))
+    values = ((total - 6.0) * std + mean).astype(np.float32).reshape(shape)
+    return torch.from_numpy(values).to(torch.bfloat16).to(torch.float32)
+
+
+def tensor_shapes(config: dict) -> dict:
+    """Names and shapes of a Qwen2.5 checkpoint (the attribute paths of src/flexengine/inference/models/qwen2.py:94-135)."""
+    h, i, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
+    qd = config["num_attention_heads"] * config["head_dim"]
+    kd = config["num_key_value_heads"] * config["head_dim"]
+    shapes = {"model.embed_tokens.weight": (v, h), "model.norm.weight": (h,)}
+    if not config.get("tie_word_embeddings"):
+        shapes["lm_head.weight"] = (v, h)
+    for l in range(config["num_hidden_layers"]):
+        p = f"model.layers.{l}."
+        shapes.update({
+            p + "input_layernorm.weight": (h,), p + "post_attention_layernorm.weight": (h,),
+            p + "self_attn.q_proj.weight": (qd, h), p + "self_attn.q_proj.bias": (qd,),
+            p + "self_attn.k_proj.weight": (kd, h), p + "self_attn.k_proj.bias": (kd,),
+            p + "self_attn.v_proj.weight": (kd, h), p + "self_attn.v_proj.bias": (kd,),
+            p + "self_attn.o_proj.weight": (h, qd),
+            p + "mlp.gate_proj.weight": (i, h), p + "mlp.up_proj.weight": (i, h), p + "mlp.down_proj.weight": (h, i)})
+    return shapes
+
+
+def fixed_weights(config: dict, seed: int = SEED) -> dict:
+    """Matrices and biases about N(0, 0.02), norm weights about 1 + N(0, 0.01)."""
+    return {name: fixed_tensor(name, shape, seed, 1.0 if "norm" in name else 0.0, 0.01 if "norm" in name else 0.02)
+            for name, shape in tensor_shapes(config).items()}
 
 
 def weights_checksum(tensors: dict) -> str:
@@ -44,11 +104,27 @@ def weights_checksum(tensors: dict) -> str:
 
 
 def prompts_for(name: str) -> list:
-    g = torch.Generator().manual_seed(99)
+    """Token ids from the same integer hash (no library generator)."""
     vocab = helpers.CONFIGS[name]["vocab_size"]
-    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in PROMPTS[name]]
+    out = []
+    for n in PROMPTS[name]:
+        with np.errstate(over="ignore"):
+            bits = _mix(np.uint64(1234567 + n) + np.arange(n, dtype=np.uint64) * np.uint64(0x9E3779B97F4A7C15))
+        out.append([int(b % np.uint64(vocab)) for b in bits])
+    return out
 
 
+def part_inputs():
+    """Fixed inputs and weights of the two part records."""
+    x = fixed_tensor("parts.x", (7, 24), SEED, 0.0, 1.5)
+    rms_w = fixed_tensor("parts.rms.weight", (24,), SEED, 1.0, 0.3)
+    gate = fixed_tensor("parts.mlp.gate", (48, 24), SEED, 0.0, 0.3)
+    up = fixed_tensor("parts.mlp.up", (48, 24), SEED, 0.0, 0.3)
+    down = fixed_tensor("parts.mlp.down", (24, 48), SEED, 0.0, 0.3)
+    return x, rms_w, gate, up, down
+
+
+# ---- the module tree the adapter walks, around our tensors ------------------------------------------------
 class RMS(nn.Module):
     def __init__(self, weight, eps):
         super().__init__()
@@ -107,17 +183,71 @@ def skeleton(config: dict, w: dict) -> nn.Module:
     return m.eval()
 
 
+def fill_fake_qwen(model: nn.Module, w: dict) -> None:
+    """Put ``w`` into the reference's FakeQwen and zero the biases that Qwen2.5 does not have."""
+    def put(param, value):
+        with torch.no_grad():
+            param.copy_(value)
+    put(model.model.embed_tokens.weight, w["model.embed_tokens.weight"])
+    put(model.model.norm.weight, w["model.norm.weight"])
+    put(model.lm_head.weight, w["lm_head.weight"])
+    for l, layer in enumerate(model.model.layers):
+        p = f"model.layers.{l}."
+        put(layer.input_layernorm.weight, w[p + "input_layernorm.weight"])
+        put(layer.post_attention_layernorm.weight, w[p + "post_attention_layernorm.weight"])
+        for proj in ("q_proj", "k_proj", "v_proj"):
+            put(getattr(layer.self_attn, proj).weight, w[p + f"self_attn.{proj}.weight"])
+            put(getattr(layer.self_attn, proj).bias, w[p + f"self_attn.{proj}.bias"])
+        put(layer.self_attn.o_proj.weight, w[p + "self_attn.o_proj.weight"])
+        layer.self_attn.o_proj.bias.data.zero_()
+        for proj in ("gate_proj", "up_proj", "down_proj"):
+            put(getattr(layer.mlp, proj).weight, w[p + f"mlp.{proj}.weight"])
+            getattr(layer.mlp, proj).bias.data.zero_()
+
+
 def main(reference_root: str) -> None:
     sys.path.insert(0, os.path.join(reference_root, "src"))
+    sys.path.insert(0, os.path.join(reference_root, "tests", "unit"))
     from flexengine.engine.kv_cache.allocator import CacheLayout, PagedKVCache
     from flexengine.engine.scheduler.policies import Chunk
     from flexengine.inference.models.qwen2 import Qwen2Adapter
-    import plain_model
+    import test_synthetic_qwen as reference_test
     out = {}
+
+    # ---- the reference's own norm and feed-forward modules on fixed inputs
+    x, rms_w, gate, up, down = part_inputs()
+    with torch.no_grad():
+        rms = reference_test.FakeRMS(24)
+        rms.weight.copy_(rms_w)
+        out["parts/rms/out"] = rms(x).numpy()
+        mlp = reference_test.FakeMLP(24)
+        mlp.gate_proj.weight.copy_(gate), mlp.up_proj.weight.copy_(up), mlp.down_proj.weight.copy_(down)
+        mlp.gate_proj.bias.zero_(), mlp.up_proj.bias.zero_(), mlp.down_proj.bias.zero_()
+        out["parts/mlp/out"] = mlp(x).numpy()
+
+    # ---- the reference's whole synthetic model, through its adapter
+    w = fixed_weights(FAKE_CONFIG)
+    out["fake/checksum"] = np.frombuffer(weights_checksum(w).encode(), dtype=np.uint8)
+    fake = reference_test.FakeQwen().eval()
+    fill_fake_qwen(fake, w)
+    a, b = FAKE_PROMPTS
+    with torch.no_grad():
+        for backend in ("blockwise", "materialized"):
+            adapter = Qwen2Adapter(fake, "cpu", attention_backend=backend)
+            cache = PagedKVCache(CacheLayout(2, 40, 4, 2, 8))
+            cache.reserve("a", len(a)), cache.reserve("b", len(b))
+            got = adapter.forward([Chunk("a", a, 0), Chunk("b", b, 0)], cache)
+            out[f"fake/{backend}/whole/a"], out[f"fake/{backend}/whole/b"] = got[0].numpy(), got[1].numpy()
+            cache.free_request("a")
+            cache.reserve("a", len(a))
+            adapter.forward([Chunk("a", a[:3], 0)], cache)
+            adapter.forward([Chunk("a", a[3:8], 3)], cache)
+            out[f"fake/{backend}/portions/a"] = adapter.forward([Chunk("a", a[8:], 8)], cache)[0].numpy()
+        out["fake/independent/a"] = reference_test.independent_reference(fake, a).numpy()
+
+    # ---- the adapter over the tests' tiny configurations
     for name, config in helpers.CONFIGS.items():
-        with tempfile.TemporaryDirectory() as folder:
-            write_random_model(config, folder, seed=SEED, dtype="bfloat16")
-            _, w = plain_model.read_model_folder(folder)
+        w = fixed_weights(config)
         out[f"{name}/checksum"] = np.frombuffer(weights_checksum(w).encode(), dtype=np.uint8)
         model = skeleton(config, w)
         page = helpers.PAGE_SIZE[name]
@@ -134,8 +264,9 @@ def main(reference_root: str) -> None:
                 # mixed batch: the longest prompt's tail as a portion beside a decoded token of another request
                 long_ids, short_ids = prompts[-1], prompts[0]
                 cut = len(long_ids) // 2
-                cache.reserve("l", len(long_ids)); cache.reserve("s", len(short_ids))
-                adapter.forward([Chunk("s", short_ids[:-1], 0)], cache) if len(short_ids) > 1 else None
+                cache.reserve("l", len(long_ids)), cache.reserve("s", len(short_ids))
+                if len(short_ids) > 1:
+                    adapter.forward([Chunk("s", short_ids[:-1], 0)], cache)
                 adapter.forward([Chunk("l", long_ids[:cut], 0)], cache)
                 got = adapter.forward([Chunk("l", long_ids[cut:], cut), Chunk("s", short_ids[-1:], len(short_ids) - 1)], cache)
                 out[f"{name}/{backend}/mixed/long"] = got[0].numpy()

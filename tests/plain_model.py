@@ -6,10 +6,11 @@ library (not the framework's reader), the configuration is the raw config.json
 dictionary.  Every function is written from the reference's formulas and cites them by
 the file's path within the reference project.
 
-This file rests on the formulas AND on a one-time comparison with the reference's own
-``Qwen2Adapter`` (its model code imports on the CPU): ``tests/golden/make_golden.py``
-drove the reference adapter over tiny random models and committed the logits;
-``tests/test_plain_model.py`` compares this file with them.
+This file rests on the formulas AND on a one-time comparison with the reference's own code,
+which imports on the CPU: ``tests/golden/make_golden.py`` drove the reference's ``Qwen2Adapter``
+over tiny fixed-weight models, its own ``FakeRMS`` / ``FakeMLP`` modules on fixed inputs and its
+whole synthetic ``FakeQwen``, and committed the outputs; ``tests/test_plain_model.py`` compares
+this file with them (the whole model at the reference's bar of 1e-5, the two parts at 1e-6).
 """
 from __future__ import annotations
 

@@ -19,15 +19,13 @@ def golden():
     return np.load(os.path.join(GOLDEN, "reference_logits.npz"))
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
-def test_plain_model_matches_the_reference_adapter(name, golden, tmp_path):
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_plain_model_matches_the_reference_adapter(name, golden):
     import make_golden
-    from flexengine_b200.weights import write_random_model
-    write_random_model(helpers.CONFIGS[name], str(tmp_path), seed=make_golden.SEED, dtype="bfloat16")
-    config, w = plain_model.read_model_folder(str(tmp_path))
-    recorded = bytes(golden[f"{name}/checksum"]).decode()
-    if make_golden.weights_checksum(w) != recorded:
-        pytest.skip("this PyTorch draws other random weights than the one that made the golden file")
+    config = helpers.CONFIGS[name]
+    w = make_golden.fixed_weights(config)          # integer arithmetic: the same on every machine, so no skip
+    assert make_golden.weights_checksum(w) == bytes(golden[f"{name}/checksum"]).decode(), \
+        "the fixed weights differ from the ones the golden file was made with"
     prompts = make_golden.prompts_for(name)
     for backend in ("blockwise", "materialized"):
         for i, ids in enumerate(prompts):
@@ -39,6 +37,34 @@ def test_plain_model_matches_the_reference_adapter(name, golden, tmp_path):
                                    torch.from_numpy(golden[f"{name}/{backend}/mixed/long"]), atol=1e-5, rtol=1e-5)
         torch.testing.assert_close(plain_model.forward_logits(config, w, short_ids)[-1],
                                    torch.from_numpy(golden[f"{name}/{backend}/mixed/short"]), atol=1e-5, rtol=1e-5)
+
+
+def test_norm_and_feed_forward_match_the_reference_modules(golden):
+    """``rms_norm`` and ``swiglu_mlp`` against outputs of the reference's own FakeRMS and FakeMLP modules
+    (tests/unit/test_synthetic_qwen.py:19-36 of the reference; eps 1e-6 is fixed in FakeRMS)."""
+    import make_golden
+    x, rms_w, gate, up, down = make_golden.part_inputs()
+    torch.testing.assert_close(plain_model.rms_norm(x, rms_w, 1e-6), torch.from_numpy(golden["parts/rms/out"]),
+                               atol=1e-6, rtol=1e-6)
+    torch.testing.assert_close(plain_model.swiglu_mlp(x, gate, up, down), torch.from_numpy(golden["parts/mlp/out"]),
+                               atol=1e-6, rtol=1e-6)
+
+
+def test_plain_model_matches_the_reference_synthetic_model(golden):
+    """The reference's whole FakeQwen (its own norm, feed-forward and layer modules) through its adapter,
+    whole, in portions and beside another request, and its own dense check (independent_reference)."""
+    import make_golden
+    config = make_golden.FAKE_CONFIG
+    w = make_golden.fixed_weights(config)
+    assert make_golden.weights_checksum(w) == bytes(golden["fake/checksum"]).decode()
+    a, b = make_golden.FAKE_PROMPTS
+    got_a = plain_model.forward_logits(config, w, a)[-1]
+    got_b = plain_model.forward_logits(config, w, b)[-1]
+    for backend in ("blockwise", "materialized"):
+        torch.testing.assert_close(got_a, torch.from_numpy(golden[f"fake/{backend}/whole/a"]), atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(got_b, torch.from_numpy(golden[f"fake/{backend}/whole/b"]), atol=1e-5, rtol=1e-5)
+        torch.testing.assert_close(got_a, torch.from_numpy(golden[f"fake/{backend}/portions/a"]), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(got_a, torch.from_numpy(golden["fake/independent/a"]), atol=1e-5, rtol=1e-5)
 
 
 def test_parts_of_the_plain_model():
