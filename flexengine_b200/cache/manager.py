@@ -4,7 +4,8 @@ and slots for per-request state of fixed size.
 The reference keeps one pool for all layers and one table per request
 (src/flexengine/engine/kv_cache/allocator.py:25-67,103-127); here each cache group (all
 keys, a window of keys, fixed-size state) has its own pool and its own table per
-request, so that layers with different needs do not share a page size or lifetime.
+request, with a page size of its own where its spec names one, so that layers with different
+needs share neither a page size nor a lifetime.
 A request's pages are given back when it ends (allocator.py:103-105) or, in a window
 group, once the window has passed them.  ``reserve`` is atomic across groups.
 
@@ -13,6 +14,7 @@ index 0, values at 1), so one (page, head) tile is contiguous.
 """
 from __future__ import annotations
 
+import math
 from collections import Counter
 from dataclasses import dataclass, field
 
@@ -56,7 +58,9 @@ class StateGroup:
 class CacheManager:
     def __init__(self, group_specs, num_pages, page_size: int, max_requests: int, dtype=torch.float32,
                  device="cpu"):
-        """``num_pages``: pages per paged group (an int for all, or a list per group)."""
+        """``num_pages``: pages per paged group (an int for all, or a list per group).  ``page_size``: tokens a
+        page for groups whose spec names none.  An int ``num_pages`` is meant for pages of that default size: a
+        group with another page size gets as many pages as hold the same number of tokens."""
         self.page_size = int(page_size)
         self.max_requests = int(max_requests)
         self.device = torch.device(device)
@@ -67,12 +71,19 @@ class CacheManager:
             if spec.kind == "state":
                 self.groups.append(StateGroup(spec, self.max_requests, self.device))
             else:
-                n = num_pages[gi] if isinstance(num_pages, (list, tuple)) else num_pages
-                self.groups.append(PagedGroup(spec, n, self.page_size, dtype, self.device))
+                own = int(getattr(spec, "page_size", 0) or self.page_size)
+                if isinstance(num_pages, (list, tuple)):
+                    n = num_pages[gi]
+                else:
+                    n = -(-num_pages * self.page_size // own)
+                self.groups.append(PagedGroup(spec, n, own, dtype, self.device))
         self.requests: dict[str, RequestCache] = {}
         self.free_state_slots = list(range(self.max_requests - 1, -1, -1))
         self._paged = [(gi, g) for gi, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
         self._windowed = [(gi, g) for gi, g in self._paged if g.spec.kind == "window" and g.spec.window > 0]
+        self.chunk_granularity = math.lcm(*[int(getattr(spec, "chunk_granularity", 1)) for spec in self.specs] or [1])
+        # complete pages in every group: what may be shared between requests
+        self.sharing_unit = math.lcm(*[g.page_size for _, g in self._paged] or [1])
 
     # --- sizes -----------------------------------------------------------------------------
     @property
@@ -92,7 +103,8 @@ class CacheManager:
         return min((g.pool.num_pages for _, g in self.paged), default=0)
 
     def capacity_tokens(self) -> int:
-        return self.total_pages * self.page_size
+        """Tokens one request could hold if it had every page."""
+        return min((g.pool.num_pages * g.page_size for _, g in self.paged), default=0)
 
     def tokens_of(self, request_id: str) -> int:
         rc = self.requests.get(request_id)
@@ -118,7 +130,7 @@ class CacheManager:
         return rc
 
     def _pages_needed(self, rc: RequestCache, gi: int, target_tokens: int) -> int:
-        need = -(-target_tokens // self.page_size)
+        need = -(-target_tokens // self.groups[gi].page_size)
         return max(0, need - len(rc.tables[gi]))
 
     def reserve(self, request_id: str, target_tokens: int) -> None:
@@ -130,7 +142,7 @@ class CacheManager:
         fresh = rc is None
         if fresh:
             rc = self.admit(request_id)
-        elif all(len(rc.tables[gi]) * self.page_size >= target_tokens for gi, _ in self._paged):
+        elif all(len(rc.tables[gi]) * g.page_size >= target_tokens for gi, g in self._paged):
             return                      # already reserved (the usual case in decode)
         needs = [(gi, g, self._pages_needed(rc, gi, target_tokens)) for gi, g in self.paged]
         short = [(g.spec.name, n, g.pool.free_pages) for _, g, n in needs if n > g.pool.free_pages]
@@ -146,15 +158,15 @@ class CacheManager:
         rc = self.requests.get(request_id)
         if rc is None:
             return 0
-        return min((len(rc.tables[gi]) for gi, _ in self.paged), default=1 << 62) * self.page_size
+        return min((len(rc.tables[gi]) * g.page_size for gi, g in self.paged), default=1 << 62)
 
     def commit(self, request_id: str, count: int) -> None:
         """``count`` more tokens of the request are now in the cache; pages that a window has
         passed are given back."""
         rc = self.requests[request_id]
         target = rc.tokens + count
-        for gi, _ in self._paged:
-            if len(rc.tables[gi]) * self.page_size < target:
+        for gi, g in self._paged:
+            if len(rc.tables[gi]) * g.page_size < target:
                 raise IndexError("KV slots not reserved")
         rc.tokens = target
         for gi, g in self._windowed:
@@ -162,7 +174,7 @@ class CacheManager:
             # the next query sits at position >= rc.tokens and sees keys t > position - w
             first_needed = rc.tokens - w + 1
             table = rc.tables[gi]
-            for j in range(min(len(table), max(0, first_needed) // self.page_size)):
+            for j in range(min(len(table), max(0, first_needed) // g.page_size)):
                 if table[j] != RELEASED:
                     g.pool.release(table[j])
                     table[j] = RELEASED
@@ -184,24 +196,25 @@ class CacheManager:
         if request_id in self.requests and self.requests[request_id].tokens:
             raise ValueError("request already has cached tokens")
         donor = self.requests[donor_id]
-        pages = tokens // self.page_size
-        if pages * self.page_size > donor.tokens:
+        shared = tokens // self.sharing_unit * self.sharing_unit       # complete pages in every group
+        if shared > donor.tokens:
             raise ValueError("donor has not cached that many complete pages")
+        if any(g.spec.kind != "full" for _, g in self.paged):
+            raise ValueError("only groups that keep every key can share a prefix")
         rc = self.admit(request_id)
         for gi, g in self.paged:
-            if g.spec.kind != "full":
-                raise ValueError("only groups that keep every key can share a prefix")
-            for page in donor.tables[gi][:pages]:
+            pages = donor.tables[gi][:shared // g.page_size]
+            for page in pages:
                 g.pool.retain(page)
-            rc.tables[gi] = list(donor.tables[gi][:pages])
-        rc.tokens = pages * self.page_size
+            rc.tables[gi] = list(pages)
+        rc.tokens = shared
 
     # --- per-step views ------------------------------------------------------------------------
     def slot_mapping(self, request_id: str, gi: int, start: int, count: int) -> list[int]:
         """Flat slot (page * page_size + offset) of tokens start..start+count-1 in group ``gi``."""
         rc = self.requests[request_id]
         table = rc.tables[gi]
-        ps = self.page_size
+        ps = self.groups[gi].page_size
         if start < 0 or start + count > len(table) * ps:
             raise IndexError("KV slots not reserved")
         out = []

@@ -1,43 +1,43 @@
-"""``flexengine <command> [options]``: one dispatcher over sub-commands, in the manner of the
-reference's command line (src/flexengine/serving/cli/__init__.py:8-38).  The server
-commands of the reference are not part of this engine; ``generate`` takes the engine
-options of its ``serve`` command under the same names (src/flexengine/serving/cli/server.py:7-54)."""
+"""``flexengine <command> [options]``.
+
+One program with sub-commands, as the reference has (its ``flexengine serve|benchmark|...``,
+src/flexengine/serving/cli/__init__.py); the commands here are this engine's: the reference's server and
+experiment runners are not part of it.  ``generate`` takes the engine options of the reference's ``serve``
+under the same names (src/flexengine/serving/cli/server.py:7-54).  A command's module is imported only when it
+is chosen, so ``flexengine --help`` does not load PyTorch.
+"""
 from __future__ import annotations
 
-import importlib
+import argparse
 import sys
-from collections.abc import Sequence
+from importlib import import_module
+from typing import NamedTuple
+
+
+class Command(NamedTuple):
+    module: str          # has ``main(argv) -> int``
+    summary: str
+
 
 COMMANDS = {
-    "generate": ("flexengine_b200.cli.generate", "main", "Generate tokens for prompts given as text or token ids"),
-    "replay": ("flexengine_b200.engine.replay", "main", "Replay token ids step by step and write logits"),
-    "random-model": ("flexengine_b200.cli.random_model", "main", "Write a model folder with seeded random weights"),
-    "build": ("flexengine_b200.cli.build", "main", "Compile the CUDA kernel libraries"),
-    "bench": ("flexengine_b200.cli.bench", "main", "Decode and prefill throughput on the Qwen2.5-7B shape (one JSON line)"),
+    "generate": Command("flexengine_b200.cli.generate", "generate tokens for prompts given as text or token ids"),
+    "replay": Command("flexengine_b200.engine.replay", "feed given token ids step by step and write the logits"),
+    "bench": Command("flexengine_b200.bench", "measure decode, prefill and serving workloads (one JSON line)"),
+    "random-model": Command("flexengine_b200.cli.random_model", "write a model folder with seeded random weights"),
+    "build": Command("flexengine_b200.cli.build", "compile the CUDA kernel libraries for sm_100a"),
 }
 
 
-def usage() -> str:
-    lines = ["usage: flexengine <command> [options]", "", "commands:"]
-    width = max(map(len, COMMANDS))
-    lines.extend(f"  {name:<{width}}  {text}" for name, (_, _, text) in COMMANDS.items())
-    return "\n".join(lines)
+def _parser() -> argparse.ArgumentParser:
+    listing = "\n".join(f"  {name:<14}{c.summary}" for name, c in COMMANDS.items())
+    p = argparse.ArgumentParser(prog="flexengine", formatter_class=argparse.RawDescriptionHelpFormatter,
+                                description="A single-GPU inference engine for NVIDIA B200.",
+                                epilog="commands:\n" + listing + "\n\n'flexengine <command> --help' shows a command's options.")
+    p.add_argument("command", choices=list(COMMANDS), metavar="<command>")
+    p.add_argument("options", nargs=argparse.REMAINDER, help="passed to the command")
+    return p
 
 
-def main(argv: Sequence[str] | None = None) -> None:
-    arguments = list(sys.argv[1:] if argv is None else argv)
-    if not arguments or arguments[0] in {"-h", "--help"}:
-        print(usage())
-        return
-    command = arguments.pop(0)
-    if command not in COMMANDS:
-        raise SystemExit(f"unknown command: {command}\n\n{usage()}")
-    module_name, function_name, _ = COMMANDS[command]
-    module = importlib.import_module(module_name)
-    code = getattr(module, function_name)(arguments)
-    if code:
-        raise SystemExit(code)
-
-
-if __name__ == "__main__":
-    main()
+def main(argv=None) -> int:
+    chosen = _parser().parse_args(sys.argv[1:] if argv is None else list(argv))
+    return int(import_module(COMMANDS[chosen.command].module).main(chosen.options) or 0)

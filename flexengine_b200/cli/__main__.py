@@ -1,3 +1,5 @@
+import sys
+
 from . import main
 
-main()
+sys.exit(main())

@@ -10,20 +10,10 @@ host plan and launch a step while the device still runs the one before.
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass, fields
+from dataclasses import dataclass, fields, replace
 
 POLICIES = ("fcfs", "decode_first", "slo_aware", "adaptive")
 DTYPES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp32": "float32"}
-
-
-def matched_kv_blocks(base_blocks: int, base_block_size: int, candidate_block_size: int) -> int:
-    """Pages of another size that hold the same number of tokens (config.py:8-14)."""
-    if min(base_blocks, base_block_size, candidate_block_size) <= 0:
-        raise ValueError("KV block counts and sizes must be positive")
-    total = base_blocks * base_block_size
-    if total % candidate_block_size:
-        raise ValueError("candidate block size must divide total KV token capacity")
-    return total // candidate_block_size
 
 
 @dataclass(frozen=True)
@@ -66,6 +56,14 @@ class EngineConfig:
         object.__setattr__(self, "dtype", DTYPES[self.dtype])
         if self.kv_num_blocks and self.kv_num_blocks * self.kv_block_size < self.max_model_len:
             raise ValueError("KV pool cannot contain one max-length request")
+
+    def with_block_size(self, kv_block_size: int) -> "EngineConfig":
+        """The same settings with pages of another size and as many of them as hold at least the same number of
+        tokens (the reference compares page sizes at equal capacity, src/flexengine/engine/config.py:8-14)."""
+        if kv_block_size <= 0:
+            raise ValueError("kv_block_size must be positive")
+        tokens = self.kv_num_blocks * self.kv_block_size
+        return replace(self, kv_block_size=int(kv_block_size), kv_num_blocks=-(-tokens // int(kv_block_size)))
 
     @classmethod
     def from_env(cls, **overrides) -> "EngineConfig":

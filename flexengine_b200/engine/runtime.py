@@ -1,28 +1,28 @@
-"""The engine: queues, admission, one scheduling iteration per ``step()``, sampling,
-finishing and freeing, and the Python entry point ``generate()``.
+"""The engine: requests come in, take a seat, are run in steps, sampled, and leave.
 
-Semantics follow the reference's runtime (src/flexengine/engine/runtime.py): ``submit``
-validates and enqueues (runtime.py:89-121); ``step`` admits while fewer than
-``max_num_seqs`` run (runtime.py:162-179), plans under the token budget (runtime.py:262),
-reserves pages chunk by chunk and, when pages run out, preempts ONE running request that
-is not planned in this step (lowest priority, then most cached tokens), retries once and
-otherwise leaves the chunk out of the step (runtime.py:273-288); a preempted request gives
-its pages back, goes to the back of the waiting queue and later recomputes its context
-without sampling a second time from it (runtime.py:242-251,318-324); a token in the end-of-
-sequence set finishes with "stop", reaching ``max_tokens`` with "length" (runtime.py:343-346);
-an exception in the executor faults the engine and fails every live request
+What happens is what the reference's runtime does (src/flexengine/engine/runtime.py): ``submit`` checks and queues a
+request (runtime.py:89-121); a step seats waiting requests while fewer than ``max_num_seqs`` run
+(runtime.py:162-179), asks the scheduler for chunks under the token budget (runtime.py:262), and reserves pages
+chunk by chunk; when pages run out ONE running request that is not part of this step is preempted (lowest
+priority, then the one holding most cached tokens), the reservation is tried once more, and otherwise the chunk
+waits for a later step (runtime.py:273-288); a preempted request gives everything back, queues again and later
+recomputes its context without sampling from it a second time (runtime.py:242-251,318-324); a token of the
+end-of-sequence set ends a request with "stop", its ``max_tokens``-th token with "length" (runtime.py:343-346);
+an exception in the executor, or a fault that a kernel recorded, fails every live request and closes the engine
 (runtime.py:349-356).  Logits are asked for only where a token will be sampled.
 
-Unlike the reference, a step is launched before the host has read the tokens of the step before
+How it happens is this engine's own.  A step is launched before the host has read the tokens of the step before
 (``overlap_steps``): sampled tokens stay on the device, the next step takes them from there
-(``StepEntry.carry``), and the host reads them one step late, while the device is busy.  A request's
-``generated_ids`` holds ``PENDING`` in the place of a token that is on its way.  A request that turns
-out to have ended with an end-of-sequence token has then been run one token too far; that token is
-dropped.  Before anyone is preempted the tokens on their way are read, so that preemption and
-recomputation see exact state.
+(``StepEntry.carry``), and the host reads them, together with the kernels' status word, from pinned memory one
+step late, while the device is busy.  Until then ``generated_ids`` holds ``PENDING`` in the token's place.  A
+request that turns out to have ended with an end-of-sequence token has been run one token too far; that token
+is dropped.  A request whose pending token is its last by ``max_tokens`` leaves its seat at once, so that the
+batches are the same, step for step, as without overlap.  Before anyone is preempted the tokens on their way
+are read, so that preemption and recomputation see exact state.
 """
 from __future__ import annotations
 
+import math
 import threading
 import time
 import uuid
@@ -34,15 +34,17 @@ import torch
 from ..cache.manager import CacheManager
 from ..cache.page_pool import CacheExhausted
 from ..config.engine_config import EngineConfig
-from ..observability.traces import TraceWriter, nvtx
+from ..observability.traces import RunTrace, marked
 from ..sampling.sampler import Sampler
 from .request import PENDING, TERMINAL, Event, Request, State
 from .scheduler import Scheduler
 from .step import ModelRunner, StepEntry
 
+TEMPERATURE_RANGE = (0.0, 5.0)          # the reference's bounds (runtime.py:95)
+
 
 class BusyError(RuntimeError):
-    pass
+    """The engine takes no request now: its waiting queue is full, or it has stopped or faulted."""
 
 
 @dataclass
@@ -56,51 +58,57 @@ class GenerationOutput:
 
 @dataclass
 class _InFlight:
-    """The step whose sampled tokens the host has not read yet."""
-    sampled: list                        # [(request, its place in generated_ids)] in the order of ``tokens``
-    tokens: torch.Tensor                 # int32 [len(sampled)], where the logits were
-    host: torch.Tensor | None = None     # pinned copy, complete once ``event`` has passed
-    event: object = None
-    index: dict | None = None            # request id -> place in ``tokens``
+    """A launched step whose sampled tokens the host has not read yet."""
+    places: list                         # [(request, index in its generated_ids)] in the order of ``tokens``
+    tokens: torch.Tensor | None          # int32 [len(places)] on the device
+    where: dict                          # request id -> index in ``tokens`` (for the next step's carry)
+    host: torch.Tensor | None = None     # pinned: the tokens, then the kernels' status word
+    ready: object = None                 # event after the copy into ``host``
+
+
+@dataclass
+class _Counters:
+    steps: int = 0
+    submitted: int = 0
+    ended: int = 0
+    preemptions: int = 0
+    output_tokens: int = 0
 
 
 class Engine:
     def __init__(self, config: EngineConfig, runner: ModelRunner, sampler: Sampler | None = None, tokenizer=None,
                  eos_token_ids=()):
+        if runner.cache.capacity_tokens() < config.max_model_len:
+            raise ValueError("KV pool cannot contain one max-length request")
         self.config = config
         self.runner = runner
         self.cache: CacheManager = runner.cache
         self.sampler = sampler if sampler is not None else Sampler(runner.ops)
         self.tokenizer = tokenizer
-        self.eos_ids = set(eos_token_ids)
+        self.eos_ids = frozenset(int(t) for t in eos_token_ids)
         self.scheduler = Scheduler(config.scheduler_policy, config.max_num_batched_tokens, config.ttft_slo_ms,
-                                   config.itl_slo_ms, config.prefill_chunk_size)
-        if self.cache.capacity_tokens() < config.max_model_len:
-            raise ValueError("KV pool cannot contain one max-length request")
-        self.waiting: deque = deque()
-        self.running: OrderedDict = OrderedDict()
-        self.all_requests: dict = {}
+                                   config.itl_slo_ms, config.prefill_chunk_size,
+                                   granularity=getattr(self.cache, "chunk_granularity", 1))
+        self.waiting: deque = deque()              # arrival order; preempted requests rejoin at the back
+        self.running: OrderedDict = OrderedDict()  # request id -> request, the seats
+        self.all_requests: dict = {}               # every request that has not ended
         self.lock = threading.RLock()
-        self.shutdown = threading.Event()
-        self.worker: threading.Thread | None = None
         self.fault: str | None = None
-        self.step_index = 0
-        self.request_sequence = 0
-        self.completed_count = 0
-        self.preemption_count = 0
-        self.output_tokens = 0
+        self.counters = _Counters()
+        self._closing = threading.Event()
+        self._thread: threading.Thread | None = None
         self._in_flight: _InFlight | None = None
-        self._pinned: list = []
-        self._pinned_at = 0
-        self.trace = TraceWriter(config.trace_dir)
-        self.trace.metadata(config)
+        self._landing: list = []                   # pinned buffers the tokens are copied into, used in turn
+        self._landing_at = 0
+        self.trace = RunTrace(config.trace_dir)
+        self.trace.describe(config)
 
-    # ---- construction from a model folder ----------------------------------------------------
+    # ---- built from a model ------------------------------------------------------------------------------------
     @classmethod
     def from_model_dir(cls, model_dir: str, config: EngineConfig | None = None, tokenizer=None, ops=None) -> "Engine":
         from ..weights.loader import load_model
         config = config or EngineConfig(model=model_dir)
-        _typed, plan, model = load_model(model_dir, config.dtype, config.device)
+        _typed, _plan, model = load_model(model_dir, config.dtype, config.device)
         return cls.from_model(model, config, tokenizer=tokenizer, ops=ops)
 
     @classmethod
@@ -112,365 +120,419 @@ class Engine:
         runner = ModelRunner(model, cache, ops=ops)
         if config.cuda_graph:
             runner.enable_decode_graphs(config.max_num_seqs, config.max_model_len)
-            runner.capture_decode_graphs()         # at start-up, not in the path of the first requests
+            runner.capture_decode_graphs()         # when the engine is built, not in the path of the first requests
         return cls(config, runner, tokenizer=tokenizer, eos_token_ids=plan.eos_token_ids)
 
-    # ---- worker thread (a server would use it; generate() steps inline) --------------------------
-    def start(self) -> None:
-        if self.worker and self.worker.is_alive():
-            return
-        self.shutdown.clear()
-        self.worker = threading.Thread(target=self._worker, name="flexengine-cuda-worker", daemon=True)
-        self.worker.start()
+    # ---- counters under the names callers know -----------------------------------------------------------------
+    @property
+    def preemption_count(self) -> int:
+        return self.counters.preemptions
 
-    def stop(self) -> None:
-        self.shutdown.set()
-        if self.worker:
-            self.worker.join(timeout=20)
+    @property
+    def step_index(self) -> int:
+        return self.counters.steps
+
+    @property
+    def output_tokens(self) -> int:
+        return self.counters.output_tokens
+
+    def snapshot(self) -> dict:
         with self.lock:
-            self._collect()
-            for req in list(self.all_requests.values()):
-                if req.state not in TERMINAL:
-                    self._finish(req, State.CANCELLED, "cancelled")
+            c = self.counters
+            return {"waiting": len(self.waiting), "running": len(self.running), "fault": self.fault,
+                    "cache_used_blocks": self.cache.used_pages, "cache_free_blocks": self.cache.free_pages,
+                    "steps": c.steps, "requests_total": c.submitted, "requests_completed": c.ended,
+                    "preemptions": c.preemptions, "output_tokens": c.output_tokens}
 
-    def _worker(self) -> None:
-        while not self.shutdown.is_set() and not self.fault:
-            if not self.step():
-                time.sleep(self.config.idle_sleep_seconds)
+    # ---- requests come in ---------------------------------------------------------------------------------------
+    def _token_ids(self, prompt) -> list:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("a text prompt needs a tokenizer; pass token ids instead")
+            ids = list(self.tokenizer.encode(prompt, add_special_tokens=False)) if prompt else []
+            if not ids:
+                start = getattr(self.tokenizer, "bos_token_id", None)
+                if not prompt or start is None:
+                    raise ValueError("the prompt is empty")
+                ids = [start]
+            return ids
+        ids = [int(t) for t in prompt]
+        if not ids:
+            raise ValueError("the prompt is empty")
+        vocab = self.runner.vocab_size
+        if min(ids) < 0 or max(ids) >= vocab:
+            raise ValueError(f"token id outside [0, {vocab})")
+        return ids
 
-    # ---- requests ------------------------------------------------------------------------------
     def submit(self, prompt, max_tokens: int = 128, temperature: float = 0.0, top_k: int = 0, priority: int = 0,
                seed: int | None = None) -> Request:
-        """``prompt``: a string (needs a tokenizer) or a list of token ids."""
-        if isinstance(prompt, str):
-            if not prompt:
-                raise ValueError("prompt must be a non-empty string")
-            if self.tokenizer is None:
-                raise ValueError("a string prompt needs a tokenizer; pass token ids instead")
-            ids = list(self.tokenizer.encode(prompt, add_special_tokens=False))
-            if not ids:
-                bos = getattr(self.tokenizer, "bos_token_id", None)
-                if bos is None:
-                    raise ValueError("empty encoded prompt")
-                ids = [bos]
-        else:
-            ids = [int(t) for t in prompt]
-            if not ids:
-                raise ValueError("prompt must hold at least one token id")
-            if min(ids) < 0 or max(ids) >= self.runner.vocab_size:
-                raise ValueError(f"token id outside [0, {self.runner.vocab_size})")
-        if not (1 <= max_tokens <= self.config.max_output_tokens):
-            raise ValueError(f"max_tokens must be between 1 and {self.config.max_output_tokens}")
-        if not (0.0 <= temperature <= 5.0) or top_k < 0:
-            raise ValueError("invalid sampling parameters")
-        if len(ids) + max_tokens > self.config.max_model_len:
-            raise ValueError(f"prompt tokens ({len(ids)}) + max_tokens ({max_tokens}) exceeds max_model_len "
-                             f"({self.config.max_model_len})")
+        """Queue a request.  ``prompt`` is text (needs a tokenizer) or a list of token ids.  Raises ValueError
+        for what can never run and BusyError when the engine takes nothing now."""
+        ids = self._token_ids(prompt)
+        cfg = self.config
+        if not 1 <= max_tokens <= cfg.max_output_tokens:
+            raise ValueError(f"max_tokens={max_tokens} is outside 1..{cfg.max_output_tokens} (max_output_tokens)")
+        low, high = TEMPERATURE_RANGE
+        if not low <= temperature <= high:
+            raise ValueError(f"temperature={temperature} is outside {low}..{high}")
+        if top_k < 0:
+            raise ValueError(f"top_k={top_k} is negative")
+        if len(ids) + max_tokens > cfg.max_model_len:
+            raise ValueError(f"{len(ids)} prompt tokens + max_tokens={max_tokens} exceed max_model_len={cfg.max_model_len}")
         with self.lock:
-            if self.shutdown.is_set() or self.fault:
-                raise BusyError("engine is not accepting requests")
-            if len(self.waiting) >= self.config.max_waiting:
-                raise BusyError("bounded waiting queue is full")
-            req = Request("cmpl-" + uuid.uuid4().hex, ids, max_tokens, float(temperature), int(top_k), int(priority))
-            # the same requests in the same order give the same tokens under every policy
-            req.seed = int(seed) if seed is not None else self.config.random_seed + self.request_sequence
-            self.request_sequence += 1
-            self.waiting.append(req)
-            self.all_requests[req.request_id] = req
-            return req
+            if self.fault or self._closing.is_set():
+                raise BusyError("the engine has stopped" if not self.fault else f"the engine faulted: {self.fault}")
+            if len(self.waiting) >= cfg.max_waiting:
+                raise BusyError(f"{len(self.waiting)} requests are waiting already (max_waiting)")
+            request = Request(f"cmpl-{uuid.uuid4().hex}", ids, int(max_tokens), float(temperature), int(top_k), int(priority))
+            # a default seed that depends only on the order of submission: the same requests in the same order
+            # draw the same tokens under every policy and batching (runtime.py:112-116)
+            request.seed = cfg.random_seed + self.counters.submitted if seed is None else int(seed)
+            self.counters.submitted += 1
+            self.all_requests[request.request_id] = request
+            self.waiting.append(request)
+        return request
 
     def cancel(self, request_id: str) -> bool:
         with self.lock:
-            req = self.all_requests.get(request_id)
-            if req is None or req.state in TERMINAL:
+            request = self.all_requests.get(request_id)
+            if request is None or request.state in TERMINAL:
                 return False
-            self._finish(req, State.CANCELLED, "cancelled")
-            return True
+            self._retire(request, State.CANCELLED, "cancelled")
+        return True
 
-    def _finish(self, req: Request, state: State, reason: str, error: str | None = None) -> None:
-        if req.state in TERMINAL:
-            return
-        req.transition(state)
-        while req.generated_ids and req.generated_ids[-1] == PENDING:      # run one token too far: dropped
-            req.generated_ids.pop()
-        req.finished_at = time.monotonic()
-        req.finish_reason = reason
-        req.error = error
-        self.cache.free(req.request_id)
-        self.running.pop(req.request_id, None)
-        if any(r.request_id == req.request_id for r in self.waiting):
-            self.waiting = deque(r for r in self.waiting if r.request_id != req.request_id)
-        if state is State.FAILED:
-            req.events.put(Event("error", error=error or reason, finish_reason=reason))
-        else:
-            remaining = req.text[len(req.emitted_text):] if req.text.startswith(req.emitted_text) else ""
-            if remaining:
-                req.emitted_text += remaining
-                req.events.put(Event("token", text=remaining))
-            req.events.put(Event("done", finish_reason=reason))
-        self.trace.write("requests", req.snapshot())
-        self.all_requests.pop(req.request_id, None)
-        self.completed_count += 1
-
-    def _admit(self) -> None:
+    # ---- seats ----------------------------------------------------------------------------------------------------
+    def _seat_waiting(self) -> None:
+        """Waiting requests take free seats in queue order.  A seat is a state slot; pages come later, chunk by chunk."""
         while self.waiting and len(self.running) < self.config.max_num_seqs:
-            req = self.waiting.popleft()
-            if req.state in TERMINAL:
+            request = self.waiting.popleft()
+            if request.state in TERMINAL:
                 continue
-            self.cache.admit(req.request_id)          # state slot; no page is taken at admission
-            req.transition(State.RUNNING)
-            self.running[req.request_id] = req
+            self.cache.admit(request.request_id)
+            request.transition(State.RUNNING)
+            self.running[request.request_id] = request
 
-    def _preempt(self, victim: Request) -> None:
-        self._collect()                          # nobody is preempted with a token on its way
-        if victim.state in TERMINAL:
+    def _retire(self, request: Request, state: State, reason: str, error: str | None = None) -> None:
+        """The request ends: its pages and its seat are free, its consumer is told, its report is written."""
+        if request.state in TERMINAL:
             return
-        self.cache.free(victim.request_id)
-        victim.cached_tokens = 0
-        victim.replaying = bool(victim.generated_ids)
-        victim.preemptions += 1
-        victim.transition(State.PREEMPTED)
-        self.running.pop(victim.request_id, None)
-        self.waiting.append(victim)
-        self.preemption_count += 1
+        request.transition(state)
+        request.finish_reason, request.error, request.finished_at = reason, error, time.monotonic()
+        generated = request.generated_ids
+        while generated and generated[-1] == PENDING:       # launched beyond its end, or cancelled with a token on its way
+            generated.pop()
+        rid = request.request_id
+        self.cache.free(rid)
+        self.running.pop(rid, None)
+        self.all_requests.pop(rid, None)
+        if request in self.waiting:
+            self.waiting.remove(request)
+        if state is State.FAILED:
+            request.events.put(Event("error", error=error or reason, finish_reason=reason))
+        else:
+            self._emit_text(request, final=True)
+            request.events.put(Event("done", finish_reason=reason))
+        self.trace.record("requests", request.report())
+        self.counters.ended += 1
 
-    def _reserve_or_preempt(self, proposed: list) -> list:
-        planned = []
-        for chunk in proposed:
-            req = self.running.get(chunk.request_id)
-            if req is None:
+    def preempt(self, victim: Request) -> None:
+        """Take the request's pages and seat; it queues again and recomputes its context when it is seated next."""
+        with self.lock:
+            self._land()                              # nobody is preempted with a token on its way
+            if victim.state in TERMINAL or victim.request_id not in self.running:
+                return
+            self.cache.free(victim.request_id)
+            del self.running[victim.request_id]
+            victim.cached_tokens = 0
+            victim.replaying = len(victim.generated_ids) > 0     # its context ends in a token it has sampled already
+            victim.preemptions += 1
+            victim.transition(State.PREEMPTED)
+            self.waiting.append(victim)
+            self.counters.preemptions += 1
+
+    def _victim_for(self, needy: Request, taken: set) -> Request | None:
+        """Who gives way when ``needy`` finds no page: a seated request outside this step that holds pages;
+        the lowest priority first, among equals the one with most tokens cached."""
+        best = None
+        for other in self.running.values():
+            if other is needy or other.request_id in taken or not self.cache.holds_pages(other.request_id):
                 continue
-            target = chunk.start + len(chunk.input_ids)
-            try:
-                self.cache.reserve(req.request_id, target)
-            except CacheExhausted:
-                if self._in_flight is not None:
-                    # exact state first: requests that have just ended give their pages back, and nobody is
-                    # preempted with a token on its way
-                    self._collect()
-                    if req.request_id not in self.running:
+            if best is None or (other.priority, -other.cached_tokens) < (best.priority, -best.cached_tokens):
+                best = other
+        return best
+
+    # ---- one step -------------------------------------------------------------------------------------------------
+    def _with_pages(self, proposed: list) -> list:
+        """The chunks of ``proposed`` that have their pages, in order.  Up to three tries per chunk: as things are;
+        after the tokens on their way were read (requests that just ended gave pages back); after one preemption."""
+        granted, taken = [], set()
+        for chunk in proposed:
+            request = self.running.get(chunk.request_id)
+            if request is None:
+                continue
+            upto = chunk.start + len(chunk.input_ids)
+            for attempt in ("as is", "after landing", "after preempting"):
+                if attempt == "after landing":
+                    if self._in_flight is None:
                         continue
-                    try:
-                        self.cache.reserve(req.request_id, target)
-                        planned.append(chunk)
-                        continue
-                    except CacheExhausted:
-                        pass
-                selected = {c.request_id for c in planned}
-                victims = [v for v in self.running.values()
-                           if v.request_id != req.request_id and v.request_id not in selected
-                           and self.cache.holds_pages(v.request_id)]
-                if not victims:
-                    continue
-                self._preempt(min(victims, key=lambda r: (r.priority, -r.cached_tokens)))
+                    self._land()
+                elif attempt == "after preempting":
+                    victim = self._victim_for(request, taken)
+                    if victim is None:
+                        break
+                    self.preempt(victim)
+                if request.request_id not in self.running:
+                    break                              # reading tokens ended it
                 try:
-                    self.cache.reserve(req.request_id, target)
+                    self.cache.reserve(request.request_id, upto)
                 except CacheExhausted:
                     continue
-            planned.append(chunk)
-        return planned
+                granted.append(chunk)
+                taken.add(chunk.request_id)
+                break
+        return [c for c in granted if c.request_id in self.running]
 
-    # ---- one scheduling iteration -----------------------------------------------------------------
     def step(self) -> bool:
+        """One scheduling iteration.  False when there was nothing to do."""
         with self.lock:
             if self.fault:
                 return False
-            t0 = time.perf_counter()
-            self._admit()
-            with nvtx("sched/select"):
+            started = time.perf_counter()
+            self._seat_waiting()
+            with marked("sched/select"):
                 proposed = self.scheduler.plan(list(self.running.values()))
-            with nvtx("kv/reserve"):
-                planned = self._reserve_or_preempt(proposed)
-                planned = [c for c in planned if c.request_id in self.running]     # reading tokens may have ended some
-            if not planned:
-                if self._in_flight is not None:
-                    self._collect()          # nothing more to launch: the tokens on their way are the progress
-                    return True
-                return False
-            scheduler_ms = (time.perf_counter() - t0) * 1000.0
-            new_tokens = sum(len(c.input_ids) for c in planned)
-            prefill_tokens = sum(len(c.input_ids) for c in planned if self.running[c.request_id].in_prefill)
-            t1 = time.perf_counter()
+            with marked("kv/reserve"):
+                chunks = self._with_pages(proposed)
+            if not chunks:
+                if self._in_flight is None:
+                    return False
+                self._land()                           # nothing to launch: the tokens on their way are the progress
+                return not self.fault
+            planned_at = time.perf_counter()
+            tokens = sum(len(c.input_ids) for c in chunks)
+            prompt_tokens = sum(len(c.input_ids) for c in chunks if self.running[c.request_id].in_prefill)
             try:
-                with nvtx(f"executor/step batch={len(planned)} tokens={new_tokens}"):
-                    launched = self._launch(planned)
-                previous, self._in_flight = self._in_flight, launched
-                self._read_tokens(previous)              # of the step before, while the device runs this one
+                with marked(f"executor/step batch={len(chunks)} tokens={tokens}"):
+                    launched = self._launch(chunks)
+                earlier, self._in_flight = self._in_flight, launched
+                self._read(earlier)                    # the step before, while the device runs this one
                 if not self.config.overlap_steps:
-                    self._collect()
-            except Exception as ex:  # noqa: BLE001 - any executor failure faults the engine
-                self.fault = f"{type(ex).__name__}: {ex}"
-                self._in_flight = None
-                for req in list(self.all_requests.values()):
-                    if req.state not in TERMINAL:
-                        self._finish(req, State.FAILED, "error", self.fault)
+                    self._land()
+            except Exception as ex:  # noqa: BLE001 - whatever the executor raises closes the engine
+                self._fail_everything(f"{type(ex).__name__}: {ex}")
                 return False
-            executor_ms = (time.perf_counter() - t1) * 1000.0
-            self.step_index += 1
-            if self.config.trace_steps and self.trace.directory:
-                self.trace.write("steps", {
-                    "step": self.step_index, "batch_size": len(planned), "new_tokens": new_tokens,
-                    "prefill_tokens": prefill_tokens, "decode_tokens": new_tokens - prefill_tokens,
-                    "kv_used_blocks": self.cache.used_pages, "waiting": len(self.waiting),
-                    "running": len(self.running), "wall_ms": (time.perf_counter() - t0) * 1000.0,
-                    "scheduler_ms": scheduler_ms, "executor_wall_ms": executor_ms,
-                    "policy": self.config.scheduler_policy, "preemptions": self.preemption_count,
-                })
+            if self.fault:
+                return False
+            done_at = time.perf_counter()
+            self.counters.steps += 1
+            if self.config.trace_steps and self.trace.enabled:
+                # keys: the reference's step records (runtime.py:358-383), which its analysis reads
+                self.trace.record("steps", {
+                    "step": self.counters.steps, "policy": self.config.scheduler_policy, "batch_size": len(chunks),
+                    "new_tokens": tokens, "prefill_tokens": prompt_tokens, "decode_tokens": tokens - prompt_tokens,
+                    "waiting": len(self.waiting), "running": len(self.running),
+                    "kv_used_blocks": self.cache.used_pages, "preemptions": self.counters.preemptions,
+                    "scheduler_ms": (planned_at - started) * 1e3, "executor_wall_ms": (done_at - planned_at) * 1e3,
+                    "wall_ms": (done_at - started) * 1e3})
             return True
 
-    def _launch(self, planned: list) -> _InFlight:
-        """Run the planned chunks and sample; nothing here waits for the device."""
-        before = self._in_flight
+    def _fail_everything(self, why: str) -> None:
+        self.fault = why
+        self._in_flight = None
+        for request in list(self.all_requests.values()):
+            self._retire(request, State.FAILED, "error", why)
+
+    def _launch(self, chunks: list) -> _InFlight:
+        """Run the chunks and sample; nothing here waits for the device."""
+        earlier = self._in_flight
         entries, sampled = [], []
-        for c in planned:
-            req = self.running[c.request_id]
-            ids, carry = c.input_ids, None
-            if ids[-1] == PENDING:                       # a decode step planned on a token that was on its way
-                last = req.generated_ids[-1]
-                if last == PENDING:
-                    ids, carry = [0], before.index[c.request_id]
+        for chunk in chunks:
+            request = self.running[chunk.request_id]
+            ids, carry = chunk.input_ids, None
+            if ids[-1] == PENDING:                     # planned on a token that was on its way
+                newest = request.generated_ids[-1]
+                if newest == PENDING:
+                    ids, carry = [0], earlier.where[chunk.request_id]
                 else:
-                    ids = [last]                         # it has been read since
-            entries.append(StepEntry(c.request_id, ids, [len(ids) - 1] if c.wants_logits else [], carry))
-            if c.wants_logits:
-                sampled.append(req)
-        logits = self.runner.step(entries, before.tokens if before is not None else None)
+                    ids = [newest]                     # it has landed since
+            entries.append(StepEntry(chunk.request_id, ids, [len(ids) - 1] if chunk.wants_logits else [], carry))
+            if chunk.wants_logits:
+                sampled.append(request)
+        logits = self.runner.step(entries, earlier.tokens if earlier is not None else None)
         tokens = None
         if sampled:
             tokens = self.sampler.sample_on_device(logits, [r.temperature for r in sampled], [r.top_k for r in sampled],
                                                    [r.seed for r in sampled], [len(r.generated_ids) for r in sampled])
         now = time.monotonic()
         places = []
-        for chunk in planned:
-            req = self.running[chunk.request_id]
-            if req.first_scheduled_at is None:
-                req.first_scheduled_at = now
-            req.cached_tokens += len(chunk.input_ids)
-            if req.in_prefill:
+        for chunk in chunks:
+            request = self.running[chunk.request_id]
+            if request.first_scheduled_at is None:
+                request.first_scheduled_at = now
+            request.cached_tokens += len(chunk.input_ids)
+            if not chunk.wants_logits:
+                request.replaying = request.replaying and request.in_prefill      # a recomputed context gives no second token
                 continue
-            if req.replaying:
-                # the recomputed context already gave its token before the preemption
-                req.replaying = False
-                continue
-            req.generated_ids.append(PENDING)
-            places.append((req, len(req.generated_ids) - 1))
-            if len(req.generated_ids) >= req.max_tokens:
-                # the token on its way is its last whatever it is: its seat and its pages serve others from the next
-                # step on (what that step writes there comes after this one on the stream); the request itself ends
-                # when the token has been read
-                self.cache.free(req.request_id)
-                self.running.pop(req.request_id, None)
-        assert [r.request_id for r, _ in places] == [r.request_id for r in sampled]
-        record = _InFlight(places, tokens, index={r.request_id: i for i, (r, _) in enumerate(places)})
+            request.generated_ids.append(PENDING)
+            places.append((request, len(request.generated_ids) - 1))
+            if len(request.generated_ids) >= request.max_tokens:
+                # whatever the token is, it is the last: seat and pages serve others from the next step on (what
+                # that step writes there comes after this one on the stream); the request ends when the token lands
+                self.cache.free(request.request_id)
+                del self.running[request.request_id]
+        record = _InFlight(places, tokens, {r.request_id: i for i, (r, _) in enumerate(places)})
         if tokens is not None and tokens.device.type == "cuda":
-            # one of a few pinned buffers kept for good (two records are alive at most): allocating pinned memory
-            # at every step costs a call into the driver now and then
-            if not self._pinned or self._pinned[0].numel() < tokens.numel():
-                self._pinned = [torch.empty(max(tokens.numel(), self.config.max_num_seqs), dtype=tokens.dtype, pin_memory=True)
-                                for _ in range(4)]
-            self._pinned_at = (self._pinned_at + 1) % len(self._pinned)
-            record.host = self._pinned[self._pinned_at][:tokens.numel()]
-            record.host.copy_(tokens, non_blocking=True)
-            record.event = torch.cuda.Event()
-            record.event.record()
+            self._copy_out(record)
         return record
 
+    def _copy_out(self, record: _InFlight) -> None:
+        """Start the copy of the sampled tokens and of the kernels' status word into pinned memory."""
+        n = record.tokens.numel()
+        if not self._landing or self._landing[0].numel() < n + 1:
+            # a few buffers kept for good (two records are alive at most): pinning memory at every step would cost
+            # a call into the driver each time
+            size = max(n, self.config.max_num_seqs) + 1
+            self._landing = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._landing_at = (self._landing_at + 1) % len(self._landing)
+        record.host = self._landing[self._landing_at][:n + 1]
+        record.host[:n].copy_(record.tokens, non_blocking=True)
+        word = getattr(self.runner.ops, "status_word", None)
+        if word is not None:
+            record.host[n:].copy_(word(record.tokens.device), non_blocking=True)
+        else:
+            record.host[n] = 0
+        record.ready = torch.cuda.Event()
+        record.ready.record()
+
+    # ---- tokens come back ----------------------------------------------------------------------------------------
     def drain(self) -> None:
-        """Wait for the step that was launched last and take its tokens in: afterwards no request
-        holds a token that the host has not read."""
+        """Wait for the step launched last and take its tokens in: afterwards no request holds ``PENDING``."""
         with self.lock:
-            self._collect()
+            self._land()
 
-    def _collect(self) -> None:
-        """Read the tokens that are on their way, if any."""
+    def _land(self) -> None:
         record, self._in_flight = self._in_flight, None
-        self._read_tokens(record)
+        self._read(record)
 
-    def _read_tokens(self, record: _InFlight | None) -> None:
-        if record is None or not record.sampled:
+    def _read(self, record: _InFlight | None) -> None:
+        if record is None or not record.places:
             return
-        if record.event is not None:
-            record.event.synchronize()
-            values = record.host.tolist()
+        if record.ready is not None:
+            record.ready.synchronize()
+            *values, status = record.host.tolist()
         else:
             values = record.tokens.tolist()
+            word = getattr(self.runner.ops, "status_word", None)
+            status = int(word(record.tokens.device).item()) if word is not None else 0
+        if status:
+            # a kernel skipped an index it could not use or gave up a bounded wait: what was sampled from such a
+            # step is not to be trusted, and neither is anything launched after it
+            explain = getattr(self.runner.ops, "describe_status", None)
+            self._fail_everything("kernel status: " + (explain(status) if explain else str(status)))
+            return
         now = time.monotonic()
-        for (req, place), token in zip(record.sampled, values):
-            if req.state in TERMINAL:
-                continue                                  # ended or cancelled meanwhile: one token too far
-            self._accept_token(req, place, int(token), now)
+        for (request, place), token in zip(record.places, values):
+            if request.state not in TERMINAL:          # else it ended or was cancelled meanwhile: one token too far
+                self._take_token(request, place, int(token), now)
 
-    def _accept_token(self, req: Request, place: int, token: int, now: float) -> None:
-        req.generated_ids[place] = token
-        known = place + 1                                 # a later place may hold the next token on its way
-        if req.first_token_at is None:
-            req.first_token_at = now
-        req.last_token_at = now
-        req.token_times.append(now)
-        self.output_tokens += 1
-        if self.tokenizer is not None:
-            req.text = self.tokenizer.decode(req.generated_ids[:known], skip_special_tokens=True,
-                                             clean_up_tokenization_spaces=False)
-            # a trailing replacement character may still be completed by the next tokens
-            stable = req.text.rstrip("\ufffd")
-            delta = stable[len(req.emitted_text):] if stable.startswith(req.emitted_text) else ""
-            if delta:
-                req.emitted_text += delta
-                req.events.put(Event("token", text=delta, token_id=token))
+    def _take_token(self, request: Request, place: int, token: int, now: float) -> None:
+        request.generated_ids[place] = token
+        if request.first_token_at is None:
+            request.first_token_at = now
+        request.last_token_at = now
+        request.token_times.append(now)
+        self.counters.output_tokens += 1
+        if self.tokenizer is None:
+            request.events.put(Event("token", token_id=token))
         else:
-            req.events.put(Event("token", token_id=token))
+            self._emit_text(request, upto=place + 1, token=token)
         if token in self.eos_ids:
-            self._finish(req, State.FINISHED, "stop")
-        elif known >= req.max_tokens:
-            self._finish(req, State.FINISHED, "length")
+            self._retire(request, State.FINISHED, "stop")
+        elif place + 1 >= request.max_tokens:
+            self._retire(request, State.FINISHED, "length")
 
-    # ---- the Python entry point ----------------------------------------------------------------------
+    def _emit_text(self, request: Request, upto: int | None = None, token: int | None = None, final: bool = False) -> None:
+        """Decode what is known of the request's tokens and send the text that is new and settled: a trailing
+        replacement character may yet be completed by the next token, so it is held back until the end."""
+        if self.tokenizer is None:
+            return
+        if not final:
+            request.text = self.tokenizer.decode(request.generated_ids[:upto], skip_special_tokens=True,
+                                                 clean_up_tokenization_spaces=False)
+        settled = request.text if final else request.text.rstrip("\ufffd")
+        if settled.startswith(request.emitted_text) and len(settled) > len(request.emitted_text):
+            fresh = settled[len(request.emitted_text):]
+            request.emitted_text = settled
+            request.events.put(Event("token", text=fresh, token_id=token))
+
+    # ---- entry points -----------------------------------------------------------------------------------------------
     def generate(self, prompts, max_tokens: int = 128, temperature: float = 0.0, top_k: int = 0,
                  seed: int | None = None, max_steps: int | None = None) -> list:
-        """Generate for every prompt (strings or lists of token ids) and return the outputs in
-        order.  Runs ``step()`` inline until all are done; prompts beyond the waiting bound are
-        submitted as room appears."""
-        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+        """Generate for every prompt (text, or lists of token ids) and return the outputs in the order given.
+        Steps inline until all have ended; prompts beyond the waiting bound are submitted as room appears.
+        ``seed``: prompt i draws with ``seed + i``."""
+        if isinstance(prompts, str) or (len(prompts) > 0 and isinstance(prompts[0], int)):
             prompts = [prompts]
-        pending = deque(enumerate(prompts))
-        requests: dict = {}
+        requests: list = []
         steps = 0
-        while pending or any(r.state not in TERMINAL for r in requests.values()):
-            while pending and len(self.waiting) < self.config.max_waiting:
-                i, p = pending.popleft()
-                s = None if seed is None else seed + i
-                requests[i] = self.submit(p, max_tokens=max_tokens, temperature=temperature, top_k=top_k, seed=s)
-            progressed = self.step()
+        while True:
+            while len(requests) < len(prompts) and len(self.waiting) < self.config.max_waiting:
+                i = len(requests)
+                requests.append(self.submit(prompts[i], max_tokens=max_tokens, temperature=temperature, top_k=top_k,
+                                            seed=None if seed is None else seed + i))
+            alive = [r for r in requests if r.state not in TERMINAL]
+            if not alive and len(requests) == len(prompts):
+                break
+            moved = self.step()
             steps += 1
             if self.fault:
                 raise RuntimeError(f"engine fault: {self.fault}")
-            if not progressed and not pending and any(r.state not in TERMINAL for r in requests.values()):
+            if not moved and len(requests) == len(prompts) and any(r.state not in TERMINAL for r in requests):
                 raise RuntimeError("the engine made no progress: the page pool cannot hold any waiting request")
             if max_steps is not None and steps >= max_steps:
                 break
         self.drain()
         return [GenerationOutput(r.request_id, r.prompt_ids, list(r.generated_ids), r.text, r.finish_reason)
-                for r in (requests[i] for i in sorted(requests))]
+                for r in requests]
 
-    def snapshot(self) -> dict:
+    def start(self) -> None:
+        """Serve from a thread of its own: ``submit`` from any thread, read ``Request.events``."""
+        if self._thread is not None and self._thread.is_alive():
+            return
+        self._closing.clear()
+
+        def serve():
+            while not (self._closing.is_set() or self.fault):
+                if not self.step():
+                    time.sleep(self.config.idle_sleep_seconds)
+
+        self._thread = threading.Thread(target=serve, name="flexengine-steps", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        """Stop serving; whatever has not ended is cancelled and gives its pages back."""
+        self._closing.set()
+        if self._thread is not None:
+            self._thread.join(timeout=20)
         with self.lock:
-            return {"waiting": len(self.waiting), "running": len(self.running),
-                    "cache_used_blocks": self.cache.used_pages, "cache_free_blocks": self.cache.free_pages,
-                    "steps": self.step_index, "fault": self.fault, "requests_total": self.request_sequence,
-                    "requests_completed": self.completed_count, "preemptions": self.preemption_count,
-                    "output_tokens": self.output_tokens}
+            self._land()
+            for request in list(self.all_requests.values()):
+                self._retire(request, State.CANCELLED, "cancelled")
+        self.trace.close()
 
 
 def pages_that_fit(plan, config: EngineConfig, dtype) -> int:
-    """Pages per paged group that fill ``kv_memory_fraction`` of the device memory now free."""
+    """Pages per paged cache group that fill ``kv_memory_fraction`` of the device memory that is free now."""
     if not str(config.device).startswith("cuda"):
-        raise ValueError("kv_num_blocks=0 (size from free memory) needs a CUDA device")
+        raise ValueError("kv_num_blocks=0 (size the pool from free memory) needs a CUDA device")
     free, _total = torch.cuda.mem_get_info(torch.device(config.device))
-    itemsize = torch.empty((), dtype=dtype).element_size()
-    per_page = sum(2 * g.slots * g.kv_heads * g.head_dim * config.kv_block_size * itemsize
-                   for g in plan.cache_groups if g.kind != "state")
-    pages = int(free * config.kv_memory_fraction) // max(per_page, 1)
-    need = -(-config.max_model_len // config.kv_block_size)
+    width = torch.empty((), dtype=dtype).element_size()
+    page_bytes = sum(2 * g.slots * g.kv_heads * g.head_dim * (g.page_size or config.kv_block_size) * width
+                     for g in plan.cache_groups if g.kind != "state")
+    pages = int(free * config.kv_memory_fraction) // max(page_bytes, 1)
+    smallest = min((g.page_size or config.kv_block_size for g in plan.cache_groups if g.kind != "state"),
+                   default=config.kv_block_size)
+    need = math.ceil(config.max_model_len / smallest)
     if pages < need:
         raise ValueError(f"free device memory holds {pages} pages; one request of max_model_len needs {need}")
     return pages

@@ -111,13 +111,13 @@ class ModelRunner:
     def _reserve(self, entries) -> None:
         """Reserve for the whole batch or for none of it."""
         cache = self.cache
-        held, page_size, paged = cache.requests, cache.page_size, [gi for gi, _ in cache.paged]
+        held, paged = cache.requests, cache.paged
         for e in entries:
             rc = held.get(e.request_id)
             if rc is None:
                 break
             need = rc.tokens + len(e.tokens)
-            if any(len(rc.tables[gi]) * page_size < need for gi in paged):
+            if any(len(rc.tables[gi]) * g.page_size < need for gi, g in paged):
                 break
         else:
             return                      # the scheduler reserved already
@@ -125,7 +125,8 @@ class ModelRunner:
         try:
             for e in entries:
                 target = cache.tokens_of(e.request_id) + len(e.tokens)
-                before = cache.reserved_tokens(e.request_id) if e.request_id in cache.requests else None
+                rc = cache.requests.get(e.request_id)
+                before = [len(rc.tables[gi]) for gi, _ in paged] if rc is not None else None
                 cache.reserve(e.request_id, target)
                 made.append((e.request_id, before))
         except Exception:
@@ -133,13 +134,12 @@ class ModelRunner:
             for rid, before in made:
                 if before is None:
                     cache.free(rid)
-                else:
-                    rc = cache.requests[rid]
-                    keep = before // cache.page_size
-                    for gi, g in cache.paged:
-                        for page in rc.tables[gi][keep:]:
-                            g.pool.release(page)
-                        del rc.tables[gi][keep:]
+                    continue
+                rc = cache.requests[rid]
+                for (gi, g), keep in zip(paged, before):
+                    for page in rc.tables[gi][keep:]:
+                        g.pool.release(page)
+                    del rc.tables[gi][keep:]
             raise
 
     def _staging(self, count: int) -> torch.Tensor:
@@ -191,14 +191,18 @@ class ModelRunner:
         return [dev[o:o + s] for o, s in zip(offsets, sizes)]
 
     # ------------------------------------------------------------------------------------------
-    def _metadata(self, entries, pad_to: int = 0, max_pages: int = 0, carrying: bool = False):
+    def _metadata(self, entries, pad_to: int = 0, max_pages=None, carrying: bool = False):
         """The step's index arrays on the host.  ``pad_to`` > len(entries) appends padding requests of
         one token each (token 0 at position 0, no cache write, state slot -1, page 0) so that a
-        batch fits a fixed shape; ``max_pages`` fixes the width of the block tables.  ``carrying``
+        batch fits a fixed shape; ``entries`` may then be empty (the stand-in batch a graph is captured
+        with).  ``max_pages`` fixes the width of each group's block table.  ``carrying``
         appends, for entries whose token is still on the device, the row to fill and where it comes
-        from (one pair per request with a fixed shape, row -1 where nothing is carried)."""
+        from (one pair per request with a fixed shape, row -1 where nothing is carried).
+
+        A padding request must leave no trace: kernels skip cache slot -1, and a part that keeps
+        per-request state skips state slot -1 (``parts.base``)."""
         cache = self.cache
-        held, ps = cache.requests, cache.page_size
+        held = cache.requests
         caches = [held.get(e.request_id) for e in entries]
         starts = [rc.tokens if rc else 0 for rc in caches]
         lengths = [len(e.tokens) for e in entries]
@@ -206,7 +210,7 @@ class ModelRunner:
         all_lengths = lengths + [1] * pad
         all_starts = starts + [0] * pad
         R = len(all_lengths)
-        single = max(lengths) == 1                  # a decode step: one token a request
+        single = max(all_lengths) == 1              # a decode step: one token a request
         if single:
             token_ids = [e.tokens[0] for e in entries] + [0] * pad
             positions = all_starts
@@ -230,11 +234,12 @@ class ModelRunner:
                   np.asarray(all_starts, dtype=np.int32), np.asarray(ctx_len, dtype=np.int32),
                   np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32)]
         widths = []
+        longest = max(ctx_len)
         for gi, g in enumerate(cache.groups):
             if not isinstance(g, PagedGroup):
                 widths.append(0)
                 continue
-            refs = g.pool.refs
+            ps, refs = g.page_size, g.pool.refs
             slots = []
             for e, rc, s, n in zip(entries, caches, starts, lengths):
                 table = rc.tables[gi]
@@ -244,7 +249,7 @@ class ModelRunner:
                 else:
                     slots.extend(cache.slot_mapping(e.request_id, gi, s, n))      # checks and messages live there
             slots += [-1] * pad
-            width = max_pages or max(1, max(-(-c // ps) for c in ctx_len))
+            width = max_pages[gi] if max_pages else max(1, -(-longest // ps))
             bt = np.full((R, width), -1, dtype=np.int32)
             for r, rc in enumerate(caches):
                 t = rc.tables[gi]
@@ -260,7 +265,7 @@ class ModelRunner:
                 carried += [(-1, 0)] * pad
             arrays += [np.asarray([c[0] for c in carried], dtype=np.int32), np.asarray([c[1] for c in carried], dtype=np.int32)]
         info = dict(T=len(token_ids), R=R, rows=len(logit_rows), starts=all_starts, lengths=all_lengths,
-                    state_slots=state_slots, widths=widths, max_q_len=max(all_lengths), max_ctx_len=max(ctx_len),
+                    state_slots=state_slots, widths=widths, max_q_len=max(all_lengths), max_ctx_len=longest,
                     request_ids=[e.request_id for e in entries])
         return arrays, info
 
@@ -272,7 +277,7 @@ class ModelRunner:
          ctx.state_slots, ctx.logit_rows) = dev[:8]
         k = 8
         for gi, g in enumerate(cache.groups):
-            view = GroupView(g, cache.page_size)
+            view = GroupView(g, getattr(g, "page_size", 0))
             if isinstance(g, PagedGroup):
                 view.max_pages = info["widths"][gi]
                 view.slot_mapping = dev[k]
@@ -309,38 +314,29 @@ class ModelRunner:
             b *= 2
         buckets.append(max_batch)
         self._graph_buckets = buckets
-        self._graph_max_pages = -(-max_model_len // self.cache.page_size)
+        self._graph_max_pages = [-(-max_model_len // g.page_size) if isinstance(g, PagedGroup) else 0
+                                 for g in self.cache.groups]
         self._graph_max_len = max_model_len
         self._graphs = {}
         self._graph_pool = torch.cuda.graph_pool_handle()
 
     def capture_decode_graphs(self) -> int:
-        """Capture every bucket now, with stand-in requests of one token, instead of at the first step that
-        needs it (a capture takes tens of milliseconds).  Buckets for which the pool has no pages to spare are
-        left for later.  Returns how many graphs exist afterwards."""
-        from ..cache.page_pool import CacheExhausted
-        replays = self.graph_replays
+        """Capture every bucket now instead of at the first step that needs it (a capture takes tens of
+        milliseconds).  Returns how many graphs exist afterwards."""
         for bucket in self._graph_buckets:
-            if bucket in self._graphs:
-                continue
-            names = [f"__graph_capture_{i}" for i in range(bucket)]
-            try:
-                for name in names:
-                    self.cache.reserve(name, 1)
-                self._graph_step([StepEntry(name, [0], [0]) for name in names])
-            except CacheExhausted:
-                pass
-            finally:
-                for name in names:
-                    self.cache.free(name)
+            self._graph_for(bucket)
         torch.cuda.synchronize(self.device)
-        self.graph_replays = replays               # the stand-in steps are not part of anyone's count
         return len(self._graphs)
 
-    def _graph_for(self, bucket: int, arrays: list, info: dict):
-        """Capture the forward pass for ``bucket`` requests of one token (first use only)."""
+    def _graph_for(self, bucket: int):
+        """The graph of the forward pass for ``bucket`` requests of one token; captured at first use.
+
+        Warm-up and capture run a stand-in batch of padding requests only: no cache slot is written and no
+        state slot touched, so capturing never advances anybody's state, whenever it happens; the real
+        requests of the step that asked for the bucket are then run by replaying the graph, once."""
         if bucket in self._graphs:
             return self._graphs[bucket]
+        arrays, info = self._metadata([], pad_to=bucket, max_pages=self._graph_max_pages, carrying=True)
         sizes = [len(a) for a in arrays]
         _offsets, total = self._layout(sizes)
         with torch.inference_mode(False):
@@ -348,6 +344,7 @@ class ModelRunner:
         dev = self._upload(arrays, into=static)
         info = dict(info, max_ctx_len=self._graph_max_len)       # fixes how decode attention splits the keys
         ctx = self._context(dev, info)
+        launches_base = getattr(self.ops, "launches", 0)
         # run once outside a graph on a side stream: libraries set themselves up, scratch is allocated
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -368,8 +365,10 @@ class ModelRunner:
             finally:
                 graph.capture_end()
         torch.cuda.current_stream().wait_stream(side)
-        record = dict(graph=graph, static=static, logits=logits, total=total, views=dev,
-                      launches=getattr(self.ops, "launches", 0) - launches_before)
+        launches = getattr(self.ops, "launches", 0) - launches_before
+        if hasattr(self.ops, "launches"):
+            self.ops.launches = launches_base                    # the stand-in runs are nobody's launches
+        record = dict(graph=graph, static=static, logits=logits, total=total, launches=launches)
         self._graphs[bucket] = record
         return record
 
@@ -380,11 +379,10 @@ class ModelRunner:
             return None
         if max(self.cache.tokens_of(e.request_id) for e in entries) + 1 > self._graph_max_len:
             return None
+        record = self._graph_for(bucket)
         # the carry arrays are always part of a bucket's buffer, so that its layout does not change
-        arrays, info = self._metadata(entries, pad_to=bucket, max_pages=self._graph_max_pages, carrying=True)
-        fresh = bucket not in self._graphs
-        record = self._graph_for(bucket, arrays, info)
-        dev = record["views"] if fresh else self._upload(arrays, into=record["static"])
+        arrays, _info = self._metadata(entries, pad_to=bucket, max_pages=self._graph_max_pages, carrying=True)
+        dev = self._upload(arrays, into=record["static"])
         if carried is not None:
             self.ops.carry_tokens(dev[0], dev[-2], dev[-1], carried)
         record["graph"].replay()

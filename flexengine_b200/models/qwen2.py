@@ -37,7 +37,8 @@ def build_qwen2_plan(cfg: Qwen2Config) -> ModelPlan:
     bindings = [WeightBinding(("embedding", "weight"), (src("model.embed_tokens.weight", v, h),)),
                 WeightBinding(("final_norm", "weight"), (src("model.norm.weight", h),), kind="vector")]
     if cfg.tie_word_embeddings:
-        bindings.append(WeightBinding(("lm_head", "weight"), alias_of=("embedding", "weight")))
+        bindings.append(WeightBinding(("lm_head", "weight"), alias_of=("embedding", "weight"),
+                                      absent=("lm_head.weight",), why="tie_word_embeddings is true"))
     else:
         bindings.append(WeightBinding(("lm_head", "weight"), (src("lm_head.weight", v, h),)))
     for l in range(cfg.num_hidden_layers):
@@ -61,8 +62,10 @@ def build_qwen2_plan(cfg: Qwen2Config) -> ModelPlan:
     # random initialisation: matrices and biases N(0, 0.02), norm weights 1 + N(0, 0.01)
     init = {"default": ("normal", 0.0, 0.02), "suffix": {"layernorm.weight": ("normal", 1.0, 0.01),
                                                           "model.norm.weight": ("normal", 1.0, 0.01)}}
+    sizes = {"vocab_size": v, "hidden_size": h}
     return ModelPlan(architecture=Qwen2Config.ARCHITECTURE, vocab_size=v, hidden_size=h, layers=layers, run=run,
                      cache_groups=groups, final_norm=norm, bindings=bindings,
+                     embedding=PartSpec("token_table", sizes), head=PartSpec("linear", sizes),
                      eos_token_ids=cfg.eos_token_ids, bos_token_id=cfg.bos_token_id, init=init)
 
 

@@ -1,3 +1,3 @@
-from .traces import TraceWriter, nvtx
+from .traces import RunTrace, marked
 
-__all__ = ["TraceWriter", "nvtx"]
+__all__ = ["RunTrace", "marked"]

@@ -10,7 +10,13 @@ Interfaces
 Every part:      ``parameter_shapes() -> {local name: (shape, kind)}`` with kind in
                  {"matrix", "vector", "int"}; ``bind({local name: tensor})``.
 Mixer:           ``cache_need() -> dict | None`` (what cache group it needs) and
-                 ``forward(ctx, h, entry) -> delta [T, hidden]``.
+                 ``forward(ctx, h, entry) -> delta [T, hidden]``.  A mixer that keeps per-request
+                 state reads and writes ``ctx.groups[g].state(slot)[ctx.state_slots[r]]`` for request r.
+                 **A state slot below 0 is a padding request** (a batch padded to a fixed shape for a
+                 CUDA graph): the mixer touches no state for it, and what it returns for its rows is
+                 never read.  The same holds for cache slot -1 in ``slot_mapping``: nothing is written.
+                 Under CUDA graphs the slots must be taken from the device tensors (``ctx.state_slots``),
+                 not from their host copies, whose values a captured graph would keep for good.
 FeedForward:     ``forward(ctx, h) -> delta [T, hidden]``.
 Norm:            ``forward(ctx, residual, delta, rows=None) -> h``: adds ``delta`` (may be None)
                  to the float32 residual stream in place and returns the normalised rows
@@ -24,13 +30,17 @@ PositionEncoding: ``rotary_table(device)`` -> (inv_freq float32 [rot/2], rot) fo
                  absolute positions.
 Block:           ``forward(ctx, residual, pending, entry) -> pending``: the arrangement of
                  norms, mixer and feed-forward around the residual stream.
+Embedding:       ``forward(ctx) -> residual``: the float32 residual stream [T, hidden] of the step's
+                 tokens (``ctx.token_ids``), which the blocks then add to in place.
+Head:            ``forward(ctx, h) -> logits``: float32 [rows, vocab] from the final norm's output
+                 rows (the rows whose logits are wanted, nothing else reaches it).
 """
 from __future__ import annotations
 
 from typing import Callable
 
 _REGISTRIES: dict[str, dict[str, Callable]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
 }
 
 
@@ -56,6 +66,14 @@ def register_position(kind: str, factory: Callable) -> None:
 
 def register_block(kind: str, factory: Callable) -> None:
     _register("block", kind, factory)
+
+
+def register_embedding(kind: str, factory: Callable) -> None:
+    _register("embedding", kind, factory)
+
+
+def register_head(kind: str, factory: Callable) -> None:
+    _register("head", kind, factory)
 
 
 def build_part(family: str, spec):
@@ -111,6 +129,16 @@ class FeedForward(Part):
 
 class Norm(Part):
     def forward(self, ctx, residual, delta, rows=None):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, ctx):  # pragma: no cover - interface
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, ctx, h):  # pragma: no cover - interface
         raise NotImplementedError
 
 

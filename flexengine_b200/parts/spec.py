@@ -30,6 +30,10 @@ class CacheGroupSpec:
     kind "state":  a fixed-size per-request slot (``state_shape`` elements of ``state_dtype``),
                    zeroed at admission.
     ``slots`` is the number of cache slots in the group (one per run entry that writes).
+    ``page_size``: tokens per page of this group; 0 takes the engine's ``kv_block_size``.
+    ``chunk_granularity``: portions of a prompt that do not end it must be multiples of this many
+    tokens (a mixer whose state advances in blocks); the scheduler rounds to the least common
+    multiple over the groups.
     """
     name: str
     kind: str
@@ -39,8 +43,12 @@ class CacheGroupSpec:
     window: int = 0
     state_shape: tuple = ()
     state_dtype: str = "float32"
+    page_size: int = 0
+    chunk_granularity: int = 1
 
     def __post_init__(self):
+        if self.page_size < 0 or self.chunk_granularity < 1:
+            raise ValueError("page_size must be >= 0 and chunk_granularity >= 1")
         if self.kind not in ("full", "window", "state"):
             raise ValueError(f"unknown cache group kind {self.kind!r}")
         if self.kind == "window" and self.window <= 0:
@@ -84,7 +92,8 @@ class WeightBinding:
     ``target`` is ("embedding"|"final_norm"|"lm_head", local) or ("layer", i, part, local)
     with part in {"mixer", "feed_forward", "norm"}.  Several sources are concatenated
     along dim 0 in the given order.  ``alias_of`` binds the target to another target's
-    storage instead (tied embeddings); then ``sources`` is empty.
+    storage instead (tied embeddings); then ``sources`` is empty, and ``absent`` may name
+    checkpoint tensors whose presence contradicts the alias (``why`` says what they contradict).
     ``kind`` is "matrix" (kept in the compute dtype, bfloat16 or as stored when 32-bit),
     "vector" (norm weights and biases; held in float32, which is lossless) or
     "int" (integer tables, int32).
@@ -93,6 +102,8 @@ class WeightBinding:
     sources: tuple = ()
     alias_of: tuple | None = None
     kind: str = "matrix"
+    absent: tuple = ()
+    why: str = ""
 
 
 @dataclass(frozen=True)
@@ -105,6 +116,10 @@ class ModelPlan:
     cache_groups: Sequence[CacheGroupSpec]
     final_norm: PartSpec
     bindings: Sequence[WeightBinding]
+    # how the residual stream starts and how logits are made of it; None: a token table and a
+    # bias-free vocabulary product of the plan's sizes
+    embedding: PartSpec | None = None
+    head: PartSpec | None = None
     eos_token_ids: tuple = ()
     bos_token_id: int | None = None
     # statistics of random initialisation, by binding kind / local name

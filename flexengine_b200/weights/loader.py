@@ -61,9 +61,10 @@ def check_against_plan(plan, entries: dict) -> None:
         if e.dtype not in allowed:
             wrong_dtype.append((name, e.dtype, allowed))
     other = []
-    tied = [b for b in plan.bindings if b.alias_of is not None]
-    if tied and "lm_head.weight" in entries and "lm_head.weight" in unexpected:
-        other.append("lm_head.weight is present although tie_word_embeddings is true")
+    for b in plan.bindings:
+        if b.alias_of is not None:
+            other += [f"{name} is present although {b.why or 'the plan binds its target to another tensor'}"
+                      for name in b.absent if name in entries]
     if missing or unexpected or wrong_shape or wrong_dtype:
         raise CheckpointError(missing, unexpected, wrong_shape, wrong_dtype, other)
 

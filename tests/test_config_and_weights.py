@@ -8,7 +8,7 @@ import torch
 
 import helpers
 import plain_model
-from flexengine_b200.config import (ConfigError, EngineConfig, Qwen2Config, known_architectures, matched_kv_blocks,
+from flexengine_b200.config import (ConfigError, EngineConfig, Qwen2Config, known_architectures,
                                     resolve)
 from flexengine_b200.weights import (CheckpointError, CheckpointReader, load_model, random_model, write_random_model,
                                      write_safetensors)
@@ -59,7 +59,9 @@ def test_registry():
 
 
 def test_engine_config_checks_and_environment(monkeypatch):
-    assert matched_kv_blocks(512, 16, 8) == 1024
+    other = EngineConfig(kv_num_blocks=512, kv_block_size=16).with_block_size(8)
+    assert (other.kv_num_blocks, other.kv_block_size) == (1024, 8)
+    assert EngineConfig(kv_num_blocks=130, kv_block_size=16).with_block_size(32).kv_num_blocks == 65
     with pytest.raises(ValueError, match="KV pool cannot contain"):
         EngineConfig(kv_num_blocks=4, kv_block_size=16, max_model_len=2048)
     with pytest.raises(ValueError, match="scheduler_policy"):
@@ -132,7 +134,7 @@ def test_load_binds_by_name_and_keeps_precisions(folder):
     assert mixer.qkv_bias.dtype == torch.float32                       # vectors are held in float32
     assert mixer.has_qkv_bias and "qkv.bias" in mixer.parameter_shapes()  # the flag survives the binding of the tensor
     assert model.weight_bytes() > 0
-    assert model.lm_head.data_ptr() == model.embedding.data_ptr()        # tied
+    assert model.head.weight.data_ptr() == model.embedding.weight.data_ptr()        # tied
     reader = CheckpointReader(folder)
     q = reader.read("model.layers.0.self_attn.q_proj.weight")
     v = reader.read("model.layers.0.self_attn.v_proj.weight")
@@ -172,7 +174,7 @@ def test_one_error_lists_missing_unexpected_and_misshapen(folder):
 
 def test_random_model_on_device_matches_plan(tmp_path):
     cfg, plan, model = random_model(helpers.TINY_B, seed=9, dtype="bfloat16", device="cpu")
-    assert model.lm_head.data_ptr() != model.embedding.data_ptr()
+    assert model.head.weight.data_ptr() != model.embedding.weight.data_ptr()
     assert tuple(model.blocks[2].feed_forward.gate_up_weight.shape) == (768, 192)
     cfg2, _, again = random_model(helpers.TINY_B, seed=9, dtype="bfloat16", device="cpu")
     assert torch.equal(model.blocks[1].mixer.out_weight, again.blocks[1].mixer.out_weight)

@@ -177,7 +177,7 @@ def test_forced_preemption_keeps_outputs():
     e.drain()                                   # the last step's token is read before it is compared
     before = list(a.generated_ids)
     assert before
-    e._preempt(a)
+    e.preempt(a)
     assert a.state is State.PREEMPTED and a.cached_tokens == 0 and a.replaying and e.cache.used_pages == 0
     run_until_done(e, [a])
     assert a.generated_ids[:len(before)] == before and a.generated_ids == [5, 6, 7, 8, 9, 10, 11]
