@@ -570,6 +570,9 @@ int check_common(const char* what, int nq, int nkv, int d, int ps, int num_pages
 
 }  // namespace
 
+// The most key splits the merge kernel takes (its per-split weights live in shared memory).
+extern "C" int fe_paged_decode_max_splits(void) { return MAX_SPLITS_SHARED; }
+
 // Number of bytes of scratch the decode kernel needs for ``splits`` > 1 (0 for one split):
 // float partial outputs [requests, nq, splits, d] followed by float log-sum-exps [requests, nq, splits].
 extern "C" long long fe_paged_decode_scratch_bytes(int requests, int nq, int d, int splits) {

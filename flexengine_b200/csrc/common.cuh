@@ -119,6 +119,7 @@ __device__ __forceinline__ void prefetch_l2_share(const void* base, long long by
 void fe_set_error(const char* fmt, ...);
 int fe_check_launch(const char* what);
 int fe_pdl_enabled();
+int fe_sm_count();      // multiprocessors of the current device (asked once per device)
 
 namespace fe {
 // Launch with the programmatic-stream-serialization attribute (when enabled).

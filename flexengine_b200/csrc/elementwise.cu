@@ -214,8 +214,11 @@ extern "C" int fe_add_rmsnorm(float* residual, const void* delta, const float* w
 // in place.  Key heads: bias + rotation, written back and to the key pages.  Value heads: bias,
 // written back and to the value pages.  Cache layout [pages, nkv, page_size, d]; slot = page *
 // page_size + offset; a negative slot writes nothing.
-template <typename T>
-__global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+// The projection is read from ``src`` as TI (the compute type, or float when the product was kept in 32-bit so that
+// bias and rotation are added before the one rounding) and written to ``qkv`` as T; with TI = T the two may be the
+// same buffer: every element is read before it is written, by the thread that writes it.
+template <typename TI, typename T>
+__global__ void qkv_bias_rope_cache_kernel(const TI* src, T* qkv, const float* __restrict__ bias,
                                            const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                            int rot, const int* __restrict__ slot_mapping, T* __restrict__ kc,
                                            T* __restrict__ vc, int nq, int nkv, int d, int ps, long long num_slots,
@@ -225,6 +228,7 @@ __global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __r
     const int t = blockIdx.x, head = blockIdx.y;
     const int width = (nq + 2 * nkv) * d;
     T* x = qkv + (size_t)t * width + (size_t)head * d;
+    const TI* xi = src + (size_t)t * width + (size_t)head * d;
     const float* b = bias ? bias + (size_t)head * d : nullptr;
     const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
     T* dst = nullptr;
@@ -243,7 +247,7 @@ __global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __r
     if (rotate) {
         const float pos = (float)positions[t];
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
-            float a = to_float(x[j]), c = to_float(x[j + half]);
+            float a = to_float(xi[j]), c = to_float(xi[j + half]);
             if (b) { a += b[j]; c += b[j + half]; }
             float sn, cs;
             sincosf(pos * inv_freq[j], &sn, &cs);
@@ -252,7 +256,7 @@ __global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __r
             if (dst) { dst[j] = ra; dst[j + half] = rc; }
         }
         for (int j = rot + threadIdx.x; j < d; j += blockDim.x) {
-            float a = to_float(x[j]);
+            float a = to_float(xi[j]);
             if (b) a += b[j];
             const T ra = from_float<T>(a);
             x[j] = ra;
@@ -260,7 +264,7 @@ __global__ void qkv_bias_rope_cache_kernel(T* __restrict__ qkv, const float* __r
         }
     } else {
         for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            float a = to_float(x[j]);
+            float a = to_float(xi[j]);
             if (b) a += b[j];
             const T ra = from_float<T>(a);
             x[j] = ra;
@@ -278,8 +282,8 @@ __device__ __forceinline__ void load8f(const float* p, float* v) {
     v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
 }
 
-template <typename T>
-__global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+template <typename TI, typename T>
+__global__ void qkv_bias_rope_cache_vec_kernel(const TI* src, T* qkv, const float* __restrict__ bias,
                                                const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                                int rot, const int* __restrict__ slot_mapping, T* __restrict__ kc,
                                                T* __restrict__ vc, int nq, int nkv, int d, int ps,
@@ -303,6 +307,7 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
     const int heads = nq + 2 * nkv;
     const int width = heads * d;
     T* x = qkv + (size_t)t * width;
+    const TI* xin = src + (size_t)t * width;
     // unit = (head, group of 8 elements of the first half of the rotated part, or of the rest)
     const int rot_units = rotary ? half / 8 : 0, rest_units = (d - (rotary ? rot : 0)) / 8;
     const int per_head = rot_units + rest_units;
@@ -310,6 +315,7 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
         const int head = u / per_head, k = u - head * per_head;
         const bool is_q = head < nq, is_k = !is_q && head < nq + nkv;
         T* hx = x + (size_t)head * d;
+        const TI* hi = xin + (size_t)head * d;
         const float* hb = bias ? bias + (size_t)head * d : nullptr;
         T* dst = nullptr;
         if (!is_q && slot >= 0) {
@@ -319,8 +325,8 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
         if (k < rot_units && (is_q || is_k)) {
             const int j = k * 8;
             float a[8], c[8];
-            load8<T>(hx + j, a);
-            load8<T>(hx + j + half, c);
+            load8<TI>(hi + j, a);
+            load8<TI>(hi + j + half, c);
             float ra[8], rc[8];
             float cs[8], sn[8];
             load8f(trig + j, cs);
@@ -347,7 +353,7 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
             else j = (rotary ? rot : 0) + (k - rot_units) * 8;
             for (int rep = 0; rep < ((k < rot_units) ? 2 : 1); ++rep, j += half) {
                 float a[8];
-                load8<T>(hx + j, a);
+                load8<TI>(hi + j, a);
                 if (hb) {
                     float ba[8];
                     load8f(hb + j, ba);
@@ -361,8 +367,8 @@ __global__ void qkv_bias_rope_cache_vec_kernel(T* __restrict__ qkv, const float*
     }
 }
 
-template <typename T>
-static int launch_rope(void* qkv, const float* bias, const int* positions, const float* inv_freq, int rot,
+template <typename TI, typename T>
+static int launch_rope(const void* src, void* qkv, const float* bias, const int* positions, const float* inv_freq, int rot,
                        const int* slot_mapping, void* kc, void* vc, int T_tokens, int nq, int nkv, int d, int ps,
                        long long num_slots, int* status, cudaStream_t stream) {
     if (d % 16 == 0 && rot % 16 == 0 && ((size_t)bias & 15) == 0) {
@@ -370,26 +376,33 @@ static int launch_rope(void* qkv, const float* bias, const int* positions, const
         // as few passes over the units as 256 threads need, and then only as many threads as fill every pass
         const int passes = (units + 255) / 256;
         const int threads = max(64, ((units + passes - 1) / passes + 31) / 32 * 32);
-        fe::launch(qkv_bias_rope_cache_vec_kernel<T>, T_tokens, threads, (size_t)rot * sizeof(float), stream, 
-            (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
+        fe::launch(qkv_bias_rope_cache_vec_kernel<TI, T>, T_tokens, threads, (size_t)rot * sizeof(float), stream,
+            (const TI*)src, (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
     } else {
         const dim3 grid(T_tokens, nq + 2 * nkv);
-        fe::launch(qkv_bias_rope_cache_kernel<T>, grid, d / 2 >= 64 ? 64 : 32, 0, stream, 
-            (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
+        fe::launch(qkv_bias_rope_cache_kernel<TI, T>, grid, d / 2 >= 64 ? 64 : 32, 0, stream,
+            (const TI*)src, (T*)qkv, bias, positions, inv_freq, rot, slot_mapping, (T*)kc, (T*)vc, nq, nkv, d, ps, num_slots, status);
     }
     return fe_check_launch("qkv_bias_rope_cache");
 }
 
-extern "C" int fe_qkv_bias_rope_cache(void* qkv, const float* bias, const int* positions, const float* inv_freq,
-                                      int rot, const int* slot_mapping, void* kc, void* vc, int T, int nq, int nkv,
-                                      int d, int ps, long long num_slots, int dtype, int* status, cudaStream_t stream) {
+// ``src``: the projection, in the compute dtype (may be ``qkv`` itself) or, with ``src_float`` set, in float;
+// ``qkv``: the result in the compute dtype ``dtype``.
+extern "C" int fe_qkv_bias_rope_cache(const void* src, int src_float, void* qkv, const float* bias, const int* positions,
+                                      const float* inv_freq, int rot, const int* slot_mapping, void* kc, void* vc, int T,
+                                      int nq, int nkv, int d, int ps, long long num_slots, int dtype, int* status,
+                                      cudaStream_t stream) {
     FE_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && d > 0 && ps > 0, "qkv_bias_rope_cache: bad sizes");
     FE_REQUIRE(rot >= 0 && rot <= d && rot % 2 == 0, "qkv_bias_rope_cache: rotary width %d does not fit head size %d", rot, d);
     if (T == 0) return 0;
+    FE_REQUIRE(src != nullptr && qkv != nullptr, "qkv_bias_rope_cache: no source or destination");
+    FE_REQUIRE(!(src_float && src == qkv), "qkv_bias_rope_cache: a float source cannot be rewritten in place as another type");
     if (dtype == FE_F32)
-        return launch_rope<float>(qkv, bias, positions, inv_freq, rot, slot_mapping, kc, vc, T, nq, nkv, d, ps, num_slots, status, stream);
+        return launch_rope<float, float>(src, qkv, bias, positions, inv_freq, rot, slot_mapping, kc, vc, T, nq, nkv, d, ps, num_slots, status, stream);
+    if (dtype == FE_BF16 && src_float)
+        return launch_rope<float, bf16>(src, qkv, bias, positions, inv_freq, rot, slot_mapping, kc, vc, T, nq, nkv, d, ps, num_slots, status, stream);
     if (dtype == FE_BF16)
-        return launch_rope<bf16>(qkv, bias, positions, inv_freq, rot, slot_mapping, kc, vc, T, nq, nkv, d, ps, num_slots, status, stream);
+        return launch_rope<bf16, bf16>(src, qkv, bias, positions, inv_freq, rot, slot_mapping, kc, vc, T, nq, nkv, d, ps, num_slots, status, stream);
     FE_REQUIRE(false, "qkv_bias_rope_cache: unknown dtype %d", dtype);
 }
 
@@ -432,7 +445,8 @@ extern "C" int fe_swiglu(const void* gate_up, void* out, int T, int I, int dtype
     const long long total = vec ? (long long)T * (I / 8) : (long long)T * I;
     const int threads = 256;
     long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    const long long most = 16LL * fe_sm_count();
+    if (blocks > most) blocks = most;
     if (dtype == FE_F32) {
         if (vec) fe::launch(swiglu_vec_kernel<float>, (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, I);
         else fe::launch(swiglu_kernel<float>, (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, I);

@@ -22,6 +22,21 @@ int fe_check_launch(const char* what) {
     return 0;
 }
 
+// The number of multiprocessors of the current device: the one place kernels' launch heuristics take it from.
+int fe_sm_count() {
+    static int cached[64] = {0};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+    if (cached[device] == 0) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) return 1;
+        cached[device] = sms;
+    }
+    return cached[device];
+}
+
+extern "C" int fe_device_sm_count() { return fe_sm_count(); }
+
 static int g_pdl = 1;
 
 int fe_pdl_enabled() { return g_pdl; }

@@ -251,11 +251,12 @@ int launch(const void* x, const void* W_, void* out, int M, int N, int K, int I,
     // with more tiles than one round of one-tile blocks takes two tiles a block: a few blocks over the round would
     // run alone after it (448 tiles: 15.9 -> 13.6 us).  A narrow one, whose blocks are all resident at once even two
     // to an SM: every warp sends twice as many loads ahead, which halves the number of round trips to memory.
-    const bool wide = EPI != EPI_QKV && tiles > 3 * 148;
-    const bool deep = !wide && tiles <= 2 * 148;
+    const int sms = fe_sm_count();
+    const bool wide = EPI != EPI_QKV && tiles > 3 * sms;
+    const bool deep = !wide && tiles <= 2 * sms;
     const int blocks = wide ? (tiles + 1) / 2 : tiles;
     // fewer blocks than SMs, and at least one round of loads (four steps) for each of sixteen warps
-    const bool narrow = (EPI == EPI_BF16 || EPI == EPI_F32) && M <= 8 && tiles <= 148 && K / KSTEP >= 4 * WARPS_NARROW;
+    const bool narrow = (EPI == EPI_BF16 || EPI == EPI_F32) && M <= 8 && tiles <= sms && K / KSTEP >= 4 * WARPS_NARROW;
 #define FE_SKINNY(NT, RT, PF, W) \
     fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF, W>, blocks, W * 32, 0, stream, (const bf16*)x, (const bf16*)W_, out, M, N, K, I, qkv)
     if (narrow) FE_SKINNY(1, 1, 4, WARPS_NARROW);

@@ -279,7 +279,7 @@ int launch_with(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, i
 template <int EPI>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int M, int MB, int N, int K, int tiles, int splits,
            int kb_per_split, int up_row_offset, int* status, cudaStream_t stream) {
-    if (tiles * splits > 2 * 148)
+    if (tiles * splits > 2 * fe_sm_count())
         return launch_with<EPI, 3>(map_w, map_x, out, M, MB, N, K, tiles, splits, kb_per_split, up_row_offset, status, stream);
     return launch_with<EPI, 6>(map_w, map_x, out, M, MB, N, K, tiles, splits, kb_per_split, up_row_offset, status, stream);
 }
@@ -290,7 +290,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, void* out, int M,
 // float scratch it then needs (0 for one split).
 extern "C" int fe_stream_gemm_splits(int N, int K) {
     const int tiles = (N + TILE_ROWS - 1) / TILE_ROWS, num_kb = (K + BK - 1) / BK;
-    int splits = (148 + tiles / 2) / tiles;
+    int splits = (fe_sm_count() + tiles / 2) / tiles;
     if (splits > num_kb / 4) splits = num_kb / 4;
     return splits < 1 ? 1 : splits;
 }
@@ -322,7 +322,8 @@ extern "C" int fe_stream_gemm_tcgen05(const void* x, const void* W, void* out, v
     const int per = (num_kb + splits - 1) / splits;
     if (launch<EPI_PARTIAL>(map_w, map_x, scratch, M, MB, N, K, tiles, splits, per, 0, status, stream)) return 1;
     const long long total = (long long)M * N;
-    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    const long long most = 8LL * fe_sm_count();
+    const int blocks = (int)((total + 255) / 256 < most ? (total + 255) / 256 : most);
     fe::launch(reduce_partials_kernel, blocks, 256, 0, stream, (const float*)scratch, (bf16*)out, total, splits);
     return fe_check_launch("stream_gemm reduce");
 }

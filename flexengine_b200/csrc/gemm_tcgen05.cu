@@ -284,13 +284,7 @@ int launch(const void* x, const void* W, void* out, int M, int N, int K, int* st
     const size_t smem = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 1024;
     cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     FE_REQUIRE(err == cudaSuccess, "gemm_tcgen05: %s", cudaGetErrorString(err));
-    static int sms = 0;
-    if (!sms) {
-        int device = 0;
-        cudaGetDevice(&device);
-        err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-        FE_REQUIRE(err == cudaSuccess && sms > 0, "gemm_tcgen05: cannot read the number of SMs");
-    }
+    const int sms = fe_sm_count();
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (n_out + OUT_COLS - 1) / OUT_COLS;
     const long long total = (long long)m_tiles * n_tiles;
     const int blocks = (int)(total < sms ? total : sms);        // one persistent block per SM

@@ -76,15 +76,22 @@ def status_word(device) -> torch.Tensor:
     return word
 
 
+STATUS_BITS = ((1, "token id out of range"), (2, "page id out of range"), (4, "cache slot out of range"),
+               (8, "a bounded wait ran out"))
+
+
+def describe_status(value: int) -> str:
+    """What the bits of a status word say, in words."""
+    return ", ".join(n for bit, n in STATUS_BITS if value & bit) or f"unknown bits {value}"
+
+
 def check_status(device) -> None:
     """Synchronises; raises if a kernel met an index it had to skip since the last check."""
     word = status_word(device)
     value = int(word.item())
     if value:
         word.zero_()
-        names = [n for bit, n in ((1, "token id out of range"), (2, "page id out of range"),
-                                  (4, "cache slot out of range"), (8, "a bounded wait ran out")) if value & bit]
-        raise RuntimeError("kernel status: " + ", ".join(names))
+        raise RuntimeError("kernel status: " + describe_status(value))
 
 
 # ------------------------------------------------------------------------------------------------
@@ -161,13 +168,14 @@ def linear(x, w, bias=None, out_float32=False):
         return y if (out_float32 or x.dtype == torch.float32) else y.to(x.dtype)
     if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         raise TypeError(f"linear: weight {w.dtype} with activations {x.dtype}")
+    wide = out_float32 or bias is not None           # a bias is added in float32, before the one rounding
     if skinny_ok(x, w):
-        y = skinny_gemm(x, w, EPI_F32 if out_float32 else EPI_BF16)
+        y = skinny_gemm(x, w, EPI_F32 if wide else EPI_BF16)
     else:
-        y = torch.mm(x, w.t(), out_dtype=torch.float32) if out_float32 else torch.mm(x, w.t())
+        y = torch.mm(x, w.t(), out_dtype=torch.float32) if wide else torch.mm(x, w.t())
     if bias is not None:
-        y += bias.to(y.dtype)
-    return y
+        y += bias
+    return y if out_float32 or not wide else y.to(torch.bfloat16)
 
 
 SKINNY_MAX_ROWS = 8          # beyond this the library product is as fast or faster
@@ -276,13 +284,18 @@ def linear_swiglu(x, w, intermediate):
 
 
 def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache,
-                        nq, nkv, d, page_size):
-    """In place on qkv [T, (nq + 2 nkv) d]: + bias, rotary encoding of the query and key heads;
-    key and value heads are also written to their cache slots (slot_mapping None: no write)."""
-    _need_cuda(qkv, bias, positions, inv_freq, slot_mapping, k_cache, v_cache)
+                        nq, nkv, d, page_size, src=None):
+    """qkv [T, (nq + 2 nkv) d] = projection + bias, with the rotary encoding of the query and key heads;
+    key and value heads are also written to their cache slots (slot_mapping None: no write).  The
+    projection is ``qkv`` itself (rewritten in place) or ``src``, a float32 tensor of the same shape: a
+    bfloat16 result is then rounded once, after bias and rotation."""
+    _need_cuda(qkv, bias, positions, inv_freq, slot_mapping, k_cache, v_cache, src)
     T, width = qkv.shape
     if width != (nq + 2 * nkv) * d or not qkv.is_contiguous():
         raise ValueError("qkv_bias_rope_cache: qkv must be contiguous [T, (nq + 2 nkv) d]")
+    if src is not None and (src.shape != qkv.shape or not src.is_contiguous() or src.dtype not in (torch.float32, qkv.dtype)):
+        raise ValueError("qkv_bias_rope_cache: src must be contiguous, shaped like qkv, float32 or of its dtype")
+    src_float = src is not None and src.dtype == torch.float32 and qkv.dtype != torch.float32
     if k_cache.dtype != qkv.dtype or tuple(k_cache.shape[1:]) != (nkv, page_size, d) or not k_cache.is_contiguous() \
             or not v_cache.is_contiguous():
         raise ValueError("qkv_bias_rope_cache: cache must be contiguous [pages, nkv, page_size, d] in the compute dtype")
@@ -291,7 +304,8 @@ def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cac
     if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2):
         raise ValueError("inv_freq must be float32 [rot / 2]")
     num_slots = k_cache.shape[0] * page_size
-    _run(_core(), "fe_qkv_bias_rope_cache", _ptr(qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq), _c_int(rot),
+    _run(_core(), "fe_qkv_bias_rope_cache", _ptr(qkv if src is None else src), _c_int(1 if src_float else 0), _ptr(qkv),
+         _ptr(bias), _ptr(positions), _ptr(inv_freq), _c_int(rot),
          _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(nq), _c_int(nkv), _c_int(d),
          _c_int(page_size), _c_ll(num_slots), _c_int(_code(qkv.dtype)), _ptr(status_word(qkv.device)), _stream())
 
@@ -312,8 +326,16 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
              _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(h.shape[1]), _c_int(nq), _c_int(nkv),
              _c_int(d), _c_int(page_size), _c_ll(k_cache.shape[0] * page_size), _ptr(status_word(h.device)), _stream())
         return out
-    qkv = linear(h, w)
-    qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size)
+    if h.dtype == torch.float32:
+        qkv = linear(h, w)
+        qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size)
+        return qkv
+    # the product stays float32 until bias and rotation are in, as in the fused kernel: a token's keys and values
+    # are rounded once whichever path its step took
+    product = linear(h, w, out_float32=True)
+    qkv = torch.empty(product.shape, dtype=h.dtype, device=h.device)
+    qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size,
+                        src=product)
     return qkv
 
 
@@ -330,7 +352,17 @@ def paged_attention_simt(q, q_stride, k_cache, v_cache, block_table, cu_q, q_sta
 
 _scratch: dict = {}
 _scratch_kept: list = []     # every scratch buffer ever handed out (see scratch())
-SM_COUNT = 148
+_sm_count: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of ``device`` (the current CUDA device when None), as the driver reports them:
+    the one number every launch heuristic here scales with (the kernels' own host code asks the same
+    attribute through the helper in ``csrc/errors.cu``)."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if index not in _sm_count:
+        _sm_count[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _sm_count[index]
 
 
 def _bf16():
@@ -355,16 +387,21 @@ def scratch(device, nbytes: int) -> torch.Tensor:
     return have
 
 
-def decode_splits(requests: int, nkv: int, max_ctx_len: int) -> int:
+DECODE_MAX_SPLITS = 256      # what the merge kernel of decode attention takes (fe_paged_decode_max_splits)
+
+
+def decode_splits(requests: int, nkv: int, max_ctx_len: int, sms: int | None = None) -> int:
     """How many ways the keys of a request are split in decode.  Between half a round and one round of resident
     blocks (six blocks fit an SM; never more than a round: a few blocks over it would run alone after it): towards
     the full round when a split still has six tiles of 32 keys or more to walk, towards the half when splits
-    would get short and the merge dominate; never a split shorter than two tiles."""
+    would get short and the merge dominate; never a split shorter than two tiles, never more splits than the
+    merge kernel takes (one request with one or two key/value heads at a very long context would ask for more)."""
+    sms = sms or sm_count()
     tiles = max(1, -(-max_ctx_len // 32))
     pairs = max(1, requests * nkv)
-    most = max(1, 6 * SM_COUNT // pairs)          # rounded down: a few blocks over the round would run alone after it
-    least = max(1, (3 * SM_COUNT + pairs // 2) // pairs)
-    want = min(most, max(least, tiles // 6))
+    most = max(1, 6 * sms // pairs)               # rounded down: a few blocks over the round would run alone after it
+    least = max(1, (3 * sms + pairs // 2) // pairs)
+    want = min(most, max(least, tiles // 6), DECODE_MAX_SPLITS)
     return int(max(1, min(want, tiles // 2)))
 
 
@@ -397,7 +434,7 @@ def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start,
     return out
 
 
-def tcgen05_attention_ok(max_q_len, nq, nkv, d, lengths=None, starts=None):
+def tcgen05_attention_ok(max_q_len, nq, nkv, d, lengths=None, starts=None, sms: int | None = None):
     """The tcgen05 prefill kernel takes head sizes 64 and 128, portions of any length: measured against the
     mma.sync kernel it is level on portions of a few tokens and ahead everywhere else, the more the longer the
     context.  Other head sizes go to the mma.sync kernel, and so does a step of many requests that bring a few
@@ -410,7 +447,7 @@ def tcgen05_attention_ok(max_q_len, nq, nkv, d, lengths=None, starts=None):
         blocks = nkv * sum(-(-n * group // 256) for n in lengths)
         rows = nkv * group * sum(lengths)
         longest = max(s + n for s, n in zip(starts, lengths))
-        if blocks > SM_COUNT and rows < 96 * blocks and longest <= 1024:
+        if blocks > (sms or sm_count()) and rows < 96 * blocks and longest <= 1024:
             return False
     return True
 
@@ -420,7 +457,7 @@ PREFILL_TILES_PER_SPLIT = 4      # a split walks at least this many tiles of 64 
 PREFILL_SPLIT_FROM_TILES = 16    # shorter walks are over before a second kernel could merge them
 
 
-def prefill_splits(lengths, starts, nq, nkv, window=0) -> int:
+def prefill_splits(lengths, starts, nq, nkv, window=0, sms: int | None = None) -> int:
     """Into how many blocks the tcgen05 prefill kernel shares out the keys of each pair of row tiles.  One block
     a multiprocessor is resident; a short portion late in a long context fills few of them, and each walks the whole
     context, so its keys are split until the blocks about cover the device."""
@@ -430,7 +467,7 @@ def prefill_splits(lengths, starts, nq, nkv, window=0) -> int:
     tiles = -(-longest // 64)
     if tiles < PREFILL_SPLIT_FROM_TILES:
         return 1
-    return int(max(1, min(SM_COUNT // max(1, blocks), tiles // PREFILL_TILES_PER_SPLIT, PREFILL_MAX_SPLITS)))
+    return int(max(1, min((sms or sm_count()) // max(1, blocks), tiles // PREFILL_TILES_PER_SPLIT, PREFILL_MAX_SPLITS)))
 
 
 def paged_prefill_tcgen05(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,

@@ -56,17 +56,36 @@ def plain_logits(model_dir: str, ids, device="cpu") -> torch.Tensor:
 
 # ---- comparison bars ----------------------------------------------------------------------------
 # float32: kernels and the plain implementation differ only in the order of float32 sums.
-# bfloat16: activations are rounded to 8 bits of mantissa between kernels (relative 2^-9 each);
-# over a few layers that is a few parts in a thousand of the logits' scale.
-def assert_logits_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "") -> None:
+# bfloat16: activations are rounded to 8 bits of mantissa between kernels, so the error scales with the
+# spread of the logits.  BF16_SEEN is the worst |difference| that the engine showed over all four scenarios of
+# cutting the work, divided by the standard deviation of the plain logits (B200, per tiny configuration; A
+# 0.0027, B 0.0087, C 0.0033, D 0.0041 in absolute terms); the bar is three times that, which stays well below
+# the models' typical gap between the best and the second-best logit (0.03 to 0.5).
+BF16_SEEN = {"A": 0.016, "B": 0.031, "C": 0.019, "D": 0.020}
+BF16_SEEN_ELSEWHERE = 0.03
+BF16_HEADROOM = 3.0
+
+
+def bf16_bar(want: torch.Tensor, config: str | None = None) -> float:
+    spread = float(want.float().std(dim=-1).mean()) if want.dim() == 2 else float(want.float().std())
+    return BF16_HEADROOM * BF16_SEEN.get(config, BF16_SEEN_ELSEWHERE) * spread
+
+
+def assert_logits_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "", config: str | None = None) -> None:
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
-    scale = max(1.0, float(want.abs().max()))
-    bar = (2e-5 if dtype == "float32" else 3e-2) * scale
+    bar = 2e-5 * max(1.0, float(want.abs().max())) if dtype == "float32" else bf16_bar(want, config)
     err = (got - want).abs()
     worst = int(err.max(dim=-1).values.argmax()) if err.dim() == 2 else 0
     assert float(err.max()) <= bar, f"{what}: max |diff| {float(err.max()):.3e} > {bar:.3e} (first worst row {worst})"
+
+
+def assert_near_maximum(row: torch.Tensor, token: int, config: str | None, what: str = "") -> None:
+    """A token chosen in bfloat16 is the float32 logits' maximum, or so close to it that bfloat16's error (the
+    bar above, on both logits) can have swapped the two."""
+    short = float(row.max() - row[token])
+    assert short <= bf16_bar(row, config), f"{what}: token {token} is {short:.3e} below the maximum (bar {bf16_bar(row, config):.3e})"
 
 
 # ---- scenarios: lists of steps; a step is (entries, ended) with entries [(rid, tokens, want)] ----------
@@ -165,10 +184,10 @@ def peak_pages(steps, page_size: int) -> int:
     return peak
 
 
-def compare_with_plain(model_dir, results: dict, requests: dict, dtype: str, what: str, device="cpu") -> None:
+def compare_with_plain(model_dir, results: dict, requests: dict, dtype: str, what: str, device="cpu", config=None) -> None:
     for rid, ids in requests.items():
         want = plain_logits(model_dir, ids, device)
         rows = [p for (r, p) in results if r == rid]
         assert sorted(rows) == list(range(len(ids))), f"{what}: request {rid} misses rows"
         got = torch.stack([results[(rid, p)] for p in range(len(ids))])
-        assert_logits_close(got, want, dtype, f"{what} request {rid}")
+        assert_logits_close(got, want, dtype, f"{what} request {rid}", config)

@@ -52,9 +52,10 @@ def linear_swiglu(x, w, intermediate):
 
 
 def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache,
-                        nq, nkv, d, page_size):
+                        nq, nkv, d, page_size, src=None):
+    """``src``: the projection in float32 when it was kept so; else ``qkv`` is rewritten in place."""
     T = qkv.shape[0]
-    x = qkv.float()
+    x = (qkv if src is None else src).float()
     if bias is not None:
         x = x + bias.float()
     x = x.view(T, nq + 2 * nkv, d)
@@ -76,8 +77,11 @@ def qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cac
 
 
 def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size):
-    qkv = linear(h, w)
-    qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size)
+    """The product stays float32 until bias and rotation are in: one rounding, whatever the number of rows."""
+    product = linear(h, w, out_float32=True)
+    qkv = torch.empty(product.shape, dtype=h.dtype, device=h.device)
+    qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size,
+                        src=product)
     return qkv
 
 

@@ -1,26 +1,33 @@
 """The host-side rules that choose a kernel and its launch shape: pure functions of sizes, checked without a GPU."""
 from flexengine_b200 import ops
 
-SLOTS = 6 * ops.SM_COUNT        # decode attention blocks resident at once
+SMS = 148                       # a B200's multiprocessors; on a device the functions ask the driver themselves
+SLOTS = 6 * SMS                 # decode attention blocks resident at once
 
 
 def test_decode_splits_stay_within_one_resident_round():
     for requests in (1, 2, 3, 5, 8, 13, 16, 31, 32, 64, 100, 256):
         for nkv in (1, 2, 4, 8):
-            for ctx in (1, 31, 64, 500, 2048, 8192, 32768, 131072):
-                splits = ops.decode_splits(requests, nkv, ctx)
+            for ctx in (1, 31, 64, 500, 2048, 8192, 32768, 65536, 131072, 1 << 20):
+                splits = ops.decode_splits(requests, nkv, ctx, SMS)
                 tiles = -(-ctx // 32)
-                assert splits >= 1
+                assert 1 <= splits <= ops.DECODE_MAX_SPLITS, "the merge kernel's limit"
                 assert splits == 1 or splits * 2 <= tiles, "a split walks at least two tiles"
                 if requests * nkv <= SLOTS:
                     assert splits * requests * nkv <= SLOTS, (requests, nkv, ctx, splits)
     # the case that showed the fault: 28 splits of 32 pairs were 8 blocks more than fit
-    assert ops.decode_splits(8, 4, 32768) == 27
-    assert ops.decode_splits(8, 4, 2048) == 14 and ops.decode_splits(64, 4, 2048) == 3 and ops.decode_splits(1, 4, 2048) == 32
+    assert ops.decode_splits(8, 4, 32768, SMS) == 27
+    assert ops.decode_splits(8, 4, 2048, SMS) == 14 and ops.decode_splits(64, 4, 2048, SMS) == 3
+    assert ops.decode_splits(1, 4, 2048, SMS) == 32
+    # one request, one or two key/value heads, very long contexts: a round of the device would be more than the merge takes
+    assert ops.decode_splits(1, 1, 32768, SMS) == ops.decode_splits(1, 2, 131072, SMS) == ops.DECODE_MAX_SPLITS
+    with open(ops.__file__.replace("ops/__init__.py", "csrc/attention_mma.cu")) as f:
+        assert f"MAX_SPLITS_SHARED = {ops.DECODE_MAX_SPLITS};" in f.read()
 
 
 def test_prefill_splits_follow_the_work():
-    split = ops.prefill_splits
+    def split(*a, **k):
+        return ops.prefill_splits(*a, sms=SMS, **k)
     assert split([2048], [0], 28, 4) == 1                      # a whole prompt fills the device by itself
     assert split([64], [2048], 28, 4) == 8                     # 33 tiles: no split shorter than four
     assert split([64], [8192], 28, 4) == 18                    # eight blocks without splits; one round of the device
@@ -35,7 +42,8 @@ def test_prefill_splits_follow_the_work():
 
 
 def test_attention_kernel_choice():
-    ok = ops.tcgen05_attention_ok
+    def ok(*a):
+        return ops.tcgen05_attention_ok(*a, sms=SMS)
     assert ok(300, 4, 2, 128) and ok(2, 4, 2, 64) and not ok(4096, 4, 2, 96) and not ok(4096, 4, 2, 256)
     # very many requests with a few tokens each at short contexts: the lighter blocks of the mma.sync kernel
     assert not ok(8, 28, 4, 128, [8] * 256, [0] * 256) and not ok(64, 28, 4, 128, [1] * 60 + [64], [200] * 60 + [0])

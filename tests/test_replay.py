@@ -115,9 +115,9 @@ def test_trace_run_program(model_dirs, name, dtype, tmp_path):
         run_trace_program(model_dirs[name], dtype, steps, out_dir)
         results = read_results(out_dir, steps, vocab)
         if kind != "sparse":
-            helpers.compare_with_plain(model_dirs[name], results, requests, dtype, f"trace_run {name}/{kind}/{dtype}")
+            helpers.compare_with_plain(model_dirs[name], results, requests, dtype, f"trace_run {name}/{kind}/{dtype}", config=name)
         else:
             for (rid, pos), row in results.items():
                 if rid not in plain:
                     plain[rid] = helpers.plain_logits(model_dirs[name], requests[rid])
-                helpers.assert_logits_close(row, plain[rid][pos], dtype, f"sparse {rid}@{pos}")
+                helpers.assert_logits_close(row, plain[rid][pos], dtype, f"sparse {rid}@{pos}", name)

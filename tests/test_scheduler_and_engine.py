@@ -206,6 +206,43 @@ def test_executor_failure_faults_the_engine_and_frees_everything():
         e.submit([1], max_tokens=1)
 
 
+def test_a_fault_recorded_by_a_kernel_fails_the_requests():
+    """Kernels record a guarded fault (an index they had to skip, a bounded wait that ran out) in a status word
+    on the device; the engine reads it with each step's tokens.  A set bit fails every live request and closes
+    the engine: what was sampled from such a step is not handed out as tokens."""
+    import types
+    word = torch.zeros(1, dtype=torch.int32)
+    e = counting_engine()
+    e.runner.ops = types.SimpleNamespace(status_word=lambda device: word,
+                                         describe_status=lambda v: "a bounded wait ran out" if v & 8 else str(v))
+    a, b = e.submit([1, 2], max_tokens=6), e.submit([3, 4], max_tokens=6)
+    e.step(); e.step(); e.drain()
+    assert a.generated_ids == [3, 4] and e.fault is None
+    word[0] = 8
+    tokens_before = len(a.generated_ids)
+    for _ in range(3):
+        e.step()
+    assert e.fault and "bounded wait" in e.fault
+    assert a.state is State.FAILED and b.state is State.FAILED and e.cache.used_pages == 0
+    assert len(a.generated_ids) == tokens_before and -1 not in a.generated_ids       # nothing of the bad step came out
+    assert a.events.get_nowait().kind == "token"
+    with pytest.raises(BusyError):
+        e.submit([1], max_tokens=1)
+
+
+def test_slo_aware_policy_end_to_end():
+    """The policy that orders by slack, through whole generations: same tokens as any other policy, everything freed."""
+    e = counting_engine(scheduler_policy="slo_aware", budget=5, ttft_slo_ms=50.0, itl_slo_ms=5.0)
+    requests = [e.submit([2 + 3 * i] * (1 + 2 * i), max_tokens=3 + i % 3, priority=i % 3 - 1) for i in range(6)]
+    run_until_done(e, requests)
+    e.drain()
+    for i, r in enumerate(requests):
+        first = 2 + 3 * i + 1
+        assert r.generated_ids == list(range(first, first + 3 + i % 3)) and r.finish_reason == "length"
+    assert e.cache.used_pages == 0 and not e.cache.requests
+    assert all(sum(n for _, n, _ in call) <= 5 for call in e.runner.calls)
+
+
 def test_worker_thread_serves_requests_and_stop_cancels_the_rest():
     """``start()`` runs the step loop on a thread of its own (the reference's serving mode); clients
     read their request's event queue; ``stop()`` cancels what is still alive and frees its pages."""

@@ -27,8 +27,13 @@ def plain_weights():
     return {name: random_tensor(plan, name, shape, 5, torch.bfloat16, DEV) for name, shape in checkpoint_tensors(plan)}
 
 
+_models = {}
+
+
 def runner_for(dtype, pages, max_requests=3):
-    _cfg, plan, model = random_model(SHAPE, seed=5, dtype=dtype, device=DEV)
+    if dtype not in _models:
+        _models[dtype] = random_model(SHAPE, seed=5, dtype=dtype, device=DEV)
+    _cfg, plan, model = _models[dtype]
     torch_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     cache = CacheManager(plan.cache_groups, pages, 16, max_requests, torch_dtype, DEV)
     return ModelRunner(model, cache)
@@ -103,3 +108,34 @@ def test_float32_path_at_the_seven_b_widths(plain_weights):
         got.append(runner.step([StepEntry("a", ids[p:p + 1], [0])]))
     want = plain_model.forward_logits(SHAPE, plain_weights, ids).cpu()
     helpers.assert_logits_close(torch.cat(got), want[[0, 50, 99, 146, 147, 148, 149]], "float32", "7B-shape float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["whole", "last_decoded", "portions", "mixed"])
+def test_every_cut_at_the_seven_b_widths(plain_weights, kind, dtype):
+    """The four ways of cutting the work, at the widths where the tuned kernel variants live (two-tile blocks and
+    sixteen-warp split-K of the weight-streaming GEMM, the tcgen05 product from 1,024 rows, tcgen05 attention with
+    split keys, split-KV decode), with a pool so small that pages are used again; every row of every request
+    against the plain implementation, in both precisions."""
+    import test_step_scenarios as scenarios
+    rng = random.Random(17)
+    vocab = SHAPE["vocab_size"]
+    requests = {f"s{i}": helpers.random_prompt(rng, n, vocab) for i, n in enumerate((1100, 70, 300, 33))}
+    steps = scenarios._scenario(kind, requests, random.Random(5))
+    pages = helpers.peak_pages(steps, 16) + (0 if kind == "mixed" else 1)
+    runner = runner_for(dtype, pages, max_requests=4)
+    results = helpers.run_steps(runner, steps)
+    assert runner.cache.used_pages == 0
+    fed = {}
+    for entries, _ in steps:
+        for rid, toks, _w in entries:
+            fed.setdefault(rid, []).extend(toks)
+    worst = 0.0
+    for rid, ids in fed.items():
+        want = plain_model.forward_logits(SHAPE, plain_weights, ids).cpu()
+        got = torch.stack([results[(rid, p)] for p in range(len(ids))])
+        worst = max(worst, float((got - want).abs().max() / want.std(dim=-1).mean()))
+        helpers.assert_logits_close(got, want, dtype, f"7B widths, {kind}, {dtype}, {rid}", "7B widths")
+    print(f"7B widths {kind} {dtype}: worst |diff| / spread = {worst:.4f}")
+    from flexengine_b200 import ops
+    ops.check_status(DEV)

@@ -56,7 +56,7 @@ def _run(model_dir, name, kind, dtype, device, ops):
     for entries, _ in steps:
         for rid, toks, _w in entries:
             all_requests.setdefault(rid, []).extend(toks)
-    helpers.compare_with_plain(model_dir, results, all_requests, dtype, f"{name}/{kind}/{dtype}")
+    helpers.compare_with_plain(model_dir, results, all_requests, dtype, f"{name}/{kind}/{dtype}", config=name)
     if device != "cpu":
         from flexengine_b200 import ops as cuda_ops
         cuda_ops.check_status(device)
@@ -103,7 +103,7 @@ def test_short_portions_late_in_a_long_context(model_dirs, dtype):
     for rid, ids, first in (("long", long_ids, 0), ("side", side_ids[:side_at], 1089)):
         want = helpers.plain_logits(model_dirs["D"], ids, "cuda:0")
         got = torch.stack([results[(rid, p)] for p in range(first, len(ids))])
-        helpers.assert_logits_close(got, want[first:], dtype, f"long context, {rid}, {dtype}")
+        helpers.assert_logits_close(got, want[first:], dtype, f"long context, {rid}, {dtype}", "D")
     from flexengine_b200 import ops as cuda_ops
     cuda_ops.check_status("cuda:0")
 
