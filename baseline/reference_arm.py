@@ -8,7 +8,9 @@ libraries: random bfloat16 weights N(0, 0.02) of the Qwen2.5-7B shape in per-lay
 whose words are ``<id>``, so that a prompt of given token ids can be handed over as the string the reference's
 ``submit`` wants.  The metric and its configuration are those of the other arm: decode tokens per second at batch 8
 after 2,048-token prompts, context limit 4,096, page size 16, bfloat16; ``materialized`` attention (the backend of
-the reference's own published numbers) and no CUDA graphs.
+the reference's own published numbers) and the reference's own CUDA graphs for decode steps (its stock
+``cuda_graph=True`` path, src/flexengine/engine/runtime.py:44-49,216-240, captured for batch buckets 1, 2, 4, 8), unless
+``--no-cuda-graph`` is given.
 If any step cannot be done here the arm prints ``{"impl": "reference", "unavailable": "<why>"}`` and exits 0.
 """
 from __future__ import annotations
@@ -84,7 +86,9 @@ def main(args) -> int:
     if not os.path.isdir(os.path.join(REF, "flexengine")):
         return unavailable("the reference is not installed under baseline/_ref")
     sys.path.insert(0, ROOT)
-    from bench import CONTEXT_LEN, PAGE, PROMPT_LEN, SEVEN_B, ClockSampler
+    # sizes of the workload and the nvidia-smi sampler: plain Python shared with the other arm, no model or kernel code
+    from flexengine_b200.bench.clocks import ClockSampler
+    from flexengine_b200.bench.shapes import CONTEXT_LEN, PAGE, PROMPT_LEN, SEVEN_B, flat_config
     folder = None
     try:
         import torch
@@ -110,7 +114,7 @@ def main(args) -> int:
             model=folder, device="cuda:0", dtype="bfloat16", max_model_len=CONTEXT_LEN, max_num_seqs=batch,
             max_num_batched_tokens=PROMPT_LEN, prefill_chunk_size=PROMPT_LEN, max_waiting=max(64, batch),
             kv_block_size=PAGE, kv_num_blocks=batch * CONTEXT_LEN // PAGE, attention_backend="materialized",
-            max_output_tokens=512, trace_steps=False), adapter)
+            max_output_tokens=512, trace_steps=False, cuda_graph=bool(args.cuda_graph)), adapter)
         gen = torch.Generator().manual_seed(1)
         sampler = ClockSampler()
         sampler.start()
@@ -144,6 +148,7 @@ def main(args) -> int:
         if not all(len(r.generated_ids) == n + steps for r, n in zip(requests, before)):
             raise RuntimeError("a timed step of the reference was not a full decode step")
         sampler.stop()
+        graph_stats = engine.graph_manager.stats() if getattr(engine, "graph_manager", None) is not None else {}
         engine.stop()
         value = batch / (ms / 1e3)
         print(json.dumps({
@@ -151,11 +156,14 @@ def main(args) -> int:
             "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: random token ids, random weights N(0, 0.02)",
-            "config": {"model": "Qwen2.5-7B shape", "layers": cfg["num_hidden_layers"], "layers_full": SEVEN_B["num_hidden_layers"],
-                       "global_batch": batch, "seq_len": CONTEXT_LEN, "prompt_len": PROMPT_LEN, "kv_page": PAGE,
-                       "attention_backend": "materialized", "cuda_graph": False, "parallelism": "single GPU"},
+            "config": flat_config(cfg, model="Qwen2.5-7B shape", layers_full=SEVEN_B["num_hidden_layers"],
+                                  global_batch=batch, seq_len=CONTEXT_LEN, prompt_len=PROMPT_LEN, kv_page=PAGE,
+                                  parallelism="single GPU", cuda_graph=bool(args.cuda_graph),
+                                  attention_backend="materialized"),
             "e2e": {"value": value, "unit": "tokens/s", "note": "the reference's API is host tokens in and out; same run"},
-            "prefill": {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms},
+            "prefill": {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
+                        "note": "the reference's first step, cold"},
+            "reference_graphs": {k: graph_stats.get(k) for k in ("captures", "replays", "fallbacks")},
             "clocks": sampler.summary(windows)}))
         return 0
     except Exception as ex:  # noqa: BLE001 - whatever keeps the reference from running is reported, not raised

@@ -63,10 +63,10 @@ def test_bfloat16_prefill_on_tcgen05_then_graph_decode(plain_weights):
     ops.check_status(DEV)
     want = plain_model.forward_logits(SHAPE, plain_weights, long_ids[:1099]).cpu()
     picks = [0, 500, 1023, 1029, 1069] + list(range(1070, 1099))
-    helpers.assert_logits_close(torch.cat(rows[0]), want[picks], "bfloat16", "7B-shape long request")
+    helpers.assert_logits_close(torch.cat(rows[0]), want[picks], "bfloat16", "7B-shape long request", "7B widths")
     for j, ids in enumerate(short, start=1):
         want = plain_model.forward_logits(SHAPE, plain_weights, ids).cpu()
-        helpers.assert_logits_close(torch.cat(rows[j]), want[len(ids) - 31:], "bfloat16", f"7B-shape short request {j}")
+        helpers.assert_logits_close(torch.cat(rows[j]), want[len(ids) - 31:], "bfloat16", f"7B-shape short request {j}", "7B widths")
 
 
 def test_a_graph_keeps_its_scratch_when_a_later_bucket_needs_more(plain_weights):
@@ -94,7 +94,7 @@ def test_a_graph_keeps_its_scratch_when_a_later_bucket_needs_more(plain_weights)
     assert runner.graph_replays == 3 and sorted(runner._graphs) == [1, 8]
     want = plain_model.forward_logits(SHAPE, plain_weights, ids[0][:63]).cpu()
     got = torch.cat([first, all_eight[0:1], again])
-    helpers.assert_logits_close(got, want[[60, 61, 62]], "bfloat16", "graph replayed after the scratch grew")
+    helpers.assert_logits_close(got, want[[60, 61, 62]], "bfloat16", "graph replayed after the scratch grew", "7B widths")
     del junk
 
 
