@@ -98,25 +98,39 @@ def kernel_table(model, cfg: dict, batch: int, context: int, peaks: dict, timer=
                 fn(l, blocks[l])
         return run
 
+    # the forms a decode step runs: the product that ends a branch adds to the residual and begins the next norm, the
+    # product that reads the norm finishes it (no norm kernel between them)
+    eps = blocks[0].input_norm.eps
+    began = ops.linear(heads_out, blocks[0].mixer.out_weight, follow=(residual, blocks[0].post_mixer_norm.weight, eps))
+    fused = isinstance(began, ops.Prenormed)
+    normed = began if fused else hidden
+
     def project(l, b):
         m = b.mixer
         inv_freq, rot = m.position.rotary_table(dev)
         k_cache, v_cache = group.kv_slot(l)
-        ops.qkv_projection(hidden, m.qkv_weight, m.qkv_bias, ctx.positions, inv_freq, rot, group.slot_mapping, k_cache, v_cache,
+        ops.qkv_projection(normed, m.qkv_weight, m.qkv_bias, ctx.positions, inv_freq, rot, group.slot_mapping, k_cache, v_cache,
                            nq, nkv, d, page)
 
     def attend(l, b):
         k_cache, v_cache = group.kv_slot(l)
         ops.paged_attention(qkv, k_cache, v_cache, group.block_table, ctx, nq, nkv, d, page, b.mixer.scale, 0)
 
-    decode_row("norm (residual add + RMSNorm)", _time_graph(each_layer(
+    def end_branch(x, weight_of, norm_of):
+        def run(l, b):
+            ops.linear(x, weight_of(b), follow=(residual, norm_of(b).weight, eps))
+        return run
+
+    decode_row("norm as a kernel (first layer and final norm only)", _time_graph(each_layer(
         lambda l, b: ops.add_rmsnorm(residual, delta, b.input_norm.weight, b.input_norm.eps, torch.bfloat16))), 0)
-    decode_row("qkv projection + bias + rotary + cache write", _time_graph(each_layer(project)), (nq + 2 * nkv) * d * h * bf)
-    decode_row("decode attention (splits + merge)", _time_graph(each_layer(attend)), batch * (context + 1) * 2 * nkv * d * bf)
-    decode_row("output projection", _time_graph(each_layer(lambda l, b: ops.linear(heads_out, b.mixer.out_weight))), nq * d * h * bf)
-    decode_row("gate/up projection + SwiGLU", _time_graph(each_layer(
-        lambda l, b: ops.linear_swiglu(hidden, b.feed_forward.gate_up_weight, inter))), 2 * inter * h * bf)
-    decode_row("down projection", _time_graph(each_layer(lambda l, b: ops.linear(act, b.feed_forward.down_weight))), inter * h * bf)
+    decode_row("qkv projection: norm scale, bias, rotary, cache write", _time_graph(each_layer(project)), (nq + 2 * nkv) * d * h * bf)
+    decode_row("decode attention (splits merged in the cluster)", _time_graph(each_layer(attend)), batch * (context + 1) * 2 * nkv * d * bf)
+    decode_row("output projection + residual add + norm begun", _time_graph(each_layer(
+        end_branch(heads_out, lambda b: b.mixer.out_weight, lambda b: b.post_mixer_norm))), nq * d * h * bf)
+    decode_row("gate/up projection: norm scale, SwiGLU", _time_graph(each_layer(
+        lambda l, b: ops.linear_swiglu(normed, b.feed_forward.gate_up_weight, inter))), 2 * inter * h * bf)
+    decode_row("down projection + residual add + norm begun", _time_graph(each_layer(
+        end_branch(act, lambda b: b.feed_forward.down_weight, lambda b: b.input_norm))), inter * h * bf)
     logits = ops.linear(hidden, model.lm_head, None, out_float32=True)
     decode_row("vocabulary projection (once a step)", _time_graph(
         lambda: ops.linear(hidden, model.lm_head, None, out_float32=True)), vocab * h * bf, count=1)
@@ -140,6 +154,7 @@ def kernel_table(model, cfg: dict, batch: int, context: int, peaks: dict, timer=
     heads_out = torch.randn(T, nq * d, device=dev).to(torch.bfloat16)
     act = torch.randn(T, inter, device=dev).to(torch.bfloat16)
     qkv = torch.randn(T, (nq + 2 * nkv) * d, device=dev).to(torch.bfloat16)
+    normed = hidden
     prefill_row("norm (residual add + RMSNorm)", _time_eager(each_layer(
         lambda l, b: ops.add_rmsnorm(residual, delta, b.input_norm.weight, b.input_norm.eps, torch.bfloat16))), 0)
     prefill_row("qkv projection, bias + rotary + cache write", _time_eager(each_layer(project)), 2.0 * T * (nq + 2 * nkv) * d * h)

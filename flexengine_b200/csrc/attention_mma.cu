@@ -230,7 +230,25 @@ constexpr int DECODE_STAGES = 2;
 constexpr int DECODE_WARPS = 2;
 constexpr int DECODE_KEYS = TK / DECODE_WARPS;   // keys of a stage per warp
 
-template <int DMAX, bool UPPER>
+// CLUSTER: the blocks of one (request, key/value head), one per split of the keys, are a thread-block cluster.  Each
+// leaves its partial result in its own shared memory; after a cluster barrier every block merges its share of the
+// output elements, reading the other blocks' partial results through distributed shared memory.  No scratch memory,
+// no second kernel, and the merge takes the splits in index order whichever block runs where.
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster(const float* own, unsigned rank) {
+    // the same variable in the shared memory of block ``rank`` of this cluster
+    unsigned remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(own)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote));
+    return v;
+}
+constexpr int CLUSTER_MAX_SPLITS = 16;
+
+template <int DMAX, bool UPPER, bool CLUSTER = false>
 __global__ void __launch_bounds__(DECODE_WARPS * 32)
 paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                     float* __restrict__ part_o, float* __restrict__ part_lse, const bf16* __restrict__ kc,
@@ -311,7 +329,11 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
         hand[(DMAX / 2 + 2) * 32 + lane] = l[0]; hand[(DMAX / 2 + 3) * 32 + lane] = l[1];
     }
     __syncthreads();
-    if (warp == 1) return;
+    if (warp == 1 && !CLUSTER) return;
+    // where a block of a cluster leaves its partial result: rows of d + 1 floats (the head's output, then the
+    // logarithm of its sum), behind the memory the two warps exchange their results through
+    float* mine = reinterpret_cast<float*>(smem_raw) + (DMAX / 2 + 4) * 32;
+    if (warp == 0) {
 #pragma unroll
     for (int i = 0; i < (UPPER ? 2 : 1); ++i) {
         const float m1 = hand[(DMAX / 2 + i) * 32 + lane], l1 = hand[(DMAX / 2 + 2 + i) * 32 + lane];
@@ -331,7 +353,15 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
         if (row >= G) continue;
         const int head = kvh * G + row;
         const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
-        if (splits == 1) {
+        if (CLUSTER) {
+            float* po = mine + (size_t)row * (d + 1);
+#pragma unroll
+            for (int n = 0; n < DMAX / 8; ++n) {
+                const int col = n * 8 + 2 * t;
+                if (col < d) { po[col] = o[n][2 * i] * inv; po[col + 1] = o[n][2 * i + 1] * inv; }
+            }
+            if (t == 0) po[d] = l[i] > 0.f ? m[i] + log2f(l[i]) : -CUDART_INF_F;
+        } else if (splits == 1) {
             bf16* op = out + (size_t)tok * out_stride + (size_t)head * d;
 #pragma unroll
             for (int n = 0; n < DMAX / 8; ++n) {
@@ -349,6 +379,35 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
             }
             if (t == 0) part_lse[slot] = l[i] > 0.f ? m[i] + log2f(l[i]) : -CUDART_INF_F;
         }
+    }
+    }   // warp 0
+    if (CLUSTER) {
+        cluster_barrier();                        // every block's partial result is in its shared memory
+        // element e = (head of the group, column): the cluster's threads share them out; each adds the splits in
+        // index order, weighted by 2^(logarithm of the split's sum - the largest of them)
+        const int total = G * d;
+        for (int e = split * THREADS + threadIdx.x; e < total; e += splits * THREADS) {
+            const int row = e / d, col = e - row * d;
+            const float* lse_at = mine + (size_t)row * (d + 1) + d;
+            const float* val_at = mine + (size_t)row * (d + 1) + col;
+            float lse[CLUSTER_MAX_SPLITS], val[CLUSTER_MAX_SPLITS];
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int s2 = 0; s2 < CLUSTER_MAX_SPLITS; ++s2) {
+                lse[s2] = s2 < splits ? ld_cluster(lse_at, s2) : -CUDART_INF_F;
+                val[s2] = s2 < splits ? ld_cluster(val_at, s2) : 0.f;
+                mx = fmaxf(mx, lse[s2]);
+            }
+            float sum = 0.f, acc = 0.f;
+#pragma unroll
+            for (int s2 = 0; s2 < CLUSTER_MAX_SPLITS; ++s2) {
+                const float w = (s2 < splits && mx != -CUDART_INF_F) ? ex2(lse[s2] - mx) : 0.f;
+                sum += w;
+                acc += w * val[s2];
+            }
+            out[(size_t)tok * out_stride + (size_t)(kvh * G + row) * d + col] = __float2bfloat16_rn(sum > 0.f ? acc / sum : 0.f);
+        }
+        cluster_barrier();                        // nobody leaves while its shared memory may still be read
     }
 }
 
@@ -620,6 +679,56 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
         return fe_check_launch("paged_decode combine");
     }
     return 0;
+}
+
+// The same attention with the splits of a (request, key/value head) as one thread-block cluster that merges its
+// partial results through distributed shared memory: one kernel, no scratch memory.  1 <= splits <= 16 (clusters
+// of more than 8 blocks are asked for as a non-portable size); the cluster must fit the device, else an error.
+extern "C" int fe_paged_decode_cluster_max_splits(void) { return CLUSTER_MAX_SPLITS; }
+
+extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* out, long long out_stride,
+                                       const void* kc, const void* vc, const int* block_table, int bt_stride,
+                                       const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,
+                                       int num_pages, float scale, int window, int splits, int* status,
+                                       cudaStream_t stream) {
+    if (check_common("paged_decode", nq, nkv, d, ps, num_pages, window, q_stride, out_stride)) return 1;
+    FE_REQUIRE(nq / nkv <= 16, "paged_decode: %d query heads per key/value head; this kernel takes up to 16", nq / nkv);
+    FE_REQUIRE(splits >= 1 && splits <= CLUSTER_MAX_SPLITS && requests >= 0,
+               "paged_decode (cluster): %d splits; a cluster takes 1 to %d", splits, CLUSTER_MAX_SPLITS);
+    FE_REQUIRE(nkv <= 65535 && requests <= 65535, "paged_decode (cluster): grid too large");
+    if (requests == 0) return 0;
+    const float scale_log2 = scale * LOG2E;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, nkv, requests);
+    cfg.blockDim = dim3(DECODE_WARPS * 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define FE_DECODE_CLUSTER(DMAX, UPPER)                                                                                 \
+    do {                                                                                                               \
+        auto kernel = paged_decode_kernel<DMAX, UPPER, true>;                                                          \
+        if (allow_smem(kernel, decode_smem<DMAX>(), "paged_decode (cluster)")) return 1;                               \
+        if (splits > 8) {                                                                                              \
+            const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);    \
+            FE_REQUIRE(err == cudaSuccess, "paged_decode (cluster): %s", cudaGetErrorString(err));                      \
+        }                                                                                                              \
+        cfg.dynamicSmemBytes = decode_smem<DMAX>();                                                                    \
+        const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, (const bf16*)q, q_stride, (bf16*)out, out_stride,     \
+            (float*)nullptr, (float*)nullptr, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, \
+            nq, nkv, d, ps, num_pages, scale_log2, window, status);                                                    \
+        FE_REQUIRE(err == cudaSuccess, "paged_decode (cluster of %d): %s", splits, cudaGetErrorString(err));           \
+    } while (0)
+    const bool upper = nq / nkv > 8;
+    if (d <= 64) { if (upper) FE_DECODE_CLUSTER(64, true); else FE_DECODE_CLUSTER(64, false); }
+    else if (d <= 128) { if (upper) FE_DECODE_CLUSTER(128, true); else FE_DECODE_CLUSTER(128, false); }
+    else { if (upper) FE_DECODE_CLUSTER(256, true); else FE_DECODE_CLUSTER(256, false); }
+#undef FE_DECODE_CLUSTER
+    return fe_check_launch("paged_decode (cluster)");
 }
 
 extern "C" int fe_paged_decode_mma(const void* q, long long q_stride, void* out, long long out_stride, void* scratch,

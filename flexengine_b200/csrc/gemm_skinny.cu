@@ -10,8 +10,19 @@
 // partial sums of a block are added in shared memory in a fixed order (deterministic).
 //
 // Epilogues: bfloat16 output; float output (vocabulary projection); SwiGLU, where a block pairs
-// 8 gate rows with their 8 up rows of a [2I, K] matrix and writes silu(gate) * up.
+// 8 gate rows with their 8 up rows of a [2I, K] matrix and writes silu(gate) * up; the fused
+// query/key/value epilogue; and the residual epilogue, which ends a branch of a layer and begins
+// the norm that follows it (below).
 // The reference runs these products through cuBLAS (inference/models/qwen2.py:99-101,129-135).
+//
+// Residual add and RMSNorm without a kernel of their own.  In a decode step a norm moves a few kilobytes
+// between two products that stream hundreds of megabytes; as a kernel it costs a launch and a few trips to
+// memory.  Instead the product that ends a branch (output projection, down projection) adds its result to the
+// float residual stream in its epilogue, writes the new residual times the next norm's weight as bfloat16,
+// and leaves each block's share of the rows' sums of squares in a small table; the product that consumes the
+// norm (query/key/value, gate/up) adds the table up in a fixed order while its first weights are on their way
+// and multiplies its accumulators by rsqrt(mean square + eps): a row's scale is a factor of every term of its
+// dot products, so it may be applied after them.
 #include "common.cuh"
 
 using namespace fe;
@@ -21,7 +32,24 @@ namespace {
 constexpr int WARPS_USUAL = 8, WARPS_NARROW = 16;
 constexpr int KSTEP = 64;       // k elements per warp step (4 MMAs)
 
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_RESID = 4 };
+
+// The residual epilogue: out[m][n] is not written; residual[m][n] += product, scaled[m][n] = bfloat16(residual *
+// norm_weight[n]), sumsq[tile][m] = this tile's share of the sum of squares of row m of the new residual.
+struct ResidEpilogue {
+    float* residual;            // [M, N] float, updated in place (every element by the one block that owns it)
+    const float* norm_weight;   // [N]
+    bf16* scaled;               // [M, N]
+    float* sumsq;               // [tiles of 16 columns][8]
+};
+
+// What a consumer of such a norm gets instead of normalised rows: the table of partial sums of squares.
+struct RowScale {
+    const float* sumsq;         // [tiles][8] or nullptr: the input is normalised already
+    int tiles;
+    float eps;
+    int width;                  // elements of a row (the mean is over them)
+};
 
 // What the fused query/key/value epilogue needs beside the product: bias, rotary table, where the
 // new keys and values go in the paged cache (see elementwise.cu for the unfused form of the same).
@@ -79,10 +107,14 @@ __device__ __forceinline__ void mma16816(float* c, unsigned a0, unsigned a1, uns
 // WARPS: warps that split K (8; 16 for a narrow matrix with a long K, whose few blocks leave SMs empty: the blocks
 //     it has then keep twice as many loads in flight)
 template <int NT, int EPI, int RT, int PF, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+// blocks an SM: three of the light variant (80 registers a thread), two of the others with eight warps (128)
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 1 : (NT == 1 && RT == 1 && PF == 2) ? 3 : NT == 1 ? 2 : 1)
 skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void* __restrict__ out, int M, int N, int K,
-                   int I, const QkvEpilogue qkv) {
+                   int I, const QkvEpilogue qkv, const ResidEpilogue resid, const RowScale scale) {
     __shared__ float red[WARPS][RT * NT * 8 * 16];
+    __shared__ float scale_part[WARPS * 4][8];     // partial sums of squares: [share of the tiles][row]
+    extern __shared__ __align__(16) float scale_table[];      // [scale.tiles][8], when the input rows are to be scaled
+    __shared__ float row_scale[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     // rows of W behind accumulator rows g and g + 8 of tile r
     const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? 8 : 16) * RT;
@@ -135,7 +167,19 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
         }
         // the weights above depend on no kernel; the activations below are the previous kernel's
         // output, so the first batch of weight loads is already in flight while that kernel ends
-        if (s == s_begin) { griddep_wait(); griddep_launch_dependents(); }
+        if (s == s_begin) {
+            griddep_wait();
+            griddep_launch_dependents();
+            // the table of the rows' sums of squares is needed in the epilogue: asynchronous copies bring it into
+            // shared memory meanwhile, so that no thread waits for it now and no block waits for memory at its end
+            if (scale.sumsq != nullptr) {
+                for (int chunk = threadIdx.x; chunk < scale.tiles * 2; chunk += WARPS * 32) {
+                    const unsigned dst = (unsigned)__cvta_generic_to_shared(scale_table + chunk * 4);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(scale.sumsq + (size_t)chunk * 4));
+                }
+                asm volatile("cp.async.commit_group;\n" ::);
+            }
+        }
 #pragma unroll
         for (int p = 0; p < PF; ++p) {
             const int sp = s + p;
@@ -167,7 +211,17 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             }
         }
     }
-    if (s_begin >= s_end) { griddep_wait(); griddep_launch_dependents(); }   // a warp without work has not waited yet
+    if (s_begin >= s_end) {                    // a warp without work has not waited yet, nor started its copies
+        griddep_wait();
+        griddep_launch_dependents();
+        if (scale.sumsq != nullptr) {
+            for (int chunk = threadIdx.x; chunk < scale.tiles * 2; chunk += WARPS * 32) {
+                const unsigned dst = (unsigned)__cvta_generic_to_shared(scale_table + chunk * 4);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(scale.sumsq + (size_t)chunk * 4));
+            }
+            asm volatile("cp.async.commit_group;\n" ::);
+        }
+    }
     // accumulator (tile r, row g + 8 (e >> 1), batch column nt * 8 + 2t + (e & 1)) -> red[warp][(r, column, row)]
 #pragma unroll
     for (int r = 0; r < RT; ++r)
@@ -176,7 +230,24 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 #pragma unroll
             for (int e = 0; e < 4; ++e)
                 red[warp][(r * NT * 8 + nt * 8 + 2 * t + (e & 1)) * 16 + g + 8 * (e >> 1)] = acc[r][nt][e];
+    if (scale.sumsq != nullptr) asm volatile("cp.async.wait_all;\n" ::: "memory");
     __syncthreads();
+    if (scale.sumsq != nullptr) {
+        // thread = (row m, one of WARPS * 4 shares of the tiles): a thread adds its tiles in ascending order; the
+        // shares are then added in a fixed order
+        const int m = threadIdx.x & 7, share = threadIdx.x >> 3;
+        float sum = 0.f;
+        for (int tile = share; tile < scale.tiles; tile += WARPS * 4) sum += scale_table[tile * 8 + m];
+        scale_part[share][m] = sum;
+        __syncthreads();
+        if (threadIdx.x < 8) {
+            float sum = 0.f;
+#pragma unroll
+            for (int share = 0; share < WARPS * 4; ++share) sum += scale_part[share][threadIdx.x];
+            row_scale[threadIdx.x] = rsqrtf(sum / (float)scale.width + scale.eps);
+        }
+        __syncthreads();
+    }
     if (EPI == EPI_QKV) {
         // bias, rotation by the token's position, and the write of new keys and values to their pages
         int row0, row1, head, j0;
@@ -189,6 +260,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             float a = 0.f, c = 0.f;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) { a += red[w][m * 16 + r]; c += red[w][m * 16 + r + 8]; }
+            if (scale.sumsq != nullptr) { a *= row_scale[m]; c *= row_scale[m]; }
             const int f0 = row0 + r, f1 = f0 + partner;              // features of the two values
             if (qkv.bias) { a += qkv.bias[f0]; c += qkv.bias[f1]; }
             if (rotated) {
@@ -226,7 +298,31 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
                 gate += red[w][(r * NT * 8 + m) * 16 + row];
                 up += red[w][(r * NT * 8 + m) * 16 + row + 8];
             }
+            if (scale.sumsq != nullptr) { gate *= row_scale[m]; up *= row_scale[m]; }
             reinterpret_cast<bf16*>(out)[(size_t)m * I + n] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+        }
+    } else if (EPI == EPI_RESID) {
+        // NT == 1: idx = (tile r, row m of the batch, column of the tile); the 16 columns of a (tile, row) sit in
+        // 16 consecutive lanes, which add their squares up with shuffles
+        for (int idx = threadIdx.x; idx < RT * 128; idx += WARPS * 32) {
+            const int r = idx >> 7, m = (idx >> 4) & 7, row = idx & 15;
+            const int n = n0 + r * 16 + row;
+            float square = 0.f;
+            if (m < M && n < N) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) v += red[w][(r * 8 + m) * 16 + row];
+                if (scale.sumsq != nullptr) v *= row_scale[m];
+                const size_t at = (size_t)m * N + n;
+                const float sum = resid.residual[at] + v;
+                resid.residual[at] = sum;
+                resid.scaled[at] = __float2bfloat16_rn(sum * resid.norm_weight[n]);
+                square = sum * sum;
+            }
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) square += __shfl_xor_sync(0xffffffffu, square, o);
+            const int tile = blockIdx.x * RT + r;
+            if (row == 0 && tile * 16 < N) resid.sumsq[(size_t)tile * 8 + m] = square;
         }
     } else {
         for (int idx = threadIdx.x; idx < RT * NT * 8 * 16; idx += WARPS * 32) {
@@ -237,6 +333,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) v += red[w][(r * NT * 8 + m) * 16 + row];
+            if (scale.sumsq != nullptr) v *= row_scale[m];
             if (EPI == EPI_F32) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
             else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v);
         }
@@ -245,21 +342,23 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
 
 template <int EPI>
 int launch(const void* x, const void* W_, void* out, int M, int N, int K, int I, cudaStream_t stream,
-           const QkvEpilogue& qkv = QkvEpilogue{}) {
+           const QkvEpilogue& qkv = QkvEpilogue{}, const ResidEpilogue& resid = ResidEpilogue{}, const RowScale& scale = RowScale{}) {
     const int tiles = EPI == EPI_SWIGLU ? (I + 7) / 8 : (N + 15) / 16;
     // Three one-tile blocks are resident on an SM (80 registers a thread), two of the others (120 to 128).  A matrix
     // with more tiles than one round of one-tile blocks takes two tiles a block: a few blocks over the round would
     // run alone after it (448 tiles: 15.9 -> 13.6 us).  A narrow one, whose blocks are all resident at once even two
     // to an SM: every warp sends twice as many loads ahead, which halves the number of round trips to memory.
     const int sms = fe_sm_count();
+    const size_t table_bytes = scale.sumsq != nullptr ? (size_t)scale.tiles * 8 * sizeof(float) : 0;
     const bool wide = EPI != EPI_QKV && tiles > 3 * sms;
     const bool deep = !wide && tiles <= 2 * sms;
     const int blocks = wide ? (tiles + 1) / 2 : tiles;
     // fewer blocks than SMs, and at least one round of loads (four steps) for each of sixteen warps
-    const bool narrow = (EPI == EPI_BF16 || EPI == EPI_F32) && M <= 8 && tiles <= sms && K / KSTEP >= 4 * WARPS_NARROW;
+    const bool narrow = (EPI == EPI_BF16 || EPI == EPI_F32 || EPI == EPI_RESID) && M <= 8 && tiles <= sms && K / KSTEP >= 4 * WARPS_NARROW;
 #define FE_SKINNY(NT, RT, PF, W) \
-    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF, W>, blocks, W * 32, 0, stream, (const bf16*)x, (const bf16*)W_, out, M, N, K, I, qkv)
+    fe::launch(skinny_gemm_kernel<NT, EPI, RT, PF, W>, blocks, W * 32, table_bytes, stream, (const bf16*)x, (const bf16*)W_, out, M, N, K, I, qkv, resid, scale)
     if (narrow) FE_SKINNY(1, 1, 4, WARPS_NARROW);
+    else if (EPI == EPI_RESID && M > 8) return 1;          // refused by the entry point already
     else if (M <= 8) { if (wide) FE_SKINNY(1, 2, 2, WARPS_USUAL); else if (deep) FE_SKINNY(1, 1, 4, WARPS_USUAL); else FE_SKINNY(1, 1, 2, WARPS_USUAL); }
     else { if (wide) FE_SKINNY(2, 2, 2, WARPS_USUAL); else if (deep) FE_SKINNY(2, 1, 4, WARPS_USUAL); else FE_SKINNY(2, 1, 2, WARPS_USUAL); }
 #undef FE_SKINNY
@@ -268,33 +367,71 @@ int launch(const void* x, const void* W_, void* out, int M, int N, int K, int I,
 
 }  // namespace
 
+// The input rows' scales, when the input is a residual times a norm's weight and not yet divided by its root mean
+// square (see the top of this file): ``sumsq`` [sumsq_tiles][8] is the table the residual epilogue left.
+static int check_scale(const char* what, const float* sumsq, int sumsq_tiles, int M, int K) {
+    if (sumsq == nullptr) return 0;
+    FE_REQUIRE(M <= 8, "%s: rows are scaled from a table of sums of squares for up to 8 rows, got %d", what, M);
+    FE_REQUIRE(sumsq_tiles == (K + 15) / 16, "%s: the table of sums of squares has %d tiles; a row of %d elements has %d",
+               what, sumsq_tiles, K, (K + 15) / 16);
+    FE_REQUIRE(sumsq_tiles <= 1024 && ((size_t)sumsq & 15) == 0, "%s: the table of sums of squares must be 16-byte aligned "
+               "and hold at most 1024 tiles (rows of up to 16384 elements)", what);
+    return 0;
+}
+
 // epilogue: 0 bfloat16 [M, N]; 1 float [M, N]; 2 SwiGLU: W is [2 I, K] (gate rows, then up rows), out bfloat16 [M, I].
-extern "C" int fe_skinny_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
-                              cudaStream_t stream) {
+// ``sumsq`` (may be null): see check_scale.
+extern "C" int fe_skinny_gemm_scaled(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
+                                     const float* sumsq, int sumsq_tiles, float eps, cudaStream_t stream) {
     FE_REQUIRE(M >= 1 && M <= 16, "skinny_gemm: %d rows; this kernel takes 1 to 16", M);
     FE_REQUIRE(N > 0 && K > 0 && K % KSTEP == 0, "skinny_gemm: K = %d must be a positive multiple of %d", K, KSTEP);
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_gemm: operands must be 16-byte aligned");
-    if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, 0, stream);
-    if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, M, N, K, 0, stream);
+    if (check_scale("skinny_gemm", sumsq, sumsq_tiles, M, K)) return 1;
+    const RowScale scale{sumsq, sumsq_tiles, eps, K};
+    if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
+    if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
     if (epilogue == EPI_SWIGLU) {
         FE_REQUIRE(N % 2 == 0, "skinny_gemm: SwiGLU needs an even number of weight rows, got %d", N);
-        return launch<EPI_SWIGLU>(x, W, out, M, N, K, N / 2, stream);
+        return launch<EPI_SWIGLU>(x, W, out, M, N, K, N / 2, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
     }
     FE_REQUIRE(false, "skinny_gemm: unknown epilogue %d", epilogue);
+}
+
+extern "C" int fe_skinny_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
+                              cudaStream_t stream) {
+    return fe_skinny_gemm_scaled(x, W, out, M, N, K, epilogue, nullptr, 0, 0.f, stream);
+}
+
+// The product that ends a branch of a layer: residual[M, N] += x W^T (float, in place); scaled[M, N] = bfloat16(new
+// residual * norm_weight); sumsq_out[ceil(N / 16)][8] = each 16-column tile's share of the rows' sums of squares.
+// ``sumsq_in`` (may be null): the scales of the input rows, as for fe_skinny_gemm_scaled.  M <= 8.
+extern "C" int fe_skinny_gemm_residual(const void* x, const void* W, float* residual, const float* norm_weight, void* scaled,
+                                       float* sumsq_out, int M, int N, int K, const float* sumsq_in, int sumsq_tiles,
+                                       float eps, cudaStream_t stream) {
+    FE_REQUIRE(M >= 1 && M <= 8, "skinny_gemm_residual: %d rows; this kernel takes 1 to 8", M);
+    FE_REQUIRE(N > 0 && K > 0 && K % KSTEP == 0, "skinny_gemm_residual: K = %d must be a positive multiple of %d", K, KSTEP);
+    FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_gemm_residual: operands must be 16-byte aligned");
+    FE_REQUIRE(residual && norm_weight && scaled && sumsq_out, "skinny_gemm_residual: a null pointer");
+    if (check_scale("skinny_gemm_residual", sumsq_in, sumsq_tiles, M, K)) return 1;
+    const ResidEpilogue resid{residual, norm_weight, (bf16*)scaled, sumsq_out};
+    return launch<EPI_RESID>(x, W, nullptr, M, N, K, 0, stream, QkvEpilogue{}, resid, RowScale{sumsq_in, sumsq_tiles, eps, K});
 }
 
 // The query/key/value projection of an attention layer with its epilogue fused: y = x W^T + bias,
 // half-split rotation of the query and key heads by the tokens' positions, in place into
 // out [M, (nq + 2 nkv) d] (bfloat16), and the write of the new keys and values into their cache
 // slots.  The whole head is rotated (rotary width = head size, a multiple of 16); M <= 8.
+// ``sumsq`` (may be null): the scales of the input rows, as for fe_skinny_gemm_scaled.
 extern "C" int fe_skinny_qkv(const void* x, const void* W, void* out, const float* bias, const int* positions,
                              const float* inv_freq, const int* slot_mapping, void* kc, void* vc, int M, int K, int nq,
-                             int nkv, int d, int ps, long long num_slots, int* status, cudaStream_t stream) {
+                             int nkv, int d, int ps, long long num_slots, const float* sumsq, int sumsq_tiles, float eps,
+                             int* status, cudaStream_t stream) {
     FE_REQUIRE(M >= 1 && M <= 8, "skinny_qkv: %d rows; this kernel takes 1 to 8", M);
     FE_REQUIRE(K > 0 && K % KSTEP == 0, "skinny_qkv: K = %d must be a positive multiple of %d", K, KSTEP);
     FE_REQUIRE(d >= 16 && d % 16 == 0 && nq > 0 && nkv > 0 && ps > 0, "skinny_qkv: bad head size or counts");
     FE_REQUIRE(positions != nullptr && inv_freq != nullptr, "skinny_qkv: positions and the rotary table are required");
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_qkv: operands must be 16-byte aligned");
+    if (check_scale("skinny_qkv", sumsq, sumsq_tiles, M, K)) return 1;
     QkvEpilogue e{bias, positions, inv_freq, slot_mapping, (bf16*)kc, (bf16*)vc, nq, nkv, d, ps, num_slots, status};
-    return launch<EPI_QKV>(x, W, out, M, (nq + 2 * nkv) * d, K, 0, stream, e);
+    return launch<EPI_QKV>(x, W, out, M, (nq + 2 * nkv) * d, K, 0, stream, e, ResidEpilogue{}, RowScale{sumsq, sumsq_tiles, eps, K});
 }

@@ -146,6 +146,36 @@ def add_rmsnorm(residual, delta, weight, eps, out_dtype, rows=None, upcoming=Non
     return out
 
 
+FUSES_RESIDUAL_NORM = True      # linear(..., follow=) may end a branch: see Prenormed
+
+
+class Prenormed:
+    """Rows that are halfway through an RMSNorm, as the residual epilogue of the weight-streaming GEMM leaves them
+    (csrc/gemm_skinny.cu): ``scaled`` = bfloat16(residual * norm weight), not yet divided by the rows' root mean
+    square, and ``sumsq`` [tiles of 16 columns, 8], every tile's share of the rows' sums of squares.  The products
+    that consume a norm (``linear``, ``linear_swiglu``, ``qkv_projection``) take it in place of a tensor and
+    finish the norm in their own epilogue; where that kernel does not apply, ``materialize`` runs the norm
+    kernel over the residual, which holds the sum already."""
+    __slots__ = ("scaled", "sumsq", "eps", "residual", "weight")
+
+    def __init__(self, scaled, sumsq, eps, residual, weight):
+        self.scaled, self.sumsq, self.eps, self.residual, self.weight = scaled, sumsq, float(eps), residual, weight
+
+    shape = property(lambda self: self.scaled.shape)
+    dtype = property(lambda self: self.scaled.dtype)
+    device = property(lambda self: self.scaled.device)
+
+    def materialize(self):
+        return add_rmsnorm(self.residual, None, self.weight, self.eps, self.scaled.dtype)
+
+
+def _rows_and_scale(x):
+    """(tensor, sumsq pointer, tiles, eps) of an input that may be a Prenormed."""
+    if isinstance(x, Prenormed):
+        return x.scaled, _ptr(x.sumsq), _c_int(x.sumsq.shape[0]), _c_float(x.eps)
+    return x, None, _c_int(0), _c_float(0.0)
+
+
 def gemm_fp32(x, w, bias=None):
     M, K = x.shape
     N = w.shape[0]
@@ -154,11 +184,34 @@ def gemm_fp32(x, w, bias=None):
     return out
 
 
-def linear(x, w, bias=None, out_float32=False):
+def linear(x, w, bias=None, out_float32=False, follow=None):
     """y = x w^T (+ bias); x [M, K], w [N, K].  A float32 weight runs the true 32-bit product
     (CUDA cores, no reduced-precision mode) whatever the activation dtype; a bfloat16 weight
-    runs on tensor cores with float32 accumulation."""
-    _need_cuda(x, w, bias)
+    runs on tensor cores with float32 accumulation.
+
+    ``follow`` = (residual, norm weight, eps): the product ends a branch of a layer; its result is to be added to
+    the float32 residual stream [M, N] and an RMSNorm reads the sum next.  Where the weight-streaming kernel runs (a
+    decode step), it does both in its epilogue and a ``Prenormed`` comes back; otherwise the plain product does,
+    and the caller adds and normalises as usual."""
+    if isinstance(x, Prenormed) and not (skinny_ok(x.scaled, w) and x.scaled.shape[0] <= SKINNY_MAX_ROWS):
+        x = x.materialize()
+    rows, sumsq, tiles, eps = _rows_and_scale(x)
+    _need_cuda(rows, w, bias)
+    if follow is not None and bias is None and not out_float32 and skinny_ok(rows, w):
+        residual, norm_weight, norm_eps = follow
+        M, N = rows.shape[0], w.shape[0]
+        if (residual.dtype == torch.float32 and tuple(residual.shape) == (M, N) and residual.is_contiguous()
+                and norm_weight.dtype == torch.float32 and norm_weight.numel() == N):
+            scaled = torch.empty((M, N), dtype=torch.bfloat16, device=rows.device)
+            table = torch.empty((-(-N // 16), 8), dtype=torch.float32, device=rows.device)
+            _run(_bf16(), "fe_skinny_gemm_residual", _ptr(rows), _ptr(w), _ptr(residual), _ptr(norm_weight), _ptr(scaled),
+                 _ptr(table), _c_int(M), _c_int(N), _c_int(rows.shape[1]), sumsq, tiles, eps, _stream())
+            return Prenormed(scaled, table, norm_eps, residual, norm_weight)
+    if isinstance(x, Prenormed):
+        y = skinny_gemm(x, w, EPI_F32 if (out_float32 or bias is not None) else EPI_BF16)
+        if bias is not None:
+            y += bias
+        return y if out_float32 or bias is None else y.to(torch.bfloat16)
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise ValueError(f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)}")
     if not x.is_contiguous():
@@ -192,15 +245,16 @@ def skinny_ok(x, w) -> bool:
 
 
 def skinny_gemm(x, w, epilogue: int = EPI_BF16):
-    """x [M <= 16, K] times w [N, K]^T by streaming w once; see csrc/gemm_skinny.cu."""
+    """x [M <= 16, K] (a tensor or a Prenormed) times w [N, K]^T by streaming w once; see csrc/gemm_skinny.cu."""
+    x, sumsq, tiles, eps = _rows_and_scale(x)
     M, K = x.shape
     N = w.shape[0]
     if epilogue == EPI_SWIGLU:
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
     else:
         out = torch.empty((M, N), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=x.device)
-    _run(_bf16(), "fe_skinny_gemm", _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue),
-         _stream())
+    _run(_bf16(), "fe_skinny_gemm_scaled", _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue),
+         sumsq, tiles, eps, _stream())
     return out
 
 
@@ -276,6 +330,10 @@ def swiglu(gate_up, intermediate):
 
 def linear_swiglu(x, w, intermediate):
     """silu(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]); one kernel for a handful of rows."""
+    if isinstance(x, Prenormed):
+        if skinny_ok(x.scaled, w) and w.shape[0] == 2 * intermediate:
+            return skinny_gemm(x, w, EPI_SWIGLU)
+        x = x.materialize()
     if skinny_ok(x, w) and w.shape[0] == 2 * intermediate:
         return skinny_gemm(x, w, EPI_SWIGLU)
     if tcgen05_ok(x, w) and w.shape[0] == 2 * intermediate:
@@ -316,16 +374,20 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
     write).  Returns qkv [T, (nq + 2 nkv) d].  For a handful of rows (decode) with the whole head
     rotated this is ONE kernel (csrc/gemm_skinny.cu); otherwise the product and the fused
     bias/rotation/cache-write kernel."""
-    _need_cuda(h, w, bias, positions, inv_freq, slot_mapping, k_cache, v_cache)
-    if (skinny_ok(h, w) and h.shape[0] <= SKINNY_QKV_MAX_ROWS and inv_freq is not None and rot == d and d % 16 == 0
+    rows, sumsq, tiles, eps = _rows_and_scale(h)
+    _need_cuda(rows, w, bias, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    if (skinny_ok(rows, w) and rows.shape[0] <= SKINNY_QKV_MAX_ROWS and inv_freq is not None and rot == d and d % 16 == 0
             and k_cache.dtype == torch.bfloat16
             and w.shape[0] == (nq + 2 * nkv) * d and (bias is None or bias.dtype == torch.float32)):
-        T = h.shape[0]
-        out = torch.empty((T, w.shape[0]), dtype=torch.bfloat16, device=h.device)
-        _run(_bf16(), "fe_skinny_qkv", _ptr(h), _ptr(w), _ptr(out), _ptr(bias), _ptr(positions), _ptr(inv_freq),
-             _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(h.shape[1]), _c_int(nq), _c_int(nkv),
-             _c_int(d), _c_int(page_size), _c_ll(k_cache.shape[0] * page_size), _ptr(status_word(h.device)), _stream())
+        T = rows.shape[0]
+        out = torch.empty((T, w.shape[0]), dtype=torch.bfloat16, device=rows.device)
+        _run(_bf16(), "fe_skinny_qkv", _ptr(rows), _ptr(w), _ptr(out), _ptr(bias), _ptr(positions), _ptr(inv_freq),
+             _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(rows.shape[1]), _c_int(nq), _c_int(nkv),
+             _c_int(d), _c_int(page_size), _c_ll(k_cache.shape[0] * page_size), sumsq, tiles, eps,
+             _ptr(status_word(rows.device)), _stream())
         return out
+    if isinstance(h, Prenormed):
+        h = h.materialize()
     if h.dtype == torch.float32:
         qkv = linear(h, w)
         qkv_bias_rope_cache(qkv, bias, positions, inv_freq, rot, slot_mapping, k_cache, v_cache, nq, nkv, d, page_size)
@@ -423,6 +485,35 @@ def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, 
     return out
 
 
+DECODE_CLUSTER_MAX_SPLITS = 16       # blocks of one thread-block cluster (fe_paged_decode_cluster_max_splits)
+DECODE_CLUSTER_MAX_TILES = 8         # a split of a cluster walks at most this many tiles of 32 keys ...
+
+
+def decode_cluster_splits(splits: int, max_ctx_len: int) -> int:
+    """How many splits the cluster kernel takes for a step that ``decode_splits`` would split ``splits`` ways, or 0
+    when the two-kernel form is the better one: a cluster holds 16 blocks at most, so a long context of a small
+    batch, which wants more splits than that, keeps them and the separate merge."""
+    if splits <= 1:
+        return 0
+    if splits <= DECODE_CLUSTER_MAX_SPLITS:
+        return splits
+    tiles = -(-max_ctx_len // 32)
+    return DECODE_CLUSTER_MAX_SPLITS if tiles <= DECODE_CLUSTER_MAX_SPLITS * DECODE_CLUSTER_MAX_TILES else 0
+
+
+def paged_decode_cluster(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
+                         scale, window, splits, out=None):
+    """Decode attention with the splits of each (request, key/value head) as one thread-block cluster that merges
+    its partial results through distributed shared memory: one launch, no scratch memory; splits <= 16."""
+    if out is None:
+        out = torch.empty((requests, nq * d), dtype=torch.bfloat16, device=k_cache.device)
+    _run(_bf16(), "fe_paged_decode_cluster", _ptr(q), _c_ll(q_stride), _ptr(out), _c_ll(out.stride(0)), _ptr(k_cache),
+         _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _ptr(cu_q), _ptr(q_start), _c_int(requests),
+         _c_int(nq), _c_int(nkv), _c_int(d), _c_int(page_size), _c_int(k_cache.shape[0]), _c_float(scale), _c_int(window),
+         _c_int(splits), _ptr(status_word(k_cache.device)), _stream())
+    return out
+
+
 def paged_prefill_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, T, requests, max_q_len, nq, nkv, d,
                       page_size, scale, window):
     """Tensor-core attention for portions of any length (decoded tokens are portions of one)."""
@@ -500,6 +591,10 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     requests = ctx.cu_q.numel() - 1
     if ctx.max_q_len == 1 and nq // nkv <= 16:
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
+        clustered = decode_cluster_splits(splits, ctx.max_ctx_len)
+        if clustered:
+            return paged_decode_cluster(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
+                                        nq, nkv, d, page_size, scale, window, clustered)
         return paged_decode_mma(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
                                 nq, nkv, d, page_size, scale, window, splits, upcoming=upcoming)
     lengths = getattr(ctx, "host_lengths", None)

@@ -16,6 +16,8 @@ from .spec import PartSpec
 
 
 class AttentionMixer(Mixer):
+    takes_prenormed = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec | dict | None = None, qkv_bias: bool = True, out_bias: bool = False,
                  window: int = 0, scale: float | None = None):
@@ -54,7 +56,7 @@ class AttentionMixer(Mixer):
         return {"kind": "window" if self.window > 0 else "full", "kv_heads": self.num_kv_heads,
                 "head_dim": self.head_dim, "window": self.window}
 
-    def forward(self, ctx, h, entry):
+    def forward(self, ctx, h, entry, follow=None):
         ops = ctx.ops
         group = ctx.groups[entry.cache_group]
         k_cache, v_cache = group.kv_slot(entry.cache_slot)
@@ -76,6 +78,8 @@ class AttentionMixer(Mixer):
         out = ops.paged_attention(qkv, k_cache, v_cache, group.block_table, ctx, self.num_heads,
                                   self.num_kv_heads, self.head_dim, group.page_size, self.scale, self.window,
                                   upcoming=self.out_weight)
+        if follow is not None:
+            return ops.linear(out, self.out_weight, self.out_bias, follow=follow)
         return ops.linear(out, self.out_weight, self.out_bias)
 
 

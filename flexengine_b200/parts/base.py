@@ -21,7 +21,8 @@ FeedForward:     ``forward(ctx, h) -> delta [T, hidden]``.
 Norm:            ``forward(ctx, residual, delta, rows=None) -> h``: adds ``delta`` (may be None)
                  to the float32 residual stream in place and returns the normalised rows
                  in the compute dtype; with ``rows`` it reads only those rows and leaves the
-                 residual untouched.
+                 residual untouched.  ``following(ctx, residual)`` may return what a product needs
+                 to do this norm's work in its own epilogue (see "a norm that follows" below).
 PositionEncoding: ``rotary_table(device)`` -> (inv_freq float32 [rot/2], rot) for the half-split
                  rotation that the mixer's kernel does itself, or None for no rotation there; an
                  encoding of its own overrides ``apply(ctx, q, k)``, which rewrites the query heads
@@ -30,6 +31,14 @@ PositionEncoding: ``rotary_table(device)`` -> (inv_freq float32 [rot/2], rot) fo
                  absolute positions.
 Block:           ``forward(ctx, residual, pending, entry) -> pending``: the arrangement of
                  norms, mixer and feed-forward around the residual stream.
+A norm that follows: in a decode step a norm is a few kilobytes between products that stream
+                 hundreds of megabytes.  A block may therefore hand the part that ends a branch
+                 ``follow=(residual, norm weight, eps)`` (only to a ``forward`` that names the
+                 parameter): the part may then add its output to the residual itself and return the
+                 rows on their way through that norm (``ctx.ops.Prenormed``) instead of its output,
+                 or ignore the hint and return its output as ever.  A part whose ``forward`` may be
+                 given such rows as its input says so with ``takes_prenormed = True``; others get
+                 them materialised.
 Embedding:       ``forward(ctx) -> residual``: the float32 residual stream [T, hidden] of the step's
                  tokens (``ctx.token_ids``), which the blocks then add to in place.
 Head:            ``forward(ctx, h) -> logits``: float32 [rows, vocab] from the final norm's output
@@ -115,6 +124,8 @@ class Part:
 
 
 class Mixer(Part):
+    takes_prenormed = False
+
     def cache_need(self):
         return None
 
@@ -123,6 +134,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_prenormed = False
+
     def forward(self, ctx, h):  # pragma: no cover - interface
         raise NotImplementedError
 
@@ -130,6 +143,10 @@ class FeedForward(Part):
 class Norm(Part):
     def forward(self, ctx, residual, delta, rows=None):  # pragma: no cover - interface
         raise NotImplementedError
+
+    def following(self, ctx, residual):
+        """(residual, weight, eps) when a product may do this norm's work in its epilogue in this step, else None."""
+        return None
 
 
 class Embedding(Part):

@@ -12,8 +12,18 @@ import inspect
 from .base import build_part, register_block
 
 
+def _accepts(function, name: str) -> bool:
+    """Whether ``function`` names the parameter (looked up once per function)."""
+    cache = _accepts.__dict__.setdefault("seen", {})
+    key = (getattr(function, "__func__", function), name)
+    if key not in cache:
+        cache[key] = name in inspect.signature(function).parameters
+    return cache[key]
+
+
 class PreNormBlock:
     part_names = ("input_norm", "mixer", "post_mixer_norm", "feed_forward")
+    takes_prenormed = True          # ``pending`` may be rows on their way through this block's input norm
 
     def __init__(self, layer_spec):
         self.input_norm = build_part("norm", layer_spec.norm)
@@ -24,20 +34,36 @@ class PreNormBlock:
     def parts(self) -> dict:
         return {name: getattr(self, name) for name in self.part_names}
 
-    def forward(self, ctx, residual, pending, entry):
-        # each norm is told which matrix comes next: in a decode step it starts that matrix into L2 meanwhile
-        h = _norm(self.input_norm, ctx, residual, pending, self.mixer.reads_first())
-        mixed = self.mixer.forward(ctx, h, entry)
-        h = _norm(self.post_mixer_norm, ctx, residual, mixed, self.feed_forward.reads_first())
-        return self.feed_forward.forward(ctx, h)
+    def forward(self, ctx, residual, pending, entry, next_norm=None):
+        """``next_norm``: the norm that will read the residual after this block (the next block's input norm), when
+        the model knows it: the feed-forward may then begin it (see ``parts.base``, "a norm that follows")."""
+        h = self._normed(self.input_norm, ctx, residual, pending, self.mixer)
+        mixed = self._branch(self.mixer, (ctx, h, entry), ctx, residual, self.post_mixer_norm)
+        h = self._normed(self.post_mixer_norm, ctx, residual, mixed, self.feed_forward)
+        return self._branch(self.feed_forward, (ctx, h), ctx, residual, next_norm)
+
+    @staticmethod
+    def _normed(norm, ctx, residual, pending, reader):
+        """The input of ``reader``: ``pending`` added to the residual and normalised, or, when the part before has
+        begun this very norm already, the rows it left (materialised for a reader that does not take them)."""
+        if getattr(pending, "weight", None) is not None and hasattr(pending, "materialize"):
+            if pending.weight is not norm.weight:
+                raise RuntimeError("a part began a norm that is not the one that follows it")
+            return pending if getattr(reader, "takes_prenormed", False) else pending.materialize()
+        # the norm is told which matrix comes next: in a decode step it starts that matrix into L2 meanwhile
+        return _norm(norm, ctx, residual, pending, reader.reads_first())
+
+    @staticmethod
+    def _branch(part, args, ctx, residual, norm_after):
+        follow = None
+        if norm_after is not None and _accepts(part.forward, "follow"):
+            follow = norm_after.following(ctx, residual)
+        return part.forward(*args, follow=follow) if follow is not None else part.forward(*args)
 
 
 def _norm(norm, ctx, residual, delta, upcoming):
     """A norm of another kind need not know the hint: it is passed only to a ``forward`` that names it."""
-    takes = getattr(norm, "_takes_upcoming", None)
-    if takes is None:
-        takes = norm._takes_upcoming = "upcoming" in inspect.signature(norm.forward).parameters
-    if takes and upcoming is not None:
+    if upcoming is not None and _accepts(norm.forward, "upcoming"):
         return norm.forward(ctx, residual, delta, upcoming=upcoming)
     return norm.forward(ctx, residual, delta)
 

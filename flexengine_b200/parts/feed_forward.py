@@ -10,6 +10,8 @@ from .base import FeedForward, register_feed_forward
 
 
 class SwiGLU(FeedForward):
+    takes_prenormed = True
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
@@ -23,8 +25,10 @@ class SwiGLU(FeedForward):
     def reads_first(self):
         return self.gate_up_weight
 
-    def forward(self, ctx, h):
+    def forward(self, ctx, h, follow=None):
         act = ctx.ops.linear_swiglu(h, self.gate_up_weight, self.intermediate_size)
+        if follow is not None:
+            return ctx.ops.linear(act, self.down_weight, follow=follow)
         return ctx.ops.linear(act, self.down_weight)
 
 

@@ -67,13 +67,28 @@ class DecoderModel:
                 visit(getattr(part, name.replace(".", "_"), None))
         return total
 
+    @staticmethod
+    def _knows_next_norm(block) -> bool:
+        known = getattr(block, "_knows_next_norm", None)
+        if known is None:
+            import inspect
+            known = block._knows_next_norm = "next_norm" in inspect.signature(block.forward).parameters
+        return known
+
     # --- forward -----------------------------------------------------------------------
     def forward(self, ctx):
         """Run the tokens of ``ctx``; returns float32 logits [len(ctx.logit_rows), V] (or None)."""
         residual = self.embedding.forward(ctx)
         pending = None
-        for entry in self.plan.run:
-            pending = self.blocks[entry.layer].forward(ctx, residual, pending, entry)
+        run = self.plan.run
+        for at, entry in enumerate(run):
+            block = self.blocks[entry.layer]
+            # a block that can make use of it is told which norm reads the residual after it
+            after = self.blocks[run[at + 1].layer] if at + 1 < len(run) else None
+            if after is not None and getattr(after, "takes_prenormed", False) and self._knows_next_norm(block):
+                pending = block.forward(ctx, residual, pending, entry, next_norm=after.input_norm)
+            else:
+                pending = block.forward(ctx, residual, pending, entry)
         if ctx.num_logit_rows == 0:
             # the last branch output only matters to rows whose logits are wanted
             return None

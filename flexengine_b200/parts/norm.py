@@ -7,6 +7,8 @@ float32; the pending branch output is added in the same kernel.
 """
 from __future__ import annotations
 
+import torch
+
 from .base import Norm, register_norm
 
 
@@ -21,6 +23,15 @@ class RMSNorm(Norm):
 
     def forward(self, ctx, residual, delta, rows=None, upcoming=None):
         return ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, ctx.dtype, rows, upcoming=upcoming)
+
+    def following(self, ctx, residual):
+        # a decode step in bfloat16 on kernels that can: the product before this norm adds to the residual and
+        # starts the norm, the product after it finishes it
+        ops = ctx.ops
+        if (getattr(ops, "FUSES_RESIDUAL_NORM", False) and ctx.dtype == torch.bfloat16
+                and ctx.num_tokens <= ops.SKINNY_MAX_ROWS and type(self).forward is RMSNorm.forward):
+            return (residual, self.weight, self.eps)
+        return None
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -107,9 +107,11 @@ def test_temperature_sampling_through_the_engine(model_dirs):
 def test_the_second_tiny_workload_as_it_is_written(model_dirs, dtype):
     """Configuration B with its own workload: four requests with prompts of 1, 40, 77 and 130 tokens, prefill in
     chunks of 24 (the ``adaptive`` policy) mixed with decoding, temperature 0.8, a seed per request, pages of
-    32 tokens (the reference's analogue: tests/integration/test_runtime.py:82-118).  Every request draws the
-    tokens it draws when it runs alone; in float32 each of them lies in the support of the plain implementation's
-    distribution at its place."""
+    32 tokens (the reference's analogue: tests/integration/test_runtime.py:82-118).  In float32 every request draws
+    the tokens it draws when it runs alone (a row's arithmetic does not depend on the batch), and each of them lies
+    in the support of the plain implementation's distribution at its place.  In bfloat16 a step of a few rows and a
+    step of many take different kernels, whose results differ by a rounding: there a draw that falls on the edge
+    between two tokens may go either way, so what is checked is the support."""
     rng = random.Random(12)
     prompts = [helpers.random_prompt(rng, n, 512) for n in (1, 40, 77, 130)]
     kw = dict(scheduler_policy="adaptive", prefill_chunk_size=24, budget=32, max_num_seqs=4, pages=12)
@@ -119,19 +121,20 @@ def test_the_second_tiny_workload_as_it_is_written(model_dirs, dtype):
     calls = []
     step = engine.runner.step
     engine.runner.step = lambda entries, carried=None: (calls.append([len(e.tokens) for e in entries]), step(entries, carried))[1]
-    together = engine.generate(prompts, max_tokens=8, temperature=0.8, seed=300)
-    assert [o.token_ids for o in together] == alone
+    together = [o.token_ids for o in engine.generate(prompts, max_tokens=8, temperature=0.8, seed=300)]
+    if dtype == "float32":
+        assert together == alone
     assert max(n for call in calls for n in call) == 24 and any(1 in call and 24 in call for call in calls), \
         "portions of 24 beside decoded tokens"
     assert all(sum(call) <= 32 for call in calls) and engine.cache.used_pages == 0
     assert len({tuple(t) for t in alone}) == 4
-    if dtype == "float32":
-        config, weights = plain_model.read_model_folder(model_dirs["B"], DEV)
-        for prompt, tokens in zip(prompts, alone):
-            logits = plain_model.forward_logits(config, weights, prompt + tokens[:-1])
-            for i, token in enumerate(tokens):
-                p = plain_model.sampling_distribution(logits[len(prompt) - 1 + i], 0.8, 0)
-                assert float(p[token]) > 1e-5
+    config, weights = plain_model.read_model_folder(model_dirs["B"], DEV)
+    for prompt, tokens in zip(prompts + prompts, alone + together):
+        assert len(tokens) == 8
+        logits = plain_model.forward_logits(config, weights, prompt + tokens[:-1])
+        for i, token in enumerate(tokens):
+            p = plain_model.sampling_distribution(logits[len(prompt) - 1 + i], 0.8, 0)
+            assert float(p[token]) > 1e-5
     from flexengine_b200 import ops
     ops.check_status(DEV)
 

@@ -267,7 +267,7 @@ def test_a_token_gets_the_same_keys_whichever_projection_path_its_step_takes(nq,
 
 
 def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered", boost=None, splits=None,
-                    simt=False, tcgen05=False, ramp=None):
+                    simt=False, tcgen05=False, ramp=None, cluster=False):
     """chunks: [(start, n)] per request.  Fills the cache for positions < start + n."""
     R = len(chunks)
     lens = [s + n for s, n in chunks]
@@ -320,7 +320,10 @@ def _attention_case(dtype, nq, nkv, d, ps, chunks, window, gen, order="scattered
     bt = bt.to(DEV)
     scale = 1.0 / math.sqrt(d)
     want = kernel_refs.paged_attention(qkv, kc, vc, bt, ctx, nq, nkv, d, ps, scale, window)
-    if splits is not None:            # the split-KV decode kernel, asked for by name
+    if splits is not None and cluster:   # the same splits as one thread-block cluster per (request, key/value head)
+        got = ops().paged_decode_cluster(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, R, nq, nkv, d, ps, scale,
+                                         window, splits)
+    elif splits is not None:          # the split-KV decode kernel, asked for by name
         got = ops().paged_decode_mma(qkv, qkv.stride(0), kc, vc, bt, ctx.cu_q, ctx.q_start, R, nq, nkv, d, ps, scale,
                                      window, splits)
     elif tcgen05:                     # the tcgen05 prefill kernel, asked for by name; an integer > 1 splits the keys
@@ -376,6 +379,95 @@ def test_split_kv_decode_kernel(nq, nkv, d, ps, splits, gen):
     chunks = [(p, 1) for p in (0, 1, 15, 16, 31, 32, 33, 63, 64, 100, 255, 256, 700, 1023)]
     got, want, _ = _attention_case(torch.bfloat16, nq, nkv, d, ps, chunks, 0, gen, splits=splits)
     torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 8, 9, 14, 16])
+@pytest.mark.parametrize("nq,nkv,d,ps", [(4, 2, 16, 16), (6, 1, 32, 32), (6, 3, 48, 16), (28, 4, 128, 16), (16, 1, 64, 8),
+                                         (2, 2, 256, 16), (5, 5, 80, 64)])
+def test_cluster_decode_kernel(nq, nkv, d, ps, splits, gen):
+    """The splits of a (request, key/value head) as one thread-block cluster, merged through distributed shared
+    memory: clusters of up to 8 blocks (portable) and up to 16; contexts so short that some splits have no key."""
+    chunks = [(p, 1) for p in (0, 1, 15, 16, 31, 32, 33, 63, 64, 100, 255, 256, 700, 1023)]
+    got, want, _ = _attention_case(torch.bfloat16, nq, nkv, d, ps, chunks, 0, gen, splits=splits, cluster=True)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    ops().check_status(DEV)
+
+
+def test_cluster_decode_kernel_window_far_key_and_limits(gen):
+    chunks = [(p, 1) for p in (0, 5, 40, 64, 300, 999)]
+    for window in (1, 32, 33, 200):
+        got, want, _ = _attention_case(torch.bfloat16, 8, 2, 64, 16, chunks, window, gen, splits=4, cluster=True)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    for far in (0, 17, 333, 798):
+        got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(799, 1), (3, 1)], 0, gen, boost=far, splits=5, cluster=True)
+        torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+        assert float((got[0].float() - 10.0).abs().max()) < 0.5
+    # splits whose sums differ by hundreds of powers of two are weighed against each other
+    got, want, _ = _attention_case(torch.bfloat16, 4, 2, 64, 16, [(900, 1), (37, 1)], 0, gen, splits=7, cluster=True, ramp=0.6)
+    torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
+    with pytest.raises(RuntimeError, match="cluster"):
+        _attention_case(torch.bfloat16, 4, 2, 64, 16, [(300, 1)], 0, gen, splits=17, cluster=True)
+    assert ops().decode_cluster_splits(14, 2048) == 14 and ops().decode_cluster_splits(32, 2048) == 16
+    assert ops().decode_cluster_splits(27, 32768) == 0 and ops().decode_cluster_splits(1, 10) == 0
+    ops().check_status(DEV)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("N,K,N2", [(3584, 3584, 4608), (1536, 8960, 2 * 8960), (192, 384, 256), (80, 128, 64), (3584, 18944, 512)])
+def test_residual_epilogue_begins_the_norm_and_the_next_product_finishes_it(M, N, K, N2, gen):
+    """A product that ends a branch adds to the residual stream in its epilogue and leaves the rows times the next
+    norm's weight with each tile's share of their sums of squares; the product after it scales its accumulators by
+    rsqrt(mean square + eps).  Against: residual += x W^T; h = rmsnorm(residual) * w; h W2^T."""
+    eps = 1e-6
+    x = rand((M, K), torch.bfloat16, gen)
+    w = rand((N, K), torch.bfloat16, gen, 0.02)
+    w2 = rand((N2, N), torch.bfloat16, gen, 0.05)
+    residual = torch.randn(M, N, device=DEV, generator=gen)
+    norm_weight = 1 + 0.1 * torch.randn(N, device=DEV, generator=gen)
+    want_residual = residual + x.float() @ w.float().T
+    want_h = kernel_refs.add_rmsnorm(want_residual.clone(), None, norm_weight, eps, torch.bfloat16)
+    began = ops().linear(x, w, follow=(residual, norm_weight, eps))
+    assert isinstance(began, ops().Prenormed) and began.residual is residual
+    torch.testing.assert_close(residual, want_residual, atol=1e-3, rtol=1e-4)
+    torch.testing.assert_close(began.scaled.float(), (want_residual * norm_weight).to(torch.bfloat16).float(), atol=1e-2, rtol=1e-2)
+    torch.testing.assert_close(began.sumsq.sum(0)[:M], want_residual.pow(2).sum(-1), atol=1e-2, rtol=1e-4)
+    assert float(began.sumsq.sum(0)[M:].abs().max() if M < 8 else 0.0) == 0.0
+    torch.testing.assert_close(began.materialize().float(), want_h.float(), **bar(torch.bfloat16))
+    # the consumers: a plain product (float32 and bfloat16 results), gate/up with the activation, and a second branch end
+    want = want_h.float() @ w2.float().T
+    scale = float(want.abs().max())
+    torch.testing.assert_close(ops().linear(began, w2, out_float32=True), want, atol=1e-2 * scale, rtol=2e-2)
+    torch.testing.assert_close(ops().linear(began, w2).float(), want, atol=1e-2 * scale, rtol=2e-2)
+    got = ops().linear_swiglu(began, w2, N2 // 2)
+    torch.testing.assert_close(got.float(), kernel_refs.linear_swiglu(want_h, w2, N2 // 2).float(), atol=1e-2 * scale * scale, rtol=3e-2)
+    if N % 64 == 0:
+        second = torch.randn(M, N2, device=DEV, generator=gen)
+        expect = second + want
+        again = ops().linear(began, w2, follow=(second, torch.ones(N2, device=DEV), eps))
+        assert isinstance(again, ops().Prenormed)
+        torch.testing.assert_close(second, expect, atol=1e-2 * scale, rtol=2e-2)
+    ops().check_status(DEV)
+
+
+def test_fused_qkv_projection_takes_rows_on_their_way_through_a_norm(gen):
+    nq, nkv, d, ps, K, M, pages = 28, 4, 128, 16, 3584, 6, 12
+    eps = 1e-6
+    residual = torch.randn(M, K, device=DEV, generator=gen)
+    norm_weight = 1 + 0.1 * torch.randn(K, device=DEV, generator=gen)
+    x = rand((M, 256), torch.bfloat16, gen)
+    began = ops().linear(x, rand((K, 256), torch.bfloat16, gen, 0.05), follow=(residual, norm_weight, eps))
+    h = kernel_refs.add_rmsnorm(residual.clone(), None, norm_weight, eps, torch.bfloat16)
+    w = rand(((nq + 2 * nkv) * d, K), torch.bfloat16, gen, 0.05)
+    bias = torch.randn((nq + 2 * nkv) * d, device=DEV, generator=gen) * 0.1
+    positions = torch.tensor([0, 1, 17, 255, 4095, 32767], device=DEV, dtype=torch.int32)
+    inv_freq = (1.0 / 1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d)).to(DEV)
+    slots = torch.randperm(pages * ps, device=DEV, generator=gen)[:M].to(torch.int32)
+    caches = [torch.zeros(2, pages, nkv, ps, d, device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    got = ops().qkv_projection(began, w, bias, positions, inv_freq, d, slots, caches[0][0], caches[0][1], nq, nkv, d, ps)
+    want = kernel_refs.qkv_projection(h, w, bias, positions, inv_freq, d, slots, caches[1][0], caches[1][1], nq, nkv, d, ps)
+    torch.testing.assert_close(got.float(), want.float(), atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(caches[0].float(), caches[1].float(), atol=3e-2, rtol=3e-2)
     ops().check_status(DEV)
 
 
