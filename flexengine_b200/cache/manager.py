@@ -18,6 +18,7 @@ import math
 from collections import Counter
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from .page_pool import CacheExhausted, PagePool
@@ -31,15 +32,31 @@ class RequestCache:
     tokens: int = 0                                   # tokens whose keys/values are in the cache
     tables: list = field(default_factory=list)        # per group: list of page ids (RELEASED where given back)
     state_slot: int = -1
+    room: int = 0                                     # tokens the tables have room for (the least over the paged groups)
 
 
 class PagedGroup:
-    def __init__(self, spec, num_pages: int, page_size: int, dtype, device):
+    def __init__(self, spec, num_pages: int, page_size: int, dtype, device, max_requests: int = 1):
         self.spec = spec
         self.page_size = int(page_size)
         self.pool = PagePool(num_pages)
         self.storage = torch.zeros((spec.slots, 2, num_pages, spec.kv_heads, self.page_size, spec.head_dim),
                                    dtype=dtype, device=device)
+        # the block tables once more, as one matrix with a row per seat (a request's state slot): what a step's
+        # metadata is gathered from with a few array operations instead of a loop over requests and pages
+        self.table_rows = np.full((max_requests, 64), RELEASED, dtype=np.int32)
+
+    def mirror(self, seat: int, first: int, pages) -> None:
+        """Entries ``first ..`` of seat ``seat``'s table are now ``pages``."""
+        need = first + len(pages)
+        if need > self.table_rows.shape[1]:
+            wider = np.full((self.table_rows.shape[0], max(need, 2 * self.table_rows.shape[1])), RELEASED, dtype=np.int32)
+            wider[:, :self.table_rows.shape[1]] = self.table_rows
+            self.table_rows = wider
+        self.table_rows[seat, first:need] = pages
+
+    def clear_row(self, seat: int, first: int = 0) -> None:
+        self.table_rows[seat, first:] = RELEASED
 
     def kv_slot(self, slot: int):
         return self.storage[slot, 0], self.storage[slot, 1]
@@ -76,7 +93,7 @@ class CacheManager:
                     n = num_pages[gi]
                 else:
                     n = -(-num_pages * self.page_size // own)
-                self.groups.append(PagedGroup(spec, n, own, dtype, self.device))
+                self.groups.append(PagedGroup(spec, n, own, dtype, self.device, self.max_requests))
         self.requests: dict[str, RequestCache] = {}
         self.free_state_slots = list(range(self.max_requests - 1, -1, -1))
         self._paged = [(gi, g) for gi, g in enumerate(self.groups) if isinstance(g, PagedGroup)]
@@ -125,7 +142,7 @@ class CacheManager:
         for g in self.groups:
             if isinstance(g, StateGroup) and g.storage.numel():
                 g.storage[:, slot].zero_()
-        rc = RequestCache(request_id, 0, [[] for _ in self.groups], slot)
+        rc = RequestCache(request_id, 0, [[] for _ in self.groups], slot, 0 if self._paged else 1 << 62)
         self.requests[request_id] = rc
         return rc
 
@@ -142,7 +159,7 @@ class CacheManager:
         fresh = rc is None
         if fresh:
             rc = self.admit(request_id)
-        elif all(len(rc.tables[gi]) * g.page_size >= target_tokens for gi, g in self._paged):
+        elif rc.room >= target_tokens:
             return                      # already reserved (the usual case in decode)
         needs = [(gi, g, self._pages_needed(rc, gi, target_tokens)) for gi, g in self.paged]
         short = [(g.spec.name, n, g.pool.free_pages) for _, g, n in needs if n > g.pool.free_pages]
@@ -152,7 +169,14 @@ class CacheManager:
             name, n, have = short[0]
             raise CacheExhausted(f"Need {n} pages in group {name!r}; only {have} free")
         for gi, g, n in needs:
-            rc.tables[gi].extend(g.pool.allocate(n))
+            if n:
+                pages = g.pool.allocate(n)
+                g.mirror(rc.state_slot, len(rc.tables[gi]), pages)
+                rc.tables[gi].extend(pages)
+        rc.room = self._room(rc)
+
+    def _room(self, rc: RequestCache) -> int:
+        return min((len(rc.tables[gi]) * g.page_size for gi, g in self._paged), default=1 << 62)
 
     def reserved_tokens(self, request_id: str) -> int:
         rc = self.requests.get(request_id)
@@ -178,6 +202,7 @@ class CacheManager:
                 if table[j] != RELEASED:
                     g.pool.release(table[j])
                     table[j] = RELEASED
+                    g.table_rows[rc.state_slot, j] = RELEASED
 
     def free(self, request_id: str) -> None:
         rc = self.requests.pop(request_id, None)
@@ -187,7 +212,19 @@ class CacheManager:
             for page in rc.tables[gi]:
                 if page != RELEASED:
                     g.pool.release(page)
+            g.clear_row(rc.state_slot)
         self.free_state_slots.append(rc.state_slot)
+
+    def truncate(self, request_id: str, gi: int, keep: int) -> None:
+        """Give back the pages of group ``gi`` beyond the first ``keep`` (a reservation that is undone)."""
+        rc = self.requests[request_id]
+        g = self.groups[gi]
+        for page in rc.tables[gi][keep:]:
+            if page != RELEASED:
+                g.pool.release(page)
+        del rc.tables[gi][keep:]
+        g.clear_row(rc.state_slot, keep)
+        rc.room = self._room(rc)
 
     def share_prefix(self, donor_id: str, request_id: str, tokens: int) -> None:
         """Let a new request hold the donor's first complete pages too (reference counts,
@@ -207,7 +244,9 @@ class CacheManager:
             for page in pages:
                 g.pool.retain(page)
             rc.tables[gi] = list(pages)
+            g.mirror(rc.state_slot, 0, rc.tables[gi])
         rc.tokens = shared
+        rc.room = self._room(rc)
 
     # --- per-step views ------------------------------------------------------------------------
     def slot_mapping(self, request_id: str, gi: int, start: int, count: int) -> list[int]:
@@ -235,6 +274,15 @@ class CacheManager:
         for gi, g in self.paged:
             owners = Counter(p for rc in self.requests.values() for p in rc.tables[gi] if p != RELEASED)
             g.pool.assert_invariants(dict(owners))
+            for rc in self.requests.values():          # the matrix of table rows says what the lists say
+                row = g.table_rows[rc.state_slot]
+                n = len(rc.tables[gi])
+                if row[:n].tolist() != rc.tables[gi] or (row[n:] != RELEASED).any():
+                    raise AssertionError(f"the table row of {rc.request_id!r} in group {g.spec.name!r} differs from its table")
+            held = {rc.state_slot for rc in self.requests.values()}
+            for seat in range(self.max_requests):
+                if seat not in held and (g.table_rows[seat] != RELEASED).any():
+                    raise AssertionError(f"seat {seat} is free but its table row is not empty")
         slots = [rc.state_slot for rc in self.requests.values()]
         if len(slots) != len(set(slots)) or set(slots) & set(self.free_state_slots):
             raise AssertionError("a state slot is held twice")

@@ -20,6 +20,7 @@ class PagePool:
         self.num_pages = int(num_pages)
         self.free: deque[int] = deque(range(self.num_pages))
         self.refs = [0] * self.num_pages
+        self.shared = 0          # pages with more than one owner (none in the usual case: a fast path asks)
 
     @property
     def free_pages(self) -> int:
@@ -47,6 +48,8 @@ class PagePool:
         if not (0 <= page < self.num_pages) or self.refs[page] <= 0:
             raise ValueError("cannot retain a page that is not allocated")
         self.refs[page] += 1
+        if self.refs[page] == 2:
+            self.shared += 1
 
     def release(self, page: int) -> None:
         """Drop one owner; the page becomes free when none is left."""
@@ -55,6 +58,8 @@ class PagePool:
         if self.refs[page] <= 0:
             raise RuntimeError(f"page {page} released more often than it was held")
         self.refs[page] -= 1
+        if self.refs[page] == 1:
+            self.shared -= 1
         if self.refs[page] == 0:
             self.free.append(page)
 

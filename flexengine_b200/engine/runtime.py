@@ -266,11 +266,17 @@ class Engine:
         """The chunks of ``proposed`` that have their pages, in order.  Up to three tries per chunk: as things are;
         after the tokens on their way were read (requests that just ended gave pages back); after one preemption."""
         granted, taken = [], set()
+        held = self.cache.requests
         for chunk in proposed:
             request = self.running.get(chunk.request_id)
             if request is None:
                 continue
             upto = chunk.start + len(chunk.input_ids)
+            record = held.get(chunk.request_id)
+            if record is not None and record.room >= upto:      # the usual case in decode: nothing to reserve
+                granted.append(chunk)
+                taken.add(chunk.request_id)
+                continue
             for attempt in ("as is", "after landing", "after preempting"):
                 if attempt == "after landing":
                     if self._in_flight is None:
@@ -309,8 +315,9 @@ class Engine:
                 self._land()                           # nothing to launch: the tokens on their way are the progress
                 return not self.fault
             planned_at = time.perf_counter()
+            tracing = self.config.trace_steps and self.trace.enabled
             tokens = sum(len(c.input_ids) for c in chunks)
-            prompt_tokens = sum(len(c.input_ids) for c in chunks if self.running[c.request_id].in_prefill)
+            prompt_tokens = sum(len(c.input_ids) for c in chunks if self.running[c.request_id].in_prefill) if tracing else 0
             try:
                 with marked(f"executor/step batch={len(chunks)} tokens={tokens}"):
                     launched = self._launch(chunks)
@@ -325,7 +332,7 @@ class Engine:
                 return False
             done_at = time.perf_counter()
             self.counters.steps += 1
-            if self.config.trace_steps and self.trace.enabled:
+            if tracing:
                 # keys: the reference's step records (runtime.py:358-383), which its analysis reads
                 self.trace.record("steps", {
                     "step": self.counters.steps, "policy": self.config.scheduler_policy, "batch_size": len(chunks),
@@ -358,7 +365,7 @@ class Engine:
             entries.append(StepEntry(chunk.request_id, ids, [len(ids) - 1] if chunk.wants_logits else [], carry))
             if chunk.wants_logits:
                 sampled.append(request)
-        logits = self.runner.step(entries, earlier.tokens if earlier is not None else None)
+        logits = self._run_step(entries, earlier.tokens if earlier is not None else None)
         tokens = None
         if sampled:
             tokens = self.sampler.sample_on_device(logits, [r.temperature for r in sampled], [r.top_k for r in sampled],
@@ -384,6 +391,15 @@ class Engine:
         if tokens is not None and tokens.device.type == "cuda":
             self._copy_out(record)
         return record
+
+    def _run_step(self, entries, carried):
+        """The runner's step; one that says it can is told that tokens were checked at submit and pages reserved
+        chunk by chunk already."""
+        trusts = getattr(self, "_runner_trusts", None)
+        if trusts is None:
+            import inspect
+            trusts = self._runner_trusts = "trusted" in inspect.signature(self.runner.step).parameters
+        return self.runner.step(entries, carried, trusted=True) if trusts else self.runner.step(entries, carried)
 
     def _copy_out(self, record: _InFlight) -> None:
         """Start the copy of the sampled tokens and of the kernels' status word into pinned memory."""

@@ -135,11 +135,8 @@ class ModelRunner:
                 if before is None:
                     cache.free(rid)
                     continue
-                rc = cache.requests[rid]
-                for (gi, g), keep in zip(paged, before):
-                    for page in rc.tables[gi][keep:]:
-                        g.pool.release(page)
-                    del rc.tables[gi][keep:]
+                for (gi, _g), keep in zip(paged, before):
+                    cache.truncate(rid, gi, keep)
             raise
 
     def _staging(self, count: int) -> torch.Tensor:
@@ -200,72 +197,86 @@ class ModelRunner:
         from (one pair per request with a fixed shape, row -1 where nothing is carried).
 
         A padding request must leave no trace: kernels skip cache slot -1, and a part that keeps
-        per-request state skips state slot -1 (``parts.base``)."""
+        per-request state skips state slot -1 (``parts.base``).
+
+        Everything is array arithmetic over the requests' seats (their state slots): block tables and slot
+        mappings are gathered from the cache manager's matrix of table rows, not looped over in Python."""
         cache = self.cache
         held = cache.requests
-        caches = [held.get(e.request_id) for e in entries]
-        starts = [rc.tokens if rc else 0 for rc in caches]
-        lengths = [len(e.tokens) for e in entries]
-        pad = max(0, pad_to - len(entries))
-        all_lengths = lengths + [1] * pad
-        all_starts = starts + [0] * pad
-        R = len(all_lengths)
-        single = max(all_lengths) == 1              # a decode step: one token a request
-        if single:
-            token_ids = [e.tokens[0] for e in entries] + [0] * pad
-            positions = all_starts
-            token_request = list(range(R))
-            cu_q = list(range(R + 1))
-            ctx_len = [s + 1 for s in all_starts]
+        real = len(entries)
+        caches = [held[e.request_id] for e in entries]
+        pad = max(0, pad_to - real)
+        R = real + pad
+        starts = np.zeros(R, dtype=np.int32)
+        lengths = np.ones(R, dtype=np.int32)
+        seats = np.full(R, -1, dtype=np.int32)
+        if real:
+            starts[:real] = [rc.tokens for rc in caches]
+            lengths[:real] = [len(e.tokens) for e in entries]
+            seats[:real] = [rc.state_slot for rc in caches]
+        cu_q = np.zeros(R + 1, dtype=np.int32)
+        np.cumsum(lengths, out=cu_q[1:])
+        T = int(cu_q[-1])
+        ctx_len = starts + lengths
+        longest = int(ctx_len.max())
+        if int(lengths.max()) == 1:                  # a decode step: one token a request
+            token_ids = np.zeros(R, dtype=np.int32)
+            if real:
+                token_ids[:real] = [e.tokens[0] for e in entries]
+            positions = starts
+            token_request = np.arange(R, dtype=np.int32)
         else:
-            token_ids = [t for e in entries for t in e.tokens] + [0] * pad
-            positions = [p for s, n in zip(starts, lengths) for p in range(s, s + n)] + [0] * pad
-            token_request = [r for r, n in enumerate(all_lengths) for _ in range(n)]
-            cu_q = [0]
-            for n in all_lengths:
-                cu_q.append(cu_q[-1] + n)
-            ctx_len = [s + n for s, n in zip(all_starts, all_lengths)]
-        state_slots = [rc.state_slot for rc in caches] + [-1] * pad
-        logit_rows = [cu_q[r] + w for r, e in enumerate(entries) for w in e.want]
+            token_ids = np.zeros(T, dtype=np.int32)
+            token_ids[:T - pad] = [t for e in entries for t in e.tokens]
+            token_request = np.repeat(np.arange(R, dtype=np.int32), lengths)
+            positions = np.arange(T, dtype=np.int32) - np.repeat(cu_q[:-1] - starts, lengths)
         if pad_to:
-            logit_rows = list(range(R))          # a fixed shape: every request's one row, padding too
-        arrays = [np.asarray(token_ids, dtype=np.int32), np.asarray(positions, dtype=np.int32),
-                  np.asarray(token_request, dtype=np.int32), np.asarray(cu_q, dtype=np.int32),
-                  np.asarray(all_starts, dtype=np.int32), np.asarray(ctx_len, dtype=np.int32),
-                  np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32)]
+            logit_rows = np.arange(R, dtype=np.int32)          # a fixed shape: every request's one row, padding too
+        else:
+            logit_rows = np.asarray([cu_q[r] + w for r, e in enumerate(entries) for w in e.want], dtype=np.int32)
+        arrays = [token_ids, positions, token_request, cu_q, starts, ctx_len, seats, logit_rows]
         widths = []
-        longest = max(ctx_len)
+        real_tokens = T - pad
+        token_seat = seats[token_request[:real_tokens]] if real else None
         for gi, g in enumerate(cache.groups):
             if not isinstance(g, PagedGroup):
                 widths.append(0)
                 continue
-            ps, refs = g.page_size, g.pool.refs
-            slots = []
-            for e, rc, s, n in zip(entries, caches, starts, lengths):
-                table = rc.tables[gi]
-                page = table[s // ps] if n == 1 and s < len(table) * ps else -1
-                if page >= 0 and refs[page] == 1:
-                    slots.append(page * ps + s % ps)       # the usual case, without a call
+            ps, rows = g.page_size, g.table_rows
+            slots = np.full(T, -1, dtype=np.int32)
+            if real:
+                where = positions[:real_tokens] // ps
+                pages = rows[token_seat, where] if int(where.max()) < rows.shape[1] else None
+                if pages is None or int(pages.min()) < 0 or g.pool.shared:
+                    # something is not as usual (a page not reserved or given back, shared pages in the pool): the
+                    # checks and their messages live in the cache manager
+                    at = 0
+                    for e, n in zip(entries, lengths[:real].tolist()):
+                        slots[at:at + n] = cache.slot_mapping(e.request_id, gi, held[e.request_id].tokens, n)
+                        at += n
                 else:
-                    slots.extend(cache.slot_mapping(e.request_id, gi, s, n))      # checks and messages live there
-            slots += [-1] * pad
+                    slots[:real_tokens] = pages * ps + positions[:real_tokens] % ps
             width = max_pages[gi] if max_pages else max(1, -(-longest // ps))
             bt = np.full((R, width), -1, dtype=np.int32)
-            for r, rc in enumerate(caches):
-                t = rc.tables[gi]
-                k = min(len(t), width)
-                bt[r, :k] = t[:k]
-            bt[len(entries):, :] = 0
-            arrays += [np.asarray(slots, dtype=np.int32), bt.reshape(-1)]
+            if real:
+                have = min(width, rows.shape[1])
+                bt[:real, :have] = rows[seats[:real], :have]
+            bt[real:, :] = 0
+            arrays += [slots, bt.reshape(-1)]
             widths.append(width)
         if carrying:
-            carried = [(cu_q[r], e.carry) for r, e in enumerate(entries) if e.carry is not None]
+            rows_to_fill = np.full(R if pad_to else 0, -1, dtype=np.int32)
+            sources = np.zeros(R if pad_to else 0, dtype=np.int32)
+            picked = [(r, e.carry) for r, e in enumerate(entries) if e.carry is not None]
             if pad_to:
-                carried = [(cu_q[r], e.carry) if e.carry is not None else (-1, 0) for r, e in enumerate(entries)]
-                carried += [(-1, 0)] * pad
-            arrays += [np.asarray([c[0] for c in carried], dtype=np.int32), np.asarray([c[1] for c in carried], dtype=np.int32)]
-        info = dict(T=len(token_ids), R=R, rows=len(logit_rows), starts=all_starts, lengths=all_lengths,
-                    state_slots=state_slots, widths=widths, max_q_len=max(all_lengths), max_ctx_len=longest,
+                for r, c in picked:
+                    rows_to_fill[r], sources[r] = cu_q[r], c
+            else:
+                rows_to_fill = np.asarray([cu_q[r] for r, _ in picked], dtype=np.int32)
+                sources = np.asarray([c for _, c in picked], dtype=np.int32)
+            arrays += [rows_to_fill, sources]
+        info = dict(T=T, R=R, rows=len(logit_rows), starts=starts.tolist(), lengths=lengths.tolist(),
+                    state_slots=seats.tolist(), widths=widths, max_q_len=int(lengths.max()), max_ctx_len=longest,
                     request_ids=[e.request_id for e in entries])
         return arrays, info
 
@@ -392,14 +403,16 @@ class ModelRunner:
         return record["logits"][:len(entries)]
 
     @torch.inference_mode()
-    def step(self, entries, carried=None):
+    def step(self, entries, carried=None, trusted: bool = False):
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] in the order
         of the entries and of their ``want`` (None when nothing is wanted).  With decode graphs
         on, the returned tensor of a decode step is overwritten by the next such step.
         ``carried``: an int32 tensor on the device from which entries with ``carry`` take their token
-        (what the step before sampled, not yet read by the host)."""
+        (what the step before sampled, not yet read by the host).  ``trusted``: the caller has checked the
+        entries and reserved their pages itself (the engine has: it does not pay for both twice)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        self._check(entries)
+        if not trusted:
+            self._check(entries)
         if any(e.carry is not None for e in entries):
             if carried is None:
                 raise ValueError("an entry carries its token but no tensor of carried tokens was given")
@@ -408,7 +421,8 @@ class ModelRunner:
                     raise ValueError(f"request {e.request_id!r}: a carried token is one token, inside the tensor given")
         else:
             carried = None
-        self._reserve(entries)
+        if not trusted:
+            self._reserve(entries)
         logits = None
         decode = self._graph_buckets and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         if decode:

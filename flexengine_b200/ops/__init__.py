@@ -170,10 +170,15 @@ class Prenormed:
 
 
 def _rows_and_scale(x):
-    """(tensor, sumsq pointer, tiles, eps) of an input that may be a Prenormed."""
+    """(tensor, sumsq pointer, tiles, eps) of an input of the weight-streaming kernel for up to 8 rows."""
     if isinstance(x, Prenormed):
         return x.scaled, _ptr(x.sumsq), _c_int(x.sumsq.shape[0]), _c_float(x.eps)
     return x, None, _c_int(0), _c_float(0.0)
+
+
+def _fits(x, w) -> str:
+    """Which weight-streaming kernel takes this product, if any: "skinny" (up to 8 rows) or ""."""
+    return "skinny" if skinny_ok(x.scaled if isinstance(x, Prenormed) else x, w) else ""
 
 
 def gemm_fp32(x, w, bias=None):
@@ -193,25 +198,29 @@ def linear(x, w, bias=None, out_float32=False, follow=None):
     the float32 residual stream [M, N] and an RMSNorm reads the sum next.  Where the weight-streaming kernel runs (a
     decode step), it does both in its epilogue and a ``Prenormed`` comes back; otherwise the plain product does,
     and the caller adds and normalises as usual."""
-    if isinstance(x, Prenormed) and not (skinny_ok(x.scaled, w) and x.scaled.shape[0] <= SKINNY_MAX_ROWS):
+    kernel = _fits(x, w)
+    if isinstance(x, Prenormed) and not kernel:
         x = x.materialize()
-    rows, sumsq, tiles, eps = _rows_and_scale(x)
+        kernel = _fits(x, w)
+    rows = x.scaled if isinstance(x, Prenormed) else x
     _need_cuda(rows, w, bias)
-    if follow is not None and bias is None and not out_float32 and skinny_ok(rows, w):
+    if follow is not None and bias is None and not out_float32 and kernel:
         residual, norm_weight, norm_eps = follow
         M, N = rows.shape[0], w.shape[0]
         if (residual.dtype == torch.float32 and tuple(residual.shape) == (M, N) and residual.is_contiguous()
                 and norm_weight.dtype == torch.float32 and norm_weight.numel() == N):
             scaled = torch.empty((M, N), dtype=torch.bfloat16, device=rows.device)
+            _rows, sumsq, tiles, eps = _rows_and_scale(x)
             table = torch.empty((-(-N // 16), 8), dtype=torch.float32, device=rows.device)
             _run(_bf16(), "fe_skinny_gemm_residual", _ptr(rows), _ptr(w), _ptr(residual), _ptr(norm_weight), _ptr(scaled),
                  _ptr(table), _c_int(M), _c_int(N), _c_int(rows.shape[1]), sumsq, tiles, eps, _stream())
             return Prenormed(scaled, table, norm_eps, residual, norm_weight)
-    if isinstance(x, Prenormed):
-        y = skinny_gemm(x, w, EPI_F32 if (out_float32 or bias is not None) else EPI_BF16)
+    if kernel and w.dtype == torch.bfloat16:
+        wide = out_float32 or bias is not None           # a bias is added in float32, before the one rounding
+        y = skinny_gemm(x, w, EPI_F32 if wide else EPI_BF16)
         if bias is not None:
             y += bias
-        return y if out_float32 or bias is None else y.to(torch.bfloat16)
+        return y if out_float32 or not wide else y.to(torch.bfloat16)
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise ValueError(f"linear: shapes {tuple(x.shape)} x {tuple(w.shape)}")
     if not x.is_contiguous():
@@ -222,10 +231,7 @@ def linear(x, w, bias=None, out_float32=False, follow=None):
     if w.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
         raise TypeError(f"linear: weight {w.dtype} with activations {x.dtype}")
     wide = out_float32 or bias is not None           # a bias is added in float32, before the one rounding
-    if skinny_ok(x, w):
-        y = skinny_gemm(x, w, EPI_F32 if wide else EPI_BF16)
-    else:
-        y = torch.mm(x, w.t(), out_dtype=torch.float32) if wide else torch.mm(x, w.t())
+    y = torch.mm(x, w.t(), out_dtype=torch.float32) if wide else torch.mm(x, w.t())
     if bias is not None:
         y += bias
     return y if out_float32 or not wide else y.to(torch.bfloat16)
@@ -258,36 +264,7 @@ def skinny_gemm(x, w, epilogue: int = EPI_BF16):
     return out
 
 
-STREAM_MAX_ROWS = 128
-
-
-def stream_ok(x, w) -> bool:
-    """Whether the swap-AB tcgen05 streaming kernel is used: bfloat16, 9 to 128 rows, K a multiple of 8."""
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and SKINNY_MAX_ROWS < x.shape[0] <= STREAM_MAX_ROWS
-            and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def stream_gemm(x, w, epilogue: int = EPI_BF16):
-    """x [M <= 128, K] times w [N, K]^T as a stream of w through tcgen05 (operands swapped);
-    see csrc/gemm_stream_tcgen05.cu."""
-    _need_cuda(x, w)
-    M, K = x.shape
-    N = w.shape[0]
-    lib = _bf16()
-    work = None
-    if epilogue == EPI_SWIGLU:
-        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
-    elif epilogue == EPI_F32:
-        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-    else:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
-        splits = lib.fe_stream_gemm_splits(_c_int(N), _c_int(K))
-        if splits > 1:
-            work = scratch(x.device, splits * M * N * 4)
-    _run(lib, "fe_stream_gemm_tcgen05", _ptr(x), _ptr(w), _ptr(out), _ptr(work), _c_int(M), _c_int(N), _c_int(K),
-         _c_int(epilogue), _ptr(status_word(x.device)), _stream())
-    return out
+FUSED_NORM_MAX_ROWS = SKINNY_MAX_ROWS     # steps of up to this many tokens do their norms in the products' epilogues
 
 
 TCGEN05_MIN_K = 1024
@@ -330,11 +307,11 @@ def swiglu(gate_up, intermediate):
 
 def linear_swiglu(x, w, intermediate):
     """silu(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]); one kernel for a handful of rows."""
-    if isinstance(x, Prenormed):
-        if skinny_ok(x.scaled, w) and w.shape[0] == 2 * intermediate:
-            return skinny_gemm(x, w, EPI_SWIGLU)
+    kernel = _fits(x, w) if w.shape[0] == 2 * intermediate else ""
+    if isinstance(x, Prenormed) and not kernel:
         x = x.materialize()
-    if skinny_ok(x, w) and w.shape[0] == 2 * intermediate:
+        kernel = _fits(x, w) if w.shape[0] == 2 * intermediate else ""
+    if kernel == "skinny":
         return skinny_gemm(x, w, EPI_SWIGLU)
     if tcgen05_ok(x, w) and w.shape[0] == 2 * intermediate:
         return gemm_tcgen05(x, w, EPI_SWIGLU)
@@ -374,12 +351,17 @@ def qkv_projection(h, w, bias, positions, inv_freq, rot, slot_mapping, k_cache, 
     write).  Returns qkv [T, (nq + 2 nkv) d].  For a handful of rows (decode) with the whole head
     rotated this is ONE kernel (csrc/gemm_skinny.cu); otherwise the product and the fused
     bias/rotation/cache-write kernel."""
-    rows, sumsq, tiles, eps = _rows_and_scale(h)
+    kernel = _fits(h, w)
+    if isinstance(h, Prenormed) and not kernel:
+        h = h.materialize()
+        kernel = _fits(h, w)
+    rows = h.scaled if isinstance(h, Prenormed) else h
     _need_cuda(rows, w, bias, positions, inv_freq, slot_mapping, k_cache, v_cache)
-    if (skinny_ok(rows, w) and rows.shape[0] <= SKINNY_QKV_MAX_ROWS and inv_freq is not None and rot == d and d % 16 == 0
-            and k_cache.dtype == torch.bfloat16
-            and w.shape[0] == (nq + 2 * nkv) * d and (bias is None or bias.dtype == torch.float32)):
+    whole_head = (inv_freq is not None and rot == d and k_cache.dtype == torch.bfloat16 and w.shape[0] == (nq + 2 * nkv) * d
+                  and (bias is None or bias.dtype == torch.float32))
+    if kernel == "skinny" and whole_head and d % 16 == 0 and rows.shape[0] <= SKINNY_QKV_MAX_ROWS:
         T = rows.shape[0]
+        _rows, sumsq, tiles, eps = _rows_and_scale(h)
         out = torch.empty((T, w.shape[0]), dtype=torch.bfloat16, device=rows.device)
         _run(_bf16(), "fe_skinny_qkv", _ptr(rows), _ptr(w), _ptr(out), _ptr(bias), _ptr(positions), _ptr(inv_freq),
              _ptr(slot_mapping), _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(rows.shape[1]), _c_int(nq), _c_int(nkv),

@@ -30,7 +30,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 # compiles only that
 GROUPS = {
     "core": ["errors.cu", "elementwise.cu", "attention_simt.cu", "gemm_fp32.cu", "sampling.cu"],
-    "bf16": ["errors.cu", "attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "gemm_stream_tcgen05.cu"],
+    "bf16": ["errors.cu", "attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny.cu", "gemm_tcgen05.cu"],
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -29,7 +29,7 @@ class RMSNorm(Norm):
         # starts the norm, the product after it finishes it
         ops = ctx.ops
         if (getattr(ops, "FUSES_RESIDUAL_NORM", False) and ctx.dtype == torch.bfloat16
-                and ctx.num_tokens <= ops.SKINNY_MAX_ROWS and type(self).forward is RMSNorm.forward):
+                and ctx.num_tokens <= ops.FUSED_NORM_MAX_ROWS and type(self).forward is RMSNorm.forward):
             return (residual, self.weight, self.eps)
         return None
 
