@@ -226,7 +226,6 @@ __device__ __forceinline__ void load_q(unsigned (*qfrag)[4], const bf16* src0, c
 // gets through, and shared memory bounds how many blocks fit an SM: so the two warps of a block
 // share every stage they load, each takes 16 of its 32 keys with running statistics of its own,
 // and the two results are merged once at the end.
-constexpr int DECODE_STAGES = 2;
 constexpr int DECODE_WARPS = 2;
 constexpr int DECODE_KEYS = TK / DECODE_WARPS;   // keys of a stage per warp
 
@@ -248,7 +247,10 @@ __device__ __forceinline__ float ld_cluster(const float* own, unsigned rank) {
 }
 constexpr int CLUSTER_MAX_SPLITS = 16;
 
-template <int DMAX, bool UPPER, bool CLUSTER = false>
+// STAGES: the ring of 32-key stages; STAGES - 1 tiles are on their way while one is multiplied.  A block that walks
+// only a few tiles (short contexts split many ways) spends its life waiting for memory: a deeper ring asks for its
+// tiles earlier.
+template <int DMAX, bool UPPER, bool CLUSTER = false, int STAGES = 2>
 __global__ void __launch_bounds__(DECODE_WARPS * 32)
 paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                     float* __restrict__ part_o, float* __restrict__ part_lse, const bf16* __restrict__ kc,
@@ -259,6 +261,7 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ long long offs[TK];
+    __shared__ long long first_offs[STAGES - 1][TK];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     constexpr int TILE = TK * pitch<DMAX>();         // elements per K (or V) stage
     constexpr int THREADS = DECODE_WARPS * 32;
@@ -275,13 +278,22 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
 
     KvSource src{kc, vc, block_table + (size_t)b * bt_stride, nkv, kvh, d, ps, (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1,
                  num_pages};
-    // thread r < 32 looks up key r of a tile; then the block copies the 32 rows
-    if (n_tiles > 0) {
-        if (threadIdx.x < TK) offs[threadIdx.x] = row_offset(src, t_begin * TK + threadIdx.x, lo, pos, status);
-        __syncthreads();
-        copy_rows<DMAX, THREADS, TK>(smem, smem + TILE, src, offs);
+    // thread r < 32 looks up key r of a tile; then the block copies the 32 rows.  The first STAGES - 1 tiles are asked
+    // for at once; every step of the loop then asks for one more.  A group of copies is committed at every turn, empty
+    // or not, so that "all but the youngest STAGES - 2 groups have landed" always means "tile ``it`` has landed".
+    constexpr int AHEAD = STAGES - 1;
+    static_assert(AHEAD * TK <= DECODE_WARPS * 32, "one thread per key of the tiles asked for at the start");
+    // all the first tiles' keys are looked up at once (one trip to the block table, not one per tile)
+    if (threadIdx.x < AHEAD * TK) {
+        const int a = threadIdx.x / TK, k = threadIdx.x - a * TK;
+        first_offs[a][k] = a < n_tiles ? row_offset(src, (t_begin + a) * TK + k, lo, pos, status) : -1;
     }
-    cp_async_commit();
+    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+        if (a < n_tiles) copy_rows<DMAX, THREADS, TK>(smem + a * 2 * TILE, smem + a * 2 * TILE + TILE, src, first_offs[a]);
+        cp_async_commit();
+    }
 
     unsigned qfrag[DMAX / 16][4];
     const bf16* qrow = q + (size_t)tok * q_stride + (size_t)kvh * G * d;
@@ -293,19 +305,20 @@ paged_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __rest
     float m[2] = {-CUDART_INF_F, -CUDART_INF_F}, l[2] = {0.f, 0.f};
 
     for (int it = 0; it < n_tiles; ++it) {
-        // the other stage is free (both warps finished tile it - 1): start tile it + 1 into it
+        // the stage of tile it - 1 is free (both warps finished it): tile it + AHEAD goes there
         long long next = -1;
-        if (it + 1 < n_tiles && threadIdx.x < TK) next = row_offset(src, (t_begin + it + 1) * TK + threadIdx.x, lo, pos, status);
-        cp_async_wait<0>();                          // this thread's part of tile ``it`` has landed
-        __syncthreads();                             // ... and everyone else's; the offsets of tile ``it`` have been read
-        if (it + 1 < n_tiles) {
+        const bool more = it + AHEAD < n_tiles;
+        if (more && threadIdx.x < TK) next = row_offset(src, (t_begin + it + AHEAD) * TK + threadIdx.x, lo, pos, status);
+        cp_async_wait<AHEAD - 1>();                  // this thread's part of tile ``it`` has landed
+        __syncthreads();                             // ... and everyone else's; the offsets of the last copy have been read
+        if (more) {
             if (threadIdx.x < TK) offs[threadIdx.x] = next;
             __syncthreads();
-            bf16* st = smem + ((it + 1) & 1) * 2 * TILE;
+            bf16* st = smem + ((it + AHEAD) % STAGES) * 2 * TILE;
             copy_rows<DMAX, THREADS, TK>(st, st + TILE, src, offs);
         }
         cp_async_commit();
-        const bf16* sp = smem + (it & 1) * 2 * TILE + warp * DECODE_KEYS * pitch<DMAX>();
+        const bf16* sp = smem + (it % STAGES) * 2 * TILE + warp * DECODE_KEYS * pitch<DMAX>();
         const int first = (t_begin + it) * TK + warp * DECODE_KEYS;
         compute_tile<DMAX, UPPER, DECODE_KEYS>(sp, sp + TILE, qfrag, o, m, l, first, d, scale_log2, pos, pos, lo, lo,
                                                first + DECODE_KEYS - 1 > pos || first < lo);
@@ -604,7 +617,7 @@ paged_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __res
 
 constexpr float LOG2E = 1.4426950408889634f;
 
-template <int DMAX> size_t decode_smem() { return (size_t)DECODE_STAGES * 2 * TK * pitch<DMAX>() * sizeof(bf16); }
+template <int DMAX> size_t decode_smem(int stages = 2) { return (size_t)stages * 2 * TK * pitch<DMAX>() * sizeof(bf16); }
 template <int DMAX> size_t prefill_smem() { return (size_t)PREFILL_STAGES * 2 * PREFILL_KEYS * pitch<DMAX>() * sizeof(bf16); }
 
 template <typename K> int allow_smem(K kernel, size_t bytes, const char* what) {
@@ -709,15 +722,22 @@ extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // a ring of three stages while all blocks still fit the device at once with it (four of them an SM at head size 128)
+    const long long blocks = (long long)splits * nkv * requests;
+    const bool deep = blocks <= 4LL * fe_sm_count();
 #define FE_DECODE_CLUSTER(DMAX, UPPER)                                                                                 \
     do {                                                                                                               \
-        auto kernel = paged_decode_kernel<DMAX, UPPER, true>;                                                          \
-        if (allow_smem(kernel, decode_smem<DMAX>(), "paged_decode (cluster)")) return 1;                               \
+        if (deep) FE_DECODE_CLUSTER_STAGES(DMAX, UPPER, 3); else FE_DECODE_CLUSTER_STAGES(DMAX, UPPER, 2);             \
+    } while (0)
+#define FE_DECODE_CLUSTER_STAGES(DMAX, UPPER, STAGES)                                                                  \
+    do {                                                                                                               \
+        auto kernel = paged_decode_kernel<DMAX, UPPER, true, STAGES>;                                                  \
+        if (allow_smem(kernel, decode_smem<DMAX>(STAGES), "paged_decode (cluster)")) return 1;                         \
         if (splits > 8) {                                                                                              \
             const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);    \
             FE_REQUIRE(err == cudaSuccess, "paged_decode (cluster): %s", cudaGetErrorString(err));                      \
         }                                                                                                              \
-        cfg.dynamicSmemBytes = decode_smem<DMAX>();                                                                    \
+        cfg.dynamicSmemBytes = decode_smem<DMAX>(STAGES);                                                              \
         const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, (const bf16*)q, q_stride, (bf16*)out, out_stride,     \
             (float*)nullptr, (float*)nullptr, (const bf16*)kc, (const bf16*)vc, block_table, bt_stride, cu_q, q_start, \
             nq, nkv, d, ps, num_pages, scale_log2, window, status);                                                    \
@@ -728,6 +748,7 @@ extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* 
     else if (d <= 128) { if (upper) FE_DECODE_CLUSTER(128, true); else FE_DECODE_CLUSTER(128, false); }
     else { if (upper) FE_DECODE_CLUSTER(256, true); else FE_DECODE_CLUSTER(256, false); }
 #undef FE_DECODE_CLUSTER
+#undef FE_DECODE_CLUSTER_STAGES
     return fe_check_launch("paged_decode (cluster)");
 }
 

@@ -601,3 +601,109 @@ def sample(logits, temperature, top_k, seed, draw):
     _run(_core(), "fe_sample", _ptr(logits), _c_ll(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
          _ptr(top_k), _ptr(seed), _ptr(draw), _ptr(out), _stream())
     return out
+
+
+# ---- a whole decoder layer as one call --------------------------------------------------------------------------
+import ctypes as _ct
+
+
+class _FeLayer(_ct.Structure):
+    """Mirror of ``struct FeLayer`` (csrc/layer_executor.cu): field for field, in its order."""
+    _fields_ = [(n, _ct.c_void_p) for n in ("input_norm", "post_norm", "qkv_weight", "qkv_bias", "out_weight", "gate_up_weight",
+                                             "down_weight", "inv_freq")] + \
+               [("eps", _ct.c_float), ("scale", _ct.c_float)] + \
+               [(n, _ct.c_int) for n in ("hidden", "nq", "nkv", "d", "intermediate", "rot", "window")]
+
+
+class _FeStep(_ct.Structure):
+    """Mirror of ``struct FeStep``."""
+    _fields_ = [(n, _ct.c_void_p) for n in ("positions", "slot_mapping", "block_table", "cu_q", "q_start", "residual", "workspace",
+                                             "attention_scratch", "status")] + \
+               [("workspace_bytes", _ct.c_longlong)] + \
+               [(n, _ct.c_int) for n in ("T", "R", "bt_stride", "max_q_len", "page_size", "num_pages", "attention", "splits",
+                                         "gate_up_tcgen05")]
+
+
+NATIVE_LAYER_MIN_ROWS = SKINNY_MAX_ROWS + 1      # fewer rows take the fused weight-streaming kernels, one by one
+_workspace: dict = {}
+_native_off = False           # set when cuBLAS could not be found from the library: kernel by kernel from then on
+
+
+class NativeLayer:
+    """The weights and sizes of one pre-norm attention + SwiGLU layer in the form ``fe_layer_forward`` takes them (the
+    cache is the step's: a model may be run over one cache manager after another).  Holds references to the tensors
+    it points at."""
+
+    def __init__(self, input_norm, post_norm, eps, qkv_weight, qkv_bias, out_weight, gate_up_weight, down_weight, inv_freq,
+                 rot, nq, nkv, d, scale, window):
+        self.keep = (input_norm, post_norm, qkv_weight, qkv_bias, out_weight, gate_up_weight, down_weight, inv_freq)
+        _need_cuda(*[t for t in self.keep if t is not None])
+        self.hidden, self.intermediate = int(out_weight.shape[0]), int(down_weight.shape[1])
+        self.nq, self.nkv, self.d, self.window = nq, nkv, d, window
+        self.c = _FeLayer(_ptr(input_norm), _ptr(post_norm), _ptr(qkv_weight), _ptr(qkv_bias), _ptr(out_weight),
+                          _ptr(gate_up_weight), _ptr(down_weight), _ptr(inv_freq),
+                          float(eps), float(scale), self.hidden, nq, nkv, d, self.intermediate, int(rot), int(window))
+
+    @staticmethod
+    def fits(*matrices) -> bool:
+        return all(m is not None and m.is_cuda and m.dtype == torch.bfloat16 and m.is_contiguous() and m.data_ptr() % 16 == 0
+                   and m.shape[1] % 8 == 0 for m in matrices)
+
+
+def _layer_workspace(device, nbytes: int) -> torch.Tensor:
+    have = _workspace.get(device)
+    if have is None or have.numel() < nbytes:
+        with torch.inference_mode(False):
+            have = _workspace[device] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return have
+
+
+def native_step(ctx, group, layer: NativeLayer, residual, write_cache: bool):
+    """The step's side of ``fe_layer_forward`` for layers of this shape: built once per step and cache group."""
+    T, requests = residual.shape[0], ctx.cu_q.numel() - 1
+    nq, nkv, d = layer.nq, layer.nkv, layer.d
+    scratch_bytes = 0
+    if ctx.max_q_len == 1 and nq // nkv <= 16:
+        splits = decode_splits(requests, nkv, ctx.max_ctx_len)
+        clustered = decode_cluster_splits(splits, ctx.max_ctx_len)
+        kind, splits = (0, clustered) if clustered else (1, splits)
+        if kind == 1:
+            scratch_bytes = _bf16().fe_paged_decode_scratch_bytes(_c_int(requests), _c_int(nq), _c_int(d), _c_int(splits))
+    elif tcgen05_attention_ok(ctx.max_q_len, nq, nkv, d, ctx.host_lengths, ctx.host_starts):
+        kind, splits = 2, prefill_splits(ctx.host_lengths, ctx.host_starts, nq, nkv, layer.window)
+        scratch_bytes = 4 * T * nq * splits * (d + 1) if splits > 1 else 0
+    else:
+        kind, splits = 3, 1
+    need = _bf16().fe_layer_workspace_bytes(_c_int(T), _c_int(layer.hidden), _c_int(nq), _c_int(nkv), _c_int(d), _c_int(layer.intermediate))
+    work = _layer_workspace(residual.device, need)
+    attention_scratch = scratch(residual.device, scratch_bytes) if scratch_bytes else None
+    gate_up_tcgen05 = T >= TCGEN05_MIN_ROWS and layer.hidden >= TCGEN05_MIN_K
+    step = _FeStep(_ptr(ctx.positions), _ptr(group.slot_mapping) if write_cache else None, _ptr(group.block_table), _ptr(ctx.cu_q),
+                   _ptr(ctx.q_start), _ptr(residual), _ptr(work), _ptr(attention_scratch), _ptr(status_word(residual.device)),
+                   work.numel(), T, requests, int(group.block_table.shape[1]), int(ctx.max_q_len), int(group.page_size),
+                   int(group.storage.shape[2]), kind, int(splits), 1 if gate_up_tcgen05 else 0)
+    step.keep = (work, attention_scratch, residual)
+    # entry points of this package behind one layer, counted as ``_run`` counts them: two norms, rotation and cache
+    # write, attention (with its merge, if any), the activation or the fused gate/up product
+    step.launches = 5
+    return step
+
+
+def layer_forward(layer: NativeLayer, step, k_cache, v_cache, pending, out):
+    """One layer through ``fe_layer_forward``; False when the library cannot (no cuBLAS in the process): the caller
+    then runs the layer kernel by kernel, now and from then on."""
+    global _native_off, launches
+    lib = _bf16()
+    rc = lib.fe_layer_forward(_ct.byref(layer.c), _ct.byref(step), _ptr(k_cache), _ptr(v_cache), _ptr(pending), _ptr(out), _stream())
+    if rc == 3:
+        _native_off = True
+        return False
+    if rc != 0:
+        raise RuntimeError(f"fe_layer_forward failed: {lib.fe_last_error().decode()}")
+    launches += step.launches
+    return True
+
+
+def native_layers_usable(ctx) -> bool:
+    return (not _native_off and ctx.dtype == torch.bfloat16 and ctx.num_tokens >= NATIVE_LAYER_MIN_ROWS
+            and not torch.cuda.is_current_stream_capturing())

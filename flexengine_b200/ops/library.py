@@ -30,7 +30,9 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
 # compiles only that
 GROUPS = {
     "core": ["errors.cu", "elementwise.cu", "attention_simt.cu", "gemm_fp32.cu", "sampling.cu"],
-    "bf16": ["errors.cu", "attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny.cu", "gemm_tcgen05.cu"],
+    # elementwise.cu once more: the layer executor launches its kernels from inside this library
+    "bf16": ["errors.cu", "attention_mma.cu", "attention_tcgen05.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "elementwise.cu",
+             "layer_executor.cu"],
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -134,7 +136,7 @@ def build(group: str, force: bool = False, verbose: bool = True) -> str:
             with ThreadPoolExecutor(max_workers=min(len(sources), os.cpu_count() or 2)) as pool:
                 objects = list(pool.map(compile_one, sources))
             tmp = path + f".tmp{os.getpid()}"
-            proc = subprocess.run([nvcc, "-shared", "-o", tmp, *objects], capture_output=True, text=True)
+            proc = subprocess.run([nvcc, "-shared", "-o", tmp, *objects, "-ldl"], capture_output=True, text=True)
             if proc.returncode != 0:
                 raise KernelLibraryError(f"linking {group} failed:\n{proc.stdout}\n{proc.stderr}")
             os.replace(tmp, path)

@@ -139,3 +139,34 @@ def test_every_cut_at_the_seven_b_widths(plain_weights, kind, dtype):
     print(f"7B widths {kind} {dtype}: worst |diff| / spread = {worst:.4f}")
     from flexengine_b200 import ops
     ops.check_status(DEV)
+
+
+def test_a_layer_as_one_call_gives_what_kernel_by_kernel_gives(plain_weights):
+    """A step of more than a handful of tokens runs each layer as one call into the kernel library (the same kernels
+    and library products in the same order, launched from C); with that switched off the parts launch them one by
+    one.  The two agree to the last bit or to a rounding (the library may choose another algorithm for a product)."""
+    from flexengine_b200 import ops
+    rng = random.Random(23)
+    ids = [helpers.random_prompt(rng, n, SHAPE["vocab_size"]) for n in (1100, 40, 150)]
+    results = {}
+    for native in (True, False):
+        ops._native_off = not native
+        try:
+            runner = runner_for("bfloat16", 90, max_requests=12)
+            before = ops.launches
+            rows = [runner.step([StepEntry("a", ids[0][:1030], [0, 1029])])]                       # 1,030 rows: the tcgen05 product
+            rows.append(runner.step([StepEntry("b", ids[1][:30], [29]), StepEntry("c", ids[2][:100], [99])]))
+            rows.append(runner.step([StepEntry("a", ids[0][1030:1070], [39]), StepEntry("b", ids[1][30:31], [0]),
+                                     StepEntry("c", ids[2][100:150], [0, 49])]))                   # a mixed step, keys split
+            rows.append(runner.step([StepEntry(r, [ids[i][-1]], [0]) for i, r in enumerate("abc")] +
+                                    [StepEntry(f"d{j}", [5 + j], [0]) for j in range(9)]))         # twelve decoded tokens
+            results[native] = (torch.cat(rows).float().cpu(), ops.launches - before)
+        finally:
+            ops._native_off = False
+    ops.check_status(DEV)
+    (fast, fast_launches), (slow, slow_launches) = results[True], results[False]
+    assert fast_launches == slow_launches, "the same kernels either way"
+    spread = float(slow.std(dim=-1).mean())
+    assert float((fast - slow).abs().max()) <= 0.02 * spread
+    want = plain_model.forward_logits(SHAPE, plain_weights, ids[0][:1070]).cpu()
+    helpers.assert_logits_close(fast[[0, 1, 4]], want[[0, 1029, 1069]], "bfloat16", "a layer as one call", "7B widths")
