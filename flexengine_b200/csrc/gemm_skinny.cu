@@ -44,11 +44,16 @@ struct ResidEpilogue {
 };
 
 // What a consumer of such a norm gets instead of normalised rows: the table of partial sums of squares.
+// ``next``: memory that the kernel after this one streams first (may be null): as a block leaves its loop it asks for its
+// share of the first ``next_bytes`` to be brought into L2, so that the next kernel's first loads, which would
+// otherwise go out to an idle memory system after the launch gap, are met there.
 struct RowScale {
     const float* sumsq;         // [tiles][8] or nullptr: the input is normalised already
     int tiles;
     float eps;
     int width;                  // elements of a row (the mean is over them)
+    const void* next;
+    long long next_bytes;
 };
 
 // What the fused query/key/value epilogue needs beside the product: bias, rotary table, where the
@@ -169,7 +174,6 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
         // output, so the first batch of weight loads is already in flight while that kernel ends
         if (s == s_begin) {
             griddep_wait();
-            griddep_launch_dependents();
             // the table of the rows' sums of squares is needed in the epilogue: asynchronous copies bring it into
             // shared memory meanwhile, so that no thread waits for it now and no block waits for memory at its end
             if (scale.sumsq != nullptr) {
@@ -211,9 +215,12 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, void*
             }
         }
     }
+    griddep_launch_dependents();               // the next kernel may start its own first loads as this one's blocks end
+    if (scale.next != nullptr)
+        prefetch_l2_share(scale.next, scale.next_bytes, (long long)blockIdx.x * (WARPS * 32) + threadIdx.x,
+                          (long long)gridDim.x * (WARPS * 32));
     if (s_begin >= s_end) {                    // a warp without work has not waited yet, nor started its copies
         griddep_wait();
-        griddep_launch_dependents();
         if (scale.sumsq != nullptr) {
             for (int chunk = threadIdx.x; chunk < scale.tiles * 2; chunk += WARPS * 32) {
                 const unsigned dst = (unsigned)__cvta_generic_to_shared(scale_table + chunk * 4);
@@ -382,12 +389,14 @@ static int check_scale(const char* what, const float* sumsq, int sumsq_tiles, in
 // epilogue: 0 bfloat16 [M, N]; 1 float [M, N]; 2 SwiGLU: W is [2 I, K] (gate rows, then up rows), out bfloat16 [M, I].
 // ``sumsq`` (may be null): see check_scale.
 extern "C" int fe_skinny_gemm_scaled(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
-                                     const float* sumsq, int sumsq_tiles, float eps, cudaStream_t stream) {
+                                     const float* sumsq, int sumsq_tiles, float eps, const void* next, long long next_bytes,
+                                     cudaStream_t stream) {
     FE_REQUIRE(M >= 1 && M <= 16, "skinny_gemm: %d rows; this kernel takes 1 to 16", M);
     FE_REQUIRE(N > 0 && K > 0 && K % KSTEP == 0, "skinny_gemm: K = %d must be a positive multiple of %d", K, KSTEP);
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_gemm: operands must be 16-byte aligned");
     if (check_scale("skinny_gemm", sumsq, sumsq_tiles, M, K)) return 1;
-    const RowScale scale{sumsq, sumsq_tiles, eps, K};
+    FE_REQUIRE(next_bytes >= 0, "skinny_gemm: negative byte count");
+    const RowScale scale{sumsq, sumsq_tiles, eps, K, next, next_bytes};
     if (epilogue == EPI_BF16) return launch<EPI_BF16>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
     if (epilogue == EPI_F32) return launch<EPI_F32>(x, W, out, M, N, K, 0, stream, QkvEpilogue{}, ResidEpilogue{}, scale);
     if (epilogue == EPI_SWIGLU) {
@@ -399,7 +408,7 @@ extern "C" int fe_skinny_gemm_scaled(const void* x, const void* W, void* out, in
 
 extern "C" int fe_skinny_gemm(const void* x, const void* W, void* out, int M, int N, int K, int epilogue,
                               cudaStream_t stream) {
-    return fe_skinny_gemm_scaled(x, W, out, M, N, K, epilogue, nullptr, 0, 0.f, stream);
+    return fe_skinny_gemm_scaled(x, W, out, M, N, K, epilogue, nullptr, 0, 0.f, nullptr, 0, stream);
 }
 
 // The product that ends a branch of a layer: residual[M, N] += x W^T (float, in place); scaled[M, N] = bfloat16(new
@@ -407,14 +416,16 @@ extern "C" int fe_skinny_gemm(const void* x, const void* W, void* out, int M, in
 // ``sumsq_in`` (may be null): the scales of the input rows, as for fe_skinny_gemm_scaled.  M <= 8.
 extern "C" int fe_skinny_gemm_residual(const void* x, const void* W, float* residual, const float* norm_weight, void* scaled,
                                        float* sumsq_out, int M, int N, int K, const float* sumsq_in, int sumsq_tiles,
-                                       float eps, cudaStream_t stream) {
+                                       float eps, const void* next, long long next_bytes, cudaStream_t stream) {
     FE_REQUIRE(M >= 1 && M <= 8, "skinny_gemm_residual: %d rows; this kernel takes 1 to 8", M);
     FE_REQUIRE(N > 0 && K > 0 && K % KSTEP == 0, "skinny_gemm_residual: K = %d must be a positive multiple of %d", K, KSTEP);
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_gemm_residual: operands must be 16-byte aligned");
     FE_REQUIRE(residual && norm_weight && scaled && sumsq_out, "skinny_gemm_residual: a null pointer");
     if (check_scale("skinny_gemm_residual", sumsq_in, sumsq_tiles, M, K)) return 1;
     const ResidEpilogue resid{residual, norm_weight, (bf16*)scaled, sumsq_out};
-    return launch<EPI_RESID>(x, W, nullptr, M, N, K, 0, stream, QkvEpilogue{}, resid, RowScale{sumsq_in, sumsq_tiles, eps, K});
+    FE_REQUIRE(next_bytes >= 0, "skinny_gemm_residual: negative byte count");
+    return launch<EPI_RESID>(x, W, nullptr, M, N, K, 0, stream, QkvEpilogue{}, resid,
+                             RowScale{sumsq_in, sumsq_tiles, eps, K, next, next_bytes});
 }
 
 // The query/key/value projection of an attention layer with its epilogue fused: y = x W^T + bias,
@@ -433,5 +444,6 @@ extern "C" int fe_skinny_qkv(const void* x, const void* W, void* out, const floa
     FE_REQUIRE((((size_t)x | (size_t)W) & 15) == 0, "skinny_qkv: operands must be 16-byte aligned");
     if (check_scale("skinny_qkv", sumsq, sumsq_tiles, M, K)) return 1;
     QkvEpilogue e{bias, positions, inv_freq, slot_mapping, (bf16*)kc, (bf16*)vc, nq, nkv, d, ps, num_slots, status};
-    return launch<EPI_QKV>(x, W, out, M, (nq + 2 * nkv) * d, K, 0, stream, e, ResidEpilogue{}, RowScale{sumsq, sumsq_tiles, eps, K});
+    return launch<EPI_QKV>(x, W, out, M, (nq + 2 * nkv) * d, K, 0, stream, e, ResidEpilogue{},
+                           RowScale{sumsq, sumsq_tiles, eps, K, nullptr, 0});
 }

@@ -117,6 +117,7 @@ def carry_tokens(token_ids, rows, sources, previous):
 
 UPCOMING_MAX_ROWS = 16            # a step of this many tokens or fewer leaves the memory system idle between products
 UPCOMING_BYTES_MERGE = 16 << 20   # the same for the merge kernel of decode attention, ahead of the output projection
+UPCOMING_TAIL_BYTES = 16 << 20    # what the blocks of a weight-streaming product ask into L2 of the next matrix as they end
 UPCOMING_BYTES = 10 << 20         # how much of the next weight matrix a norm asks into L2 ahead of its product: what the
                                   # memory system delivers while the norm runs (8-12 MB measured best on the 7B shape)
 
@@ -189,7 +190,7 @@ def gemm_fp32(x, w, bias=None):
     return out
 
 
-def linear(x, w, bias=None, out_float32=False, follow=None):
+def linear(x, w, bias=None, out_float32=False, follow=None, upcoming=None):
     """y = x w^T (+ bias); x [M, K], w [N, K].  A float32 weight runs the true 32-bit product
     (CUDA cores, no reduced-precision mode) whatever the activation dtype; a bfloat16 weight
     runs on tensor cores with float32 accumulation.
@@ -197,7 +198,8 @@ def linear(x, w, bias=None, out_float32=False, follow=None):
     ``follow`` = (residual, norm weight, eps): the product ends a branch of a layer; its result is to be added to
     the float32 residual stream [M, N] and an RMSNorm reads the sum next.  Where the weight-streaming kernel runs (a
     decode step), it does both in its epilogue and a ``Prenormed`` comes back; otherwise the plain product does,
-    and the caller adds and normalises as usual."""
+    and the caller adds and normalises as usual.  ``upcoming``: the matrix that the kernel after this one streams;
+    the weight-streaming kernel asks for its start to be brought into L2 as its blocks end."""
     kernel = _fits(x, w)
     if isinstance(x, Prenormed) and not kernel:
         x = x.materialize()
@@ -213,11 +215,12 @@ def linear(x, w, bias=None, out_float32=False, follow=None):
             _rows, sumsq, tiles, eps = _rows_and_scale(x)
             table = torch.empty((-(-N // 16), 8), dtype=torch.float32, device=rows.device)
             _run(_bf16(), "fe_skinny_gemm_residual", _ptr(rows), _ptr(w), _ptr(residual), _ptr(norm_weight), _ptr(scaled),
-                 _ptr(table), _c_int(M), _c_int(N), _c_int(rows.shape[1]), sumsq, tiles, eps, _stream())
+                 _ptr(table), _c_int(M), _c_int(N), _c_int(rows.shape[1]), sumsq, tiles, eps,
+                 *_upcoming(upcoming, M, UPCOMING_TAIL_BYTES), _stream())
             return Prenormed(scaled, table, norm_eps, residual, norm_weight)
     if kernel and w.dtype == torch.bfloat16:
         wide = out_float32 or bias is not None           # a bias is added in float32, before the one rounding
-        y = skinny_gemm(x, w, EPI_F32 if wide else EPI_BF16)
+        y = skinny_gemm(x, w, EPI_F32 if wide else EPI_BF16, upcoming=upcoming)
         if bias is not None:
             y += bias
         return y if out_float32 or not wide else y.to(torch.bfloat16)
@@ -250,7 +253,7 @@ def skinny_ok(x, w) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def skinny_gemm(x, w, epilogue: int = EPI_BF16):
+def skinny_gemm(x, w, epilogue: int = EPI_BF16, upcoming=None):
     """x [M <= 16, K] (a tensor or a Prenormed) times w [N, K]^T by streaming w once; see csrc/gemm_skinny.cu."""
     x, sumsq, tiles, eps = _rows_and_scale(x)
     M, K = x.shape
@@ -260,7 +263,7 @@ def skinny_gemm(x, w, epilogue: int = EPI_BF16):
     else:
         out = torch.empty((M, N), dtype=torch.float32 if epilogue == EPI_F32 else torch.bfloat16, device=x.device)
     _run(_bf16(), "fe_skinny_gemm_scaled", _ptr(x), _ptr(w), _ptr(out), _c_int(M), _c_int(N), _c_int(K), _c_int(epilogue),
-         sumsq, tiles, eps, _stream())
+         sumsq, tiles, eps, *_upcoming(upcoming, M, UPCOMING_TAIL_BYTES), _stream())
     return out
 
 
@@ -305,14 +308,14 @@ def swiglu(gate_up, intermediate):
     return out
 
 
-def linear_swiglu(x, w, intermediate):
+def linear_swiglu(x, w, intermediate, upcoming=None):
     """silu(x Wg^T) * (x Wu^T) with w = [Wg; Wu] ([2I, K]); one kernel for a handful of rows."""
     kernel = _fits(x, w) if w.shape[0] == 2 * intermediate else ""
     if isinstance(x, Prenormed) and not kernel:
         x = x.materialize()
         kernel = _fits(x, w) if w.shape[0] == 2 * intermediate else ""
     if kernel == "skinny":
-        return skinny_gemm(x, w, EPI_SWIGLU)
+        return skinny_gemm(x, w, EPI_SWIGLU, upcoming=upcoming)
     if tcgen05_ok(x, w) and w.shape[0] == 2 * intermediate:
         return gemm_tcgen05(x, w, EPI_SWIGLU)
     return swiglu(linear(x, w), intermediate)

@@ -56,7 +56,7 @@ class AttentionMixer(Mixer):
         return {"kind": "window" if self.window > 0 else "full", "kv_heads": self.num_kv_heads,
                 "head_dim": self.head_dim, "window": self.window}
 
-    def forward(self, ctx, h, entry, follow=None):
+    def forward(self, ctx, h, entry, follow=None, upcoming=None):
         ops = ctx.ops
         group = ctx.groups[entry.cache_group]
         k_cache, v_cache = group.kv_slot(entry.cache_slot)
@@ -79,7 +79,7 @@ class AttentionMixer(Mixer):
                                   self.num_kv_heads, self.head_dim, group.page_size, self.scale, self.window,
                                   upcoming=self.out_weight)
         if follow is not None:
-            return ops.linear(out, self.out_weight, self.out_bias, follow=follow)
+            return ops.linear(out, self.out_weight, self.out_bias, follow=follow, upcoming=upcoming)
         return ops.linear(out, self.out_weight, self.out_bias)
 
 

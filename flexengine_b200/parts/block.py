@@ -36,17 +36,18 @@ class PreNormBlock:
     def parts(self) -> dict:
         return {name: getattr(self, name) for name in self.part_names}
 
-    def forward(self, ctx, residual, pending, entry, next_norm=None):
+    def forward(self, ctx, residual, pending, entry, next_norm=None, next_reads=None):
         """``next_norm``: the norm that will read the residual after this block (the next block's input norm), when
-        the model knows it: the feed-forward may then begin it (see ``parts.base``, "a norm that follows")."""
+        the model knows it: the feed-forward may then begin it (see ``parts.base``, "a norm that follows").
+        ``next_reads``: the matrix the next block streams first."""
         if getattr(ctx.ops, "native_layers_usable", None) is not None and ctx.ops.native_layers_usable(ctx):
             done = self._native_forward(ctx, residual, pending, entry)
             if done is not None:
                 return done
         h = self._normed(self.input_norm, ctx, residual, pending, self.mixer)
-        mixed = self._branch(self.mixer, (ctx, h, entry), ctx, residual, self.post_mixer_norm)
+        mixed = self._branch(self.mixer, (ctx, h, entry), ctx, residual, self.post_mixer_norm, self.feed_forward.reads_first())
         h = self._normed(self.post_mixer_norm, ctx, residual, mixed, self.feed_forward)
-        return self._branch(self.feed_forward, (ctx, h), ctx, residual, next_norm)
+        return self._branch(self.feed_forward, (ctx, h), ctx, residual, next_norm, next_reads)
 
     def _native_forward(self, ctx, residual, pending, entry):
         """The whole layer as one call into the kernel library (a step of more than a handful of tokens, outside graph
@@ -102,11 +103,15 @@ class PreNormBlock:
         return _norm(norm, ctx, residual, pending, reader.reads_first())
 
     @staticmethod
-    def _branch(part, args, ctx, residual, norm_after):
+    def _branch(part, args, ctx, residual, norm_after, upcoming=None):
         follow = None
         if norm_after is not None and _accepts(part.forward, "follow"):
             follow = norm_after.following(ctx, residual)
-        return part.forward(*args, follow=follow) if follow is not None else part.forward(*args)
+        if follow is None:
+            return part.forward(*args)
+        if upcoming is not None and _accepts(part.forward, "upcoming"):
+            return part.forward(*args, follow=follow, upcoming=upcoming)
+        return part.forward(*args, follow=follow)
 
 
 def _norm(norm, ctx, residual, delta, upcoming):

@@ -25,11 +25,12 @@ class SwiGLU(FeedForward):
     def reads_first(self):
         return self.gate_up_weight
 
-    def forward(self, ctx, h, follow=None):
-        act = ctx.ops.linear_swiglu(h, self.gate_up_weight, self.intermediate_size)
-        if follow is not None:
-            return ctx.ops.linear(act, self.down_weight, follow=follow)
-        return ctx.ops.linear(act, self.down_weight)
+    def forward(self, ctx, h, follow=None, upcoming=None):
+        if follow is None and upcoming is None:
+            return ctx.ops.linear(ctx.ops.linear_swiglu(h, self.gate_up_weight, self.intermediate_size), self.down_weight)
+        # a decode step on kernels that take the hints: each product is told which matrix is streamed after it
+        act = ctx.ops.linear_swiglu(h, self.gate_up_weight, self.intermediate_size, upcoming=self.down_weight)
+        return ctx.ops.linear(act, self.down_weight, follow=follow, upcoming=upcoming)
 
 
 register_feed_forward("swiglu", SwiGLU)

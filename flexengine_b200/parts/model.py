@@ -72,7 +72,8 @@ class DecoderModel:
         known = getattr(block, "_knows_next_norm", None)
         if known is None:
             import inspect
-            known = block._knows_next_norm = "next_norm" in inspect.signature(block.forward).parameters
+            names = inspect.signature(block.forward).parameters
+            known = block._knows_next_norm = "next_norm" in names and "next_reads" in names
         return known
 
     # --- forward -----------------------------------------------------------------------
@@ -86,7 +87,9 @@ class DecoderModel:
             # a block that can make use of it is told which norm reads the residual after it
             after = self.blocks[run[at + 1].layer] if at + 1 < len(run) else None
             if after is not None and getattr(after, "takes_prenormed", False) and self._knows_next_norm(block):
-                pending = block.forward(ctx, residual, pending, entry, next_norm=after.input_norm)
+                reads = getattr(after, "mixer", None)
+                pending = block.forward(ctx, residual, pending, entry, next_norm=after.input_norm,
+                                        next_reads=reads.reads_first() if reads is not None else None)
             else:
                 pending = block.forward(ctx, residual, pending, entry)
         if ctx.num_logit_rows == 0:
