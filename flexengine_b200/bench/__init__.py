@@ -18,8 +18,9 @@ def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="flexengine bench", description="Measure the engine on one GPU; prints one JSON line")
     p.add_argument("--workload", choices=["decode", "serve-1.5b", "long-14b"], default="decode")
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=16, help="timed decode steps (decode workload)")
-    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--steps", type=int, default=64, help="timed decode steps (decode workload)")
+    p.add_argument("--warmup", type=int, default=16,
+                   help="untimed steps before the timed ones (after a prompt the first dozen decode steps run a few percent slow)")
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (both numbers are reported)")

@@ -133,9 +133,9 @@ def run(args) -> int:
         print(json.dumps({"profiled": args.profile, "batch": args.batch}))
         return 0
 
-    for w in range(warmup):
+    for w in range(3):
         prefill_once(-1 - w)
-    prefill_ms, _ = timer.timed(prefill_once, 3)
+    prefill_ms, _ = timer.timed(prefill_once, 5)
     flops = prefill_flops(cfg, PROMPT_LEN)
     prefill = {"value": PROMPT_LEN / (prefill_ms / 1e3), "tokens": PROMPT_LEN, "ms": prefill_ms,
                "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12)}
@@ -146,7 +146,7 @@ def run(args) -> int:
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            pms, _, pctx = decode(b, max(4, args.steps // 2), 3)
+            pms, _, pctx = decode(b, max(4, args.steps // 2), warmup)
             points[f"decode_b{b}"] = b / (pms / 1e3)
             points[f"decode_b{b}_hbm_frac"] = decode_bytes(cfg, b, pctx) / (pms / 1e3) / 1e9 / peaks["hbm_gbs"]
         # tokens a second of a step that brings 128 prompt tokens after 3,072 beside seven decoded tokens

@@ -20,6 +20,7 @@
 //          key/value stages.
 #include <math_constants.h>
 
+#define FE_PDL_CLASS 2      // FE_PDL_DECODE_ATTENTION
 #include "common.cuh"
 
 using namespace fe;
@@ -715,13 +716,15 @@ extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* 
     cfg.gridDim = dim3(splits, nkv, requests);
     cfg.blockDim = dim3(DECODE_WARPS * 32);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = (fe_pdl_enabled() & 16) != 0;     // a class of its own
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     // a ring of three stages while all blocks still fit the device at once with it (four of them an SM at head size 128)
     const long long blocks = (long long)splits * nkv * requests;
     const bool deep = blocks <= 4LL * fe_sm_count();

@@ -121,8 +121,18 @@ int fe_check_launch(const char* what);
 int fe_pdl_enabled();
 int fe_sm_count();      // multiprocessors of the current device (asked once per device)
 
+// Classes of kernels for fe_set_pdl: a source file names its own before including this header.
+#define FE_PDL_STREAMING_GEMM 1
+#define FE_PDL_DECODE_ATTENTION 2
+#define FE_PDL_ELEMENTWISE 4
+#define FE_PDL_SAMPLING 8
+#define FE_PDL_OTHER 128
+#ifndef FE_PDL_CLASS
+#define FE_PDL_CLASS FE_PDL_OTHER
+#endif
+
 namespace fe {
-// Launch with the programmatic-stream-serialization attribute (when enabled).
+// Launch with the programmatic-stream-serialization attribute (when enabled for this file's class of kernels).
 template <typename... KArgs, typename... Args>
 inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
@@ -132,7 +142,7 @@ inline void launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = fe_pdl_enabled();
+    attr[0].val.programmaticStreamSerializationAllowed = (fe_pdl_enabled() & FE_PDL_CLASS) != 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);       // errors surface in fe_check_launch

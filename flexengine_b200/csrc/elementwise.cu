@@ -4,6 +4,7 @@
 //   rotary   pairs (j, j + rot/2), angle = position * inv_freq   (reference: inference/models/qwen2.py:73-77)
 //   SwiGLU   silu(g) * u, silu(g) = g / (1 + exp(-g))            (reference: tests/unit/test_synthetic_qwen.py:35-36)
 // All arithmetic is float; sine, cosine, exp and rsqrt are the accurate library forms.
+#define FE_PDL_CLASS 4      // FE_PDL_ELEMENTWISE
 #include "common.cuh"
 
 using namespace fe;

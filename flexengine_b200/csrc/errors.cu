@@ -37,12 +37,13 @@ int fe_sm_count() {
 
 extern "C" int fe_device_sm_count() { return fe_sm_count(); }
 
-static int g_pdl = 1;
+static int g_pdl = 0;
 
 int fe_pdl_enabled() { return g_pdl; }
 
-// 1: kernels may overlap their preamble with the tail of the kernel before them (default); 0: off.
-extern "C" void fe_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+// Which kernels may overlap their preamble with the tail of the kernel before them: a set of FE_PDL_* classes
+// (0: none).  A file's kernels belong to the class it defines before it includes common.cuh.
+extern "C" void fe_set_pdl(int classes) { g_pdl = classes; }
 
 extern "C" const char* fe_last_error() { return g_last_error; }
 

@@ -23,6 +23,7 @@
 // norm (query/key/value, gate/up) adds the table up in a fixed order while its first weights are on their way
 // and multiplies its accumulators by rsqrt(mean square + eps): a row's scale is a factor of every term of its
 // dot products, so it may be applied after them.
+#define FE_PDL_CLASS 1      // FE_PDL_STREAMING_GEMM
 #include "common.cuh"
 
 using namespace fe;

@@ -13,6 +13,7 @@
 // arithmetic, so the intervals of the tokens tile [0, total) and the result is the same on every run.
 #include <math_constants.h>
 
+#define FE_PDL_CLASS 8      // FE_PDL_SAMPLING
 #include "common.cuh"
 
 using namespace fe;

@@ -209,9 +209,10 @@ def load(group: str) -> ctypes.CDLL:
         for fn, (restype, argtypes) in prototypes(group).items():
             entry = getattr(lib, fn)
             entry.restype, entry.argtypes = restype, argtypes
-        # programmatic dependent launch (a kernel's preamble overlaps the tail of the one before):
-        # measured to bring nothing inside CUDA graphs, so it is off unless FLEXENGINE_PDL=1
-        lib.fe_set_pdl(ctypes.c_int(1 if os.environ.get("FLEXENGINE_PDL", "0") == "1" else 0))
+        # programmatic dependent launch (a kernel's preamble overlaps the tail of the one before): off unless
+        # FLEXENGINE_PDL names classes of kernels (a sum of 1 streaming products, 2 decode attention, 4 elementwise,
+        # 8 sampling, 16 decode attention in clusters, 128 the rest)
+        lib.fe_set_pdl(ctypes.c_int(int(os.environ.get("FLEXENGINE_PDL", "0") or 0)))
         _loaded[group] = lib
         return lib
 
