@@ -99,7 +99,11 @@ template <> __device__ __forceinline__ void store8<bf16>(bf16* p, const float* v
 // may be touched before.  launch_dependents lets the next kernel start its own preamble; it is
 // called after the wait, so that at most one kernel is resident ahead of the one that runs
 // (called before, every later kernel of a graph piles onto the SMs and starves the running one).
-// Without the launch attribute both are no-ops.
+// Without the launch attribute both are no-ops, and the attribute is off unless fe_set_pdl names classes of
+// kernels: inside the CUDA graph of a decode step (28 layers, B200) a step took 3.24 ms without it; with it on the
+// weight-streaming products alone 3.36 ms when they never trigger (the dependent starts as the last block exits),
+// 4.25 ms with the trigger behind their main loop and 5.5 ms with the trigger first: the earlier the dependent's
+// blocks become resident, the slower the step.
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
