@@ -1,6 +1,6 @@
 """``flexengine bench``: the measurements of this engine as a program of the package.
 
-    flexengine bench [--workload decode|serve-1.5b|long-14b] [--steps K] [--warmup W] [--kernels] ...
+    flexengine bench [--workload decode|serve-1.5b|long-14b|lengths] [--steps K] [--warmup W] [--kernels] ...
 
 ``decode`` (the default) is the headline: decode tokens per second on the Qwen2.5-7B shape at batch 8 after
 2,048-token prompts, with prefill, end-to-end, roofline and batch 1 / 64 beside it; ``--kernels`` adds a table of the
@@ -16,7 +16,7 @@ import argparse
 
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="flexengine bench", description="Measure the engine on one GPU; prints one JSON line")
-    p.add_argument("--workload", choices=["decode", "serve-1.5b", "long-14b"], default="decode")
+    p.add_argument("--workload", choices=["decode", "serve-1.5b", "long-14b", "lengths"], default="decode")
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=64, help="timed decode steps (decode workload)")
     p.add_argument("--warmup", type=int, default=16,
@@ -52,5 +52,8 @@ def main(argv=None, reference_arm=None) -> int:
     if args.workload == "long-14b":
         from .serving import long_context
         return long_context(args)
+    if args.workload == "lengths":
+        from .lengths import run as run_lengths
+        return run_lengths(args)
     from .headline import run
     return run(args)

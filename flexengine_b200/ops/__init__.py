@@ -470,14 +470,17 @@ def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, 
     return out
 
 
-DECODE_CLUSTER_MAX_SPLITS = 16       # blocks of one thread-block cluster (fe_paged_decode_cluster_max_splits)
-DECODE_CLUSTER_MAX_TILES = 8         # a split of a cluster walks at most this many tiles of 32 keys ...
+DECODE_CLUSTER_MAX_SPLITS = 14       # blocks of one cluster, as this rule uses them (the kernel takes up to 16, see below)
+DECODE_CLUSTER_MAX_TILES = 10        # a split of a cluster walks at most this many tiles of 32 keys ...
 
 
 def decode_cluster_splits(splits: int, max_ctx_len: int) -> int:
     """How many splits the cluster kernel takes for a step that ``decode_splits`` would split ``splits`` ways, or 0
-    when the two-kernel form is the better one: a cluster holds 16 blocks at most, so a long context of a small
-    batch, which wants more splits than that, keeps them and the separate merge."""
+    when the two-kernel form is the better one: a long context of a small batch, which wants more splits than a
+    cluster holds, keeps them and the separate merge (batch 8 at 8,192 tokens: 3.53 against 3.59 ms a step, at
+    16,384: 4.12 against 4.24; batch 1 at 16,384: 3.0 against 3.8).  Clusters of 15 and 16 blocks are not used:
+    32 of them (batch 8, four key/value heads) make a step of the 7B shape 3.25 ms long where clusters of 8 to 14
+    make it 3.11 to 3.13; with 4 or 16 clusters (batch 1 or 4) the sizes are level."""
     if splits <= 1:
         return 0
     if splits <= DECODE_CLUSTER_MAX_SPLITS:

@@ -393,7 +393,8 @@ def test_cluster_decode_kernel_window_far_key_and_limits(gen):
     torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
     with pytest.raises(RuntimeError, match="cluster"):
         _attention_case(torch.bfloat16, 4, 2, 64, 16, [(300, 1)], 0, gen, splits=17, cluster=True)
-    assert ops().decode_cluster_splits(14, 2048) == 14 and ops().decode_cluster_splits(32, 2048) == 16
+    assert ops().decode_cluster_splits(14, 2048) == 14 and ops().decode_cluster_splits(32, 2048) == 14
+    assert ops().decode_cluster_splits(16, 2048) == 14 and ops().decode_cluster_splits(21, 4096) == 14
     assert ops().decode_cluster_splits(27, 32768) == 0 and ops().decode_cluster_splits(1, 10) == 0
     ops().check_status(DEV)
 
