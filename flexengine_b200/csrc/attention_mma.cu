@@ -700,6 +700,52 @@ extern "C" int fe_paged_decode_mma_upcoming(const void* q, long long q_stride, v
 // of more than 8 blocks are asked for as a non-portable size); the cluster must fit the device, else an error.
 extern "C" int fe_paged_decode_cluster_max_splits(void) { return CLUSTER_MAX_SPLITS; }
 
+// How many clusters of ``splits`` blocks of the kernel that fe_paged_decode_cluster would launch for these sizes are
+// resident on the device at once (a cluster lives inside one processing cluster of the GPU, so this is less than
+// the blocks that fit divided by ``splits``); 0 when the device cannot place such a cluster at all, -1 on an error.
+// A step that needs a few clusters more than this runs them alone after the round.
+extern "C" int fe_paged_decode_cluster_resident(int requests, int nq, int nkv, int d, int splits) {
+    FE_REQUIRE(splits >= 1 && splits <= CLUSTER_MAX_SPLITS && requests >= 1 && nq >= 1 && nkv >= 1 && d >= 1 && d <= 256,
+               "paged_decode (cluster): bad sizes");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, nkv, requests);
+    cfg.blockDim = dim3(DECODE_WARPS * 32);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const bool deep = (long long)splits * nkv * requests <= 4LL * fe_sm_count();
+    int clusters = 0;
+#define FE_RESIDENT_STAGES(DMAX, UPPER, STAGES)                                                                        \
+    do {                                                                                                               \
+        auto kernel = paged_decode_kernel<DMAX, UPPER, true, STAGES>;                                                  \
+        if (allow_smem(kernel, decode_smem<DMAX>(STAGES), "paged_decode (cluster)")) return -1;                        \
+        if (splits > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) { \
+            cudaGetLastError();                                                                                        \
+            return 0;                                                                                                  \
+        }                                                                                                              \
+        cfg.dynamicSmemBytes = decode_smem<DMAX>(STAGES);                                                              \
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) {                                  \
+            cudaGetLastError();                                                                                        \
+            return 0;                                                                                                  \
+        }                                                                                                              \
+    } while (0)
+#define FE_RESIDENT(DMAX, UPPER)                                                                                       \
+    do {                                                                                                               \
+        if (deep) FE_RESIDENT_STAGES(DMAX, UPPER, 3); else FE_RESIDENT_STAGES(DMAX, UPPER, 2);                         \
+    } while (0)
+    const bool upper = nq / nkv > 8;
+    if (d <= 64) { if (upper) FE_RESIDENT(64, true); else FE_RESIDENT(64, false); }
+    else if (d <= 128) { if (upper) FE_RESIDENT(128, true); else FE_RESIDENT(128, false); }
+    else { if (upper) FE_RESIDENT(256, true); else FE_RESIDENT(256, false); }
+#undef FE_RESIDENT
+#undef FE_RESIDENT_STAGES
+    return clusters;
+}
+
 extern "C" int fe_paged_decode_cluster(const void* q, long long q_stride, void* out, long long out_stride,
                                        const void* kc, const void* vc, const int* block_table, int bt_stride,
                                        const int* cu_q, const int* q_start, int requests, int nq, int nkv, int d, int ps,

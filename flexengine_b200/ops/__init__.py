@@ -470,23 +470,44 @@ def paged_decode_mma(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, 
     return out
 
 
-DECODE_CLUSTER_MAX_SPLITS = 14       # blocks of one cluster, as this rule uses them (the kernel takes up to 16, see below)
-DECODE_CLUSTER_MAX_TILES = 10        # a split of a cluster walks at most this many tiles of 32 keys ...
+DECODE_CLUSTER_MAX_SPLITS = 16       # blocks of one thread-block cluster (fe_paged_decode_cluster_max_splits)
+DECODE_CLUSTER_MAX_TILES = 8         # a split of a cluster walks at most this many tiles of 32 keys ...
+DECODE_CLUSTER_ONE_ROUND_MIN = 8     # ... and a cluster is cut down to fit one round only if this many splits remain
+_CLUSTERS_RESIDENT: dict = {}
 
 
-def decode_cluster_splits(splits: int, max_ctx_len: int) -> int:
+def clusters_resident(requests: int, nq: int, nkv: int, d: int, splits: int) -> int:
+    """How many clusters of ``splits`` blocks of the decode kernel the device holds at once (asked of the driver once
+    per shape): a cluster lives inside one of the GPU's processing clusters, so it is fewer than blocks / splits."""
+    key = (requests, nq, nkv, d, splits)
+    if key not in _CLUSTERS_RESIDENT:
+        _CLUSTERS_RESIDENT[key] = int(_bf16().fe_paged_decode_cluster_resident(requests, nq, nkv, d, splits))
+    return _CLUSTERS_RESIDENT[key]
+
+
+def decode_cluster_splits(splits: int, max_ctx_len: int, clusters: int = 0, resident=None) -> int:
     """How many splits the cluster kernel takes for a step that ``decode_splits`` would split ``splits`` ways, or 0
     when the two-kernel form is the better one: a long context of a small batch, which wants more splits than a
-    cluster holds, keeps them and the separate merge (batch 8 at 8,192 tokens: 3.53 against 3.59 ms a step, at
-    16,384: 4.12 against 4.24; batch 1 at 16,384: 3.0 against 3.8).  Clusters of 15 and 16 blocks are not used:
-    32 of them (batch 8, four key/value heads) make a step of the 7B shape 3.25 ms long where clusters of 8 to 14
-    make it 3.11 to 3.13; with 4 or 16 clusters (batch 1 or 4) the sizes are level."""
+    cluster holds, keeps them and the separate merge (batch 8 at 8,192 tokens: 3.53 against 3.59 ms a step of the 7B
+    shape, at 16,384: 4.12 against 4.24; batch 1 at 16,384: 3.0 against 3.8).
+
+    ``clusters``: how many clusters the step needs (requests x key/value heads); ``resident(s)``: how many clusters of
+    s blocks the device holds at once.  A few clusters over one round run alone after it: 32 clusters of 15 or 16
+    blocks, of which fewer than 32 fit, make a step 3.25 ms long where clusters of 8 to 14 make it 3.11 to 3.13, and
+    64 clusters of 9 cost 4.07 ms where 64 of 8 cost 3.80.  So the count is cut down to the largest that fits one
+    round, if that leaves eight splits or more; large batches, whose clusters of two to six blocks take several
+    rounds anyway, keep their count (batch 64: three splits 4.88 ms, two 4.97)."""
     if splits <= 1:
         return 0
-    if splits <= DECODE_CLUSTER_MAX_SPLITS:
-        return splits
-    tiles = -(-max_ctx_len // 32)
-    return DECODE_CLUSTER_MAX_SPLITS if tiles <= DECODE_CLUSTER_MAX_SPLITS * DECODE_CLUSTER_MAX_TILES else 0
+    most = min(splits, DECODE_CLUSTER_MAX_SPLITS)
+    if splits > most and -(-max_ctx_len // 32) > most * DECODE_CLUSTER_MAX_TILES:
+        return 0
+    if resident is None or clusters <= 0:
+        return most
+    fit = next((s for s in range(most, 1, -1) if resident(s) >= clusters), 0)
+    if fit >= min(most, DECODE_CLUSTER_ONE_ROUND_MIN):
+        return fit
+    return most if resident(most) > 0 else 0
 
 
 def paged_decode_cluster(q, q_stride, k_cache, v_cache, block_table, cu_q, q_start, requests, nq, nkv, d, page_size,
@@ -579,7 +600,8 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
     requests = ctx.cu_q.numel() - 1
     if ctx.max_q_len == 1 and nq // nkv <= 16:
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
-        clustered = decode_cluster_splits(splits, ctx.max_ctx_len)
+        clustered = decode_cluster_splits(splits, ctx.max_ctx_len, requests * nkv,
+                                          lambda s: clusters_resident(requests, nq, nkv, d, s))
         if clustered:
             return paged_decode_cluster(qkv, qkv.stride(0), k_cache, v_cache, block_table, ctx.cu_q, ctx.q_start, requests,
                                         nq, nkv, d, page_size, scale, window, clustered)
@@ -671,7 +693,8 @@ def native_step(ctx, group, layer: NativeLayer, residual, write_cache: bool):
     scratch_bytes = 0
     if ctx.max_q_len == 1 and nq // nkv <= 16:
         splits = decode_splits(requests, nkv, ctx.max_ctx_len)
-        clustered = decode_cluster_splits(splits, ctx.max_ctx_len)
+        clustered = decode_cluster_splits(splits, ctx.max_ctx_len, requests * nkv,
+                                          lambda s: clusters_resident(requests, nq, nkv, d, s))
         kind, splits = (0, clustered) if clustered else (1, splits)
         if kind == 1:
             scratch_bytes = _bf16().fe_paged_decode_scratch_bytes(_c_int(requests), _c_int(nq), _c_int(d), _c_int(splits))

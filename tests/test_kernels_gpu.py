@@ -393,8 +393,18 @@ def test_cluster_decode_kernel_window_far_key_and_limits(gen):
     torch.testing.assert_close(got.float(), want.float(), **bar(torch.bfloat16))
     with pytest.raises(RuntimeError, match="cluster"):
         _attention_case(torch.bfloat16, 4, 2, 64, 16, [(300, 1)], 0, gen, splits=17, cluster=True)
-    assert ops().decode_cluster_splits(14, 2048) == 14 and ops().decode_cluster_splits(32, 2048) == 14
-    assert ops().decode_cluster_splits(16, 2048) == 14 and ops().decode_cluster_splits(21, 4096) == 14
+    assert ops().decode_cluster_splits(14, 2048) == 14 and ops().decode_cluster_splits(32, 2048) == 16
+    # cut down to what fits the device in one round, as long as eight splits remain
+    fits = {16: 20, 15: 24, 14: 35, 13: 36, 9: 60, 8: 74, 3: 190, 2: 296}
+    resident = lambda s: fits.get(s, fits[min(k for k in fits if k >= s)])
+    assert ops().decode_cluster_splits(21, 4096, 32, resident) == 14
+    assert ops().decode_cluster_splits(13, 4096, 64, resident) == 8
+    assert ops().decode_cluster_splits(3, 4096, 256, resident) == 3 and ops().decode_cluster_splits(16, 4096, 4, resident) == 16
+    assert ops().decode_cluster_splits(12, 4096, 32, lambda s: 0) == 0
+    real = lambda s: ops().clusters_resident(8, 28, 4, 128, s)
+    assert real(2) >= real(8) >= real(16) >= 1
+    chosen = ops().decode_cluster_splits(21, 4096, 32, real)
+    assert 8 <= chosen <= 16 and real(chosen) >= 32
     assert ops().decode_cluster_splits(27, 32768) == 0 and ops().decode_cluster_splits(1, 10) == 0
     ops().check_status(DEV)
 
