@@ -76,7 +76,9 @@ def main(argv=None) -> int:
     parser.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True,
-                        help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+                        help="the most tokens that live requests hold at any time; the page pool is made for exactly "
+                             "this many, in pages of 16 tokens, so pages are used again (a caller that rounds each "
+                             "request up to a multiple of 64 has counted enough)")
     parser.add_argument("--device", default="cuda:0")
     args = parser.parse_args(argv)
     runner = build_runner(args.model, args.dtype, args.max_tokens, args.device)
