@@ -17,6 +17,8 @@ import argparse
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="flexengine bench", description="Measure the engine on one GPU; prints one JSON line")
     p.add_argument("--workload", choices=["decode", "serve-1.5b", "long-14b", "lengths"], default="decode")
+    p.add_argument("--shape", choices=["7b", "1.5b", "14b"], default="7b",
+                   help="the model shape of the decode workload (the headline is 7b)")
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=64, help="timed decode steps (decode workload)")
     p.add_argument("--warmup", type=int, default=16,

@@ -11,7 +11,7 @@ from __future__ import annotations
 import json
 
 from .clocks import ClockSampler, load_peaks
-from .shapes import CONTEXT_LEN, PAGE, PROMPT_LEN, SEVEN_B, decode_bytes, flat_config, prefill_flops
+from .shapes import CONTEXT_LEN, PAGE, PROMPT_LEN, SHAPES, decode_bytes, flat_config, prefill_flops
 from .timing import Timer
 
 MIXED_PORTION, MIXED_AFTER, MIXED_DECODERS = 128, 3072, 7
@@ -28,7 +28,8 @@ def run(args) -> int:
 
     dev = "cuda:0"
     peaks, peak_source = load_peaks(args.peaks)
-    cfg = dict(SEVEN_B)
+    cfg = dict(SHAPES[args.shape])
+    shape_name = f"Qwen2.5-{args.shape.upper()} shape"
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -161,7 +162,7 @@ def run(args) -> int:
     del runner, cache
     torch.cuda.empty_cache()
     engine = Engine.from_model(model, EngineConfig(
-        model="random-7b-shape", device=dev, dtype="bfloat16", max_model_len=CONTEXT_LEN, max_num_seqs=args.batch,
+        model=f"random-{args.shape}-shape", device=dev, dtype="bfloat16", max_model_len=CONTEXT_LEN, max_num_seqs=args.batch,
         max_num_batched_tokens=PROMPT_LEN, prefill_chunk_size=PROMPT_LEN, kv_block_size=PAGE,
         kv_num_blocks=args.batch * CONTEXT_LEN // PAGE, max_output_tokens=4096, max_waiting=max(64, args.batch),
         scheduler_policy="fcfs", trace_steps=False, cuda_graph=args.cuda_graph))
@@ -191,13 +192,13 @@ def run(args) -> int:
     sampler.stop()
 
     line = {
-        "metric": "decode tokens/s (Qwen2.5-7B shape, batch 8, 2,048-token prompts)", "value": value, "unit": "tokens/s",
+        "metric": f"decode tokens/s ({shape_name}, batch {args.batch}, 2,048-token prompts)", "value": value, "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic: random token ids, random weights N(0, 0.02)",
         "impl": "ours",
-        "config": flat_config(cfg, model="Qwen2.5-7B shape", layers_full=full_layers, global_batch=args.batch,
+        "config": flat_config(cfg, model=shape_name, layers_full=full_layers, global_batch=args.batch,
                               seq_len=CONTEXT_LEN, prompt_len=PROMPT_LEN, kv_page=PAGE, parallelism="single GPU",
-                              cuda_graph=bool(args.cuda_graph), l2="inputs larger than L2 (15 GB of weights per step)",
+                              cuda_graph=bool(args.cuda_graph), l2=f"inputs larger than L2 ({decode_bytes(cfg, 0, 0) / 1e9:.0f} GB of weights per step)",
                               peaks=peak_source),
         "e2e": e2e,
         "prefill": prefill,
