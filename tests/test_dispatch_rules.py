@@ -25,6 +25,26 @@ def test_decode_splits_stay_within_one_resident_round():
         assert f"MAX_SPLITS_SHARED = {ops.DECODE_MAX_SPLITS};" in f.read()
 
 
+def test_cluster_splits_fit_one_round_of_the_device():
+    # clusters resident at once by cluster size, as a B200 answered for the decode kernel at head size 128
+    held = {2: 296, 3: 187, 4: 142, 5: 112, 6: 93, 7: 78, 8: 71, 9: 60, 10: 56, 11: 45, 12: 42, 13: 38, 14: 35, 15: 31, 16: 31}
+    resident = held.__getitem__
+    cluster = ops.decode_cluster_splits
+    assert cluster(1, 2048, 32, resident) == 0                        # nothing to merge
+    assert cluster(21, 4096, 32, resident) == 14                      # batch 8, four heads: 31 clusters of 16 fit, 32 are needed
+    assert cluster(14, 2048, 32, resident) == 14
+    assert cluster(13, 4096, 64, resident) == 8                       # batch 16: 60 clusters of 9 fit, 71 of 8
+    assert cluster(64, 4096, 4, resident) == 16 and cluster(28, 4096, 16, resident) == 16      # few clusters: the largest
+    assert cluster(6, 4096, 128, resident) == 6 and cluster(3, 4096, 256, resident) == 3       # many small ones: rounds anyway
+    assert cluster(27, 8192, 32, resident) == 0 and cluster(111, 16384, 4, resident) == 0      # long contexts: two kernels
+    assert cluster(12, 2048, 32, lambda s: 0) == 0                    # a device that places no such cluster
+    assert cluster(21, 4096) == 16                                    # no word from the device: the kernel's limit
+    for splits in range(1, 40):
+        for clusters in (1, 4, 32, 64, 100, 256, 1000):
+            got = cluster(splits, 2048, clusters, resident)
+            assert 0 <= got <= min(splits, ops.DECODE_CLUSTER_MAX_SPLITS)
+
+
 def test_prefill_splits_follow_the_work():
     def split(*a, **k):
         return ops.prefill_splits(*a, sms=SMS, **k)
