@@ -1,4 +1,6 @@
-// Sampling on the device: one block per row of logits.
+// Sampling on the device: a thread-block cluster per row of logits (one to eight blocks of 1,024 threads, by how
+// many rows there are), each block with a contiguous slice of the vocabulary; what the blocks have to know of one
+// another (maxima, histograms, masses, tie counts) they read from each other's shared memory.
 //
 // temperature == 0: the lowest index of the maximum (reference: engine/sampling/sampler.py:12-13).
 // otherwise: x = logits / T; when 0 < k < V keep the k largest (ties go to the lowest indices);
@@ -7,10 +9,11 @@
 // generator keyed by (request seed, number of the draw), so that a request's tokens do not
 // depend on what else is in the batch (reference: engine/scheduler/state.py:64-65).
 //
-// Every pass over a row is coalesced: warp w owns the contiguous segment [w S, (w + 1) S) of the vocabulary and
-// walks it 32 indices at a time.  Mass is summed chunk by chunk (a fixed butterfly inside the chunk, then a running
-// sum), warp totals are added up by one thread in index order, and the pass that looks for the token repeats the same
-// arithmetic, so the intervals of the tokens tile [0, total) and the result is the same on every run.
+// The vocabulary is cut into 256 segments of equal length, whatever the cluster size; a warp walks a segment 32
+// indices at a time, so every pass is coalesced.  Mass is summed chunk by chunk (a fixed butterfly inside the chunk,
+// then a running sum), the segments' masses are added up by one thread in index order, and the pass that looks for
+// the token repeats the same arithmetic, so the intervals of the tokens tile [0, total) and the result is the same
+// on every run, in every batch and with every cluster size.
 #include <math_constants.h>
 
 #define FE_PDL_CLASS 8      // FE_PDL_SAMPLING
@@ -23,6 +26,20 @@ namespace {
 constexpr int THREADS = 1024;
 constexpr int WARPS = THREADS / 32;
 constexpr int RADIX_LOADS = 8;      // loads on their way at once in a pass of the radix select
+constexpr int SEGMENTS = 256;       // of a row; a block of a cluster of C owns SEGMENTS / C of them, a warp SEGMENTS / C / 32
+constexpr int MAX_CLUSTER = 8;
+
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the same 32-bit variable in the shared memory of block ``rank`` of this cluster
+__device__ __forceinline__ unsigned int ld_peer(const void* own, unsigned rank) {
+    unsigned remote, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"((unsigned)__cvta_generic_to_shared(own)), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];\n" : "=r"(v) : "r"(remote));
+    return v;
+}
 
 __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
     x += 0x9E3779B97F4A7C15ull;
@@ -48,32 +65,41 @@ __device__ __forceinline__ float warp_total(float v) {       // the same value i
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, long long ld, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const long long* __restrict__ seed,
-              const long long* __restrict__ draw, int* __restrict__ out) {
+              const long long* __restrict__ draw, int* __restrict__ out, const int C) {
     griddep_wait();
     griddep_launch_dependents();
     __shared__ float s_val[THREADS];
     __shared__ int s_idx[THREADS];
-    __shared__ unsigned int hist[256], suffix[256];
+    __shared__ float blk_val;                           // this block's maximum and its lowest index
+    __shared__ int blk_idx;
+    __shared__ unsigned int hist[256], total_hist[256], suffix[256];
     __shared__ unsigned int warp_hist[WARPS][256];      // one histogram per warp: no two warps meet in a bin
     __shared__ unsigned int s_prefix, s_need;
-    __shared__ float warp_mass[WARPS + 1];      // after the prefix: mass before warp w; [WARPS] = total
-    __shared__ int warp_ties[WARPS];            // after the prefix: threshold ties before warp w, in index order
-    __shared__ int s_result;
+    __shared__ float seg_mass[SEGMENTS];                // of this block's segments (the first SEGMENTS / C entries)
+    __shared__ int seg_ties[SEGMENTS];
+    __shared__ float mass_before[SEGMENTS + 1];         // of every segment of the row: mass before it; [SEGMENTS] = total
+    __shared__ int ties_before[SEGMENTS];               // threshold ties before it, in index order
 
-    const int row = blockIdx.x, tid = threadIdx.x;
+    const int row = blockIdx.x / C, tid = threadIdx.x;
+    const unsigned rank = blockIdx.x % C;               // of this block in its cluster
     const float* x = logits + (size_t)row * ld;
     const float temp = temperature[row];
+    // segments of S indices (a multiple of 32); this block's slice of the row is its segments side by side
+    const int S = ((V + SEGMENTS - 1) / SEGMENTS + 31) / 32 * 32;
+    const int per_block = SEGMENTS / C, per_warp = per_block / WARPS;
+    const int lo = (int)min((long long)V, (long long)rank * per_block * S), hi = (int)min((long long)V, (long long)(rank + 1) * per_block * S);
 
     // ---- maximum and its lowest index (needed by both branches)
     float best = -CUDART_INF_F;
     int best_i = 0x7fffffff;
-    if ((V & 3) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
-        // four logits per load, four loads in flight per thread: a row is read by one block, so what bounds this
-        // pass is how many loads are on their way at once
+    const bool vector = (V & 3) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0;      // lo is a multiple of 32
+    if (vector) {
+        // four logits per load, four loads in flight per thread: what bounds this pass is how many loads are on
+        // their way at once
         const float4* x4 = reinterpret_cast<const float4*>(x);
-        const int n4 = V >> 2;
+        const int n4 = hi >> 2;                          // hi is V or a multiple of 32
         const float4 none = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
-        for (int i = tid; i < n4; i += 4 * THREADS) {
+        for (int i = (lo >> 2) + tid; i < n4; i += 4 * THREADS) {
             float4 part[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) part[u] = i + u * THREADS < n4 ? x4[i + u * THREADS] : none;
@@ -90,7 +116,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
             }
         }
     } else {
-        for (int i = tid; i < V; i += THREADS) {
+        for (int i = lo + tid; i < hi; i += THREADS) {
             const float v = sanitize(x[i]);
             if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
         }
@@ -104,10 +130,19 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
         }
         __syncthreads();
     }
-    const float max_logit = s_val[0];
-    const int argmax = s_idx[0] == 0x7fffffff ? 0 : s_idx[0];
+    if (tid == 0) { blk_val = s_val[0]; blk_idx = s_idx[0]; }
+    cluster_sync();
+    float max_logit = -CUDART_INF_F;
+    int argmax = 0x7fffffff;
+    for (int c = 0; c < C; ++c) {                       // the blocks' slices are in index order
+        const float v = __uint_as_float(ld_peer(&blk_val, c));
+        const int i = (int)ld_peer(&blk_idx, c);
+        if (v > max_logit || (v == max_logit && i < argmax)) { max_logit = v; argmax = i; }
+    }
+    if (argmax == 0x7fffffff) argmax = 0;
+    if (rank == 0 && tid == 0) out[row] = argmax;       // the answer at temperature 0, and what stands if no mass is found
     if (temp == 0.f) {
-        if (tid == 0) out[row] = argmax;
+        cluster_sync();                                 // no block leaves while another may still read its maximum
         return;
     }
 
@@ -130,11 +165,11 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
                 const unsigned int key = ordered_key(sanitize(raw));
                 if ((key & mask) == prefix) atomicAdd(&warp_hist[tid >> 5][(key >> shift) & 0xffu], 1u);
             };
-            if ((V & 3) == 0 && (reinterpret_cast<size_t>(x) & 15) == 0) {
+            if (vector) {
                 // the order does not matter here: four logits per load, four loads on their way per thread
                 const float4* x4 = reinterpret_cast<const float4*>(x);
-                const int n4 = V >> 2;
-                for (int i = tid; i < n4; i += 4 * THREADS) {
+                const int n4 = hi >> 2;
+                for (int i = (lo >> 2) + tid; i < n4; i += 4 * THREADS) {
                     float4 part[4];
                     bool in[4];
 #pragma unroll
@@ -147,13 +182,13 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
                         if (in[u]) { count(part[u].x); count(part[u].y); count(part[u].z); count(part[u].w); }
                 }
             } else {
-                for (int i0 = tid; i0 < V; i0 += RADIX_LOADS * THREADS) {
+                for (int i0 = lo + tid; i0 < hi; i0 += RADIX_LOADS * THREADS) {
                     float v[RADIX_LOADS];
 #pragma unroll
-                    for (int u = 0; u < RADIX_LOADS; ++u) v[u] = i0 + u * THREADS < V ? x[i0 + u * THREADS] : 0.f;
+                    for (int u = 0; u < RADIX_LOADS; ++u) v[u] = i0 + u * THREADS < hi ? x[i0 + u * THREADS] : 0.f;
 #pragma unroll
                     for (int u = 0; u < RADIX_LOADS; ++u)
-                        if (i0 + u * THREADS < V) count(v[u]);
+                        if (i0 + u * THREADS < hi) count(v[u]);
                 }
             }
             __syncthreads();
@@ -162,11 +197,17 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
                 for (int w = 0; w < WARPS; ++w) sum += warp_hist[w][tid];
                 hist[tid] = sum;
             }
+            cluster_sync();
+            // every block adds up the blocks' histograms and finds the bin for itself: the same in all of them
+            if (tid < 256) {
+                unsigned int sum = 0;
+                for (int c = 0; c < C; ++c) sum += ld_peer(&hist[tid], c);
+                total_hist[tid] = sum;
+                suffix[tid] = sum;
+            }
             __syncthreads();
             // the bin in which the count of larger keys passes what is still needed: thread b holds the number of keys
             // in bins above b (suffix sums by doubling), exactly one thread finds need within its own bin
-            if (tid < 256) suffix[tid] = hist[tid];
-            __syncthreads();
             for (int off = 1; off < 256; off <<= 1) {
                 const unsigned int add = tid < 256 && tid + off < 256 ? suffix[tid + off] : 0u;
                 __syncthreads();
@@ -176,126 +217,130 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
             const unsigned int remaining = s_need;
             __syncthreads();
             if (tid < 256) {
-                const unsigned int above = suffix[tid] - hist[tid];        // keys in bins above this one
+                const unsigned int above = suffix[tid] - total_hist[tid];        // keys in bins above this one
                 if (above < remaining && (suffix[tid] >= remaining || tid == 0)) {
                     s_prefix = prefix | ((unsigned int)tid << shift);
                     s_need = remaining - above;
                 }
             }
-            __syncthreads();
+            cluster_sync();                             // the blocks' histograms have been read: they may be made anew
         }
         thr_key = s_prefix;
         need = s_need;             // how many of the keys equal to the threshold are kept
     }
 
-    // ---- warp w owns the contiguous segment [seg0, seg1) of the vocabulary and walks it 32 indices at a time
+    // ---- warp w walks its segments, one after the other, 32 indices at a time
     const int warp = tid >> 5, lane = tid & 31;
-    const int S = ((V + WARPS - 1) / WARPS + 31) / 32 * 32;
-    const int seg0 = min(V, warp * S), seg1 = min(V, seg0 + S);
     const unsigned int below = (1u << lane) - 1u;
 
-    // Eight chunks (256 indices) are loaded at once, so that eight loads are on their way together: a row is read by
-    // one block, and what bounds a pass is the latency of its loads.
+    // Eight chunks (256 indices) are loaded at once, so that eight loads are on their way together.
     constexpr int GROUP = 8;
-    auto load_group = [&](int base, float* v) {
+    auto load_group = [&](int base, int seg1, float* v) {
 #pragma unroll
         for (int c = 0; c < GROUP; ++c) {
             const int i = base + 32 * c + lane;
             v[c] = i < seg1 ? x[i] : 0.f;
         }
     };
+    auto bounds = [&](int segment, int& seg0, int& seg1) {      // of segment ``segment`` of the row
+        seg0 = (int)min((long long)V, (long long)segment * S);
+        seg1 = (int)min((long long)V, (long long)seg0 + S);
+    };
 
-    // threshold ties before this warp's segment, in index order
+    // threshold ties of every segment, and from them the ties before each, in index order
     if (use_k) {
-        int ties = 0;
-        for (int base = seg0; base < seg1; base += 32 * GROUP) {
-            float v[GROUP];
-            load_group(base, v);
+        for (int j = 0; j < per_warp; ++j) {
+            const int mine = warp * per_warp + j;
+            int seg0, seg1;
+            bounds((int)rank * per_block + mine, seg0, seg1);
+            int ties = 0;
+            for (int base = seg0; base < seg1; base += 32 * GROUP) {
+                float v[GROUP];
+                load_group(base, seg1, v);
 #pragma unroll
-            for (int c = 0; c < GROUP; ++c)
-                ties += __popc(__ballot_sync(0xffffffffu, base + 32 * c + lane < seg1 && ordered_key(sanitize(v[c])) == thr_key));
+                for (int c = 0; c < GROUP; ++c)
+                    ties += __popc(__ballot_sync(0xffffffffu, base + 32 * c + lane < seg1 && ordered_key(sanitize(v[c])) == thr_key));
+            }
+            if (lane == 0) seg_ties[mine] = ties;
         }
-        if (lane == 0) warp_ties[warp] = ties;
+        cluster_sync();
+        if (tid < SEGMENTS) ties_before[tid] = (int)ld_peer(&seg_ties[tid % per_block], tid / per_block);
         __syncthreads();
         if (tid == 0) {
             int run = 0;
-            for (int w = 0; w < WARPS; ++w) { const int t = warp_ties[w]; warp_ties[w] = run; run += t; }
+            for (int g = 0; g < SEGMENTS; ++g) { const int t = ties_before[g]; ties_before[g] = run; run += t; }
         }
         __syncthreads();
     }
-    const int tie_base = use_k ? warp_ties[warp] : 0;
     const float inv_temp = 1.f / temp, inv_shift = max_logit * inv_temp;
 
     // the unnormalised probability of index ``i`` with logit ``raw`` (0 when it is cut off), and the running tie count
-    auto mass_of = [&](int i, float raw, int& ties_seen) -> float {
+    auto mass_of = [&](int i, int seg1, int tie_base, float raw, int& ties_seen) -> float {
         const bool in = i < seg1;
         const float v = sanitize(raw);
         bool keep = in;
         if (use_k) {
             const unsigned int key = ordered_key(v);
             const unsigned int tied = __ballot_sync(0xffffffffu, in && key == thr_key);
-            const int rank = tie_base + ties_seen + __popc(tied & below);
-            keep = in && (key > thr_key || (key == thr_key && (unsigned int)rank < need));
+            const int rank_of_tie = tie_base + ties_seen + __popc(tied & below);
+            keep = in && (key > thr_key || (key == thr_key && (unsigned int)rank_of_tie < need));
             ties_seen += __popc(tied);
         }
         return keep ? __expf(v * inv_temp - inv_shift) : 0.f;
     };
 
-    // mass of the segment: per group, each lane adds its eight values in order, the lanes' sums are added by a fixed
-    // butterfly, and the groups' sums are added up as the walk goes.  Lane g remembers where group g began (the sum
-    // and the tie count before it), so that the search below can start at the right group.
-    float began_at = 0.f;
-    int ties_at = 0;
-    {
+    // mass of a segment: per group, each lane adds its eight values in order, the lanes' sums are added by a fixed
+    // butterfly, and the groups' sums are added up as the walk goes
+    for (int j = 0; j < per_warp; ++j) {
+        const int mine = warp * per_warp + j, segment = (int)rank * per_block + mine;
+        int seg0, seg1;
+        bounds(segment, seg0, seg1);
+        const int tie_base = use_k ? ties_before[segment] : 0;
         float cum = 0.f;
-        int ties_seen = 0, g = 0;
-        for (int base = seg0; base < seg1; base += 32 * GROUP, ++g) {
-            if (lane == g) { began_at = cum; ties_at = ties_seen; }
+        int ties_seen = 0;
+        for (int base = seg0; base < seg1; base += 32 * GROUP) {
             float v[GROUP];
-            load_group(base, v);
+            load_group(base, seg1, v);
             float part = 0.f;
 #pragma unroll
-            for (int c = 0; c < GROUP; ++c) part += mass_of(base + 32 * c + lane, v[c], ties_seen);
+            for (int c = 0; c < GROUP; ++c) part += mass_of(base + 32 * c + lane, seg1, tie_base, v[c], ties_seen);
             cum += warp_total(part);
         }
-        if (lane == 0) warp_mass[warp] = cum;
+        if (lane == 0) seg_mass[mine] = cum;
     }
+    cluster_sync();
+    if (tid < SEGMENTS) mass_before[tid] = __uint_as_float(ld_peer(&seg_mass[tid % per_block], tid / per_block));
     __syncthreads();
     if (tid == 0) {
-        // accumulated by one thread in index order: nondecreasing, so the warps' intervals tile [0, total)
+        // accumulated by one thread in index order: nondecreasing, so the segments' intervals tile [0, total)
         float run = 0.f;
-        for (int w = 0; w < WARPS; ++w) { const float m = warp_mass[w]; warp_mass[w] = run; run += m; }
-        warp_mass[WARPS] = run;
-        s_result = -1;
+        for (int g = 0; g < SEGMENTS; ++g) { const float m = mass_before[g]; mass_before[g] = run; run += m; }
+        mass_before[SEGMENTS] = run;
     }
-    __syncthreads();
-    const float total = warp_mass[WARPS];
+    cluster_sync();                                     // every block has read the others' masses (and ties): they may leave
+    const float total = mass_before[SEGMENTS];
     const unsigned long long bits = splitmix64(splitmix64((unsigned long long)seed[row]) + (unsigned long long)draw[row]);
     const float u = (float)(bits >> 40) * (1.0f / 16777216.0f);
     float target = u * total;
     if (target >= total) target = nextafterf(total, 0.f);
 
-    // the warp into whose interval the target falls repeats its walk with the same arithmetic, stops at the group
+    // the warp into whose segment the target falls repeats its walk with the same arithmetic, stops at the group
     // that takes the running sum past the target, and looks for the token inside it chunk by chunk, lane by lane
-    if (warp_mass[warp] <= target && target < warp_mass[warp + 1]) {
-        float cum = warp_mass[warp];
-        int ties_seen = 0, found = -1, last_kept = -1, first = seg0;
-        const int groups = (seg1 - seg0 + 32 * GROUP - 1) / (32 * GROUP);
-        if (groups <= 32) {
-            // the last group that began at or below the target (sums are nondecreasing along the groups)
-            const unsigned int at_or_below = __ballot_sync(0xffffffffu, lane < groups && warp_mass[warp] + began_at <= target);
-            const int g = at_or_below ? 31 - __clz(at_or_below) : 0;
-            cum += __shfl_sync(0xffffffffu, began_at, g);
-            ties_seen = __shfl_sync(0xffffffffu, ties_at, g);
-            first = seg0 + g * 32 * GROUP;
-        }
-        for (int base = first; base < seg1 && found < 0; base += 32 * GROUP) {
+    for (int j = 0; j < per_warp; ++j) {
+        const int segment = (int)rank * per_block + warp * per_warp + j;
+        if (!(mass_before[segment] <= target && target < mass_before[segment + 1])) continue;
+        int seg0, seg1;
+        bounds(segment, seg0, seg1);
+        const int tie_base = use_k ? ties_before[segment] : 0;
+        float cum = mass_before[segment];
+        int ties_seen = 0, found = -1, last_kept = -1;
+        for (int base = seg0; base < seg1 && found < 0; base += 32 * GROUP) {
             float v[GROUP], p[GROUP];
-            load_group(base, v);
+            load_group(base, seg1, v);
             float part = 0.f;
 #pragma unroll
             for (int c = 0; c < GROUP; ++c) {
-                p[c] = mass_of(base + 32 * c + lane, v[c], ties_seen);
+                p[c] = mass_of(base + 32 * c + lane, seg1, tie_base, v[c], ties_seen);
                 part += p[c];
             }
             const float group = warp_total(part);
@@ -324,19 +369,63 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
             cum += group;
         }
         if (found < 0) found = last_kept;              // rounding at the very end of the segment
-        if (lane == 0 && found >= 0) atomicMax(&s_result, found);
+        // exactly one segment of the row holds the target; block 0's argmax was written two cluster barriers ago
+        if (lane == 0 && found >= 0) out[row] = found;
     }
-    __syncthreads();
-    if (tid == 0) out[row] = s_result >= 0 ? s_result : argmax;
 }
 
 }  // namespace
+
+// How many blocks share a row: as many as keep the device to one round of blocks (one of 1,024 threads fits an SM).
+static int blocks_per_row(int R) {
+    const int slots = fe_sm_count();
+    int c = MAX_CLUSTER;
+    while (c > 1 && (long long)R * c > slots) c >>= 1;
+    return c;
+}
 
 extern "C" int fe_sample(const float* logits, long long ld, int R, int V, const float* temperature,
                          const int* top_k, const long long* seed, const long long* draw, int* out,
                          cudaStream_t stream) {
     FE_REQUIRE(R >= 0 && V > 0 && ld >= V, "sample: bad sizes R=%d V=%d ld=%lld", R, V, ld);
+    FE_REQUIRE((long long)R * MAX_CLUSTER < (1LL << 31), "sample: too many rows");
     if (R == 0) return 0;
-    fe::launch(sample_kernel, R, THREADS, 0, stream, logits, ld, V, temperature, top_k, seed, draw, out);
+    const int C = blocks_per_row(R);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(R * C));
+    cfg.blockDim = dim3(THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, temperature, top_k, seed, draw, out, C);
+    FE_REQUIRE(err == cudaSuccess, "sample (clusters of %d): %s", C, cudaGetErrorString(err));
+    return fe_check_launch("sample");
+}
+
+// The same with a given number of blocks a row (1, 2, 4 or 8): the tokens are the same for every number.
+extern "C" int fe_sample_blocks(const float* logits, long long ld, int R, int V, const float* temperature,
+                                const int* top_k, const long long* seed, const long long* draw, int* out,
+                                int blocks, cudaStream_t stream) {
+    FE_REQUIRE(R >= 0 && V > 0 && ld >= V, "sample: bad sizes R=%d V=%d ld=%lld", R, V, ld);
+    FE_REQUIRE(blocks == 1 || blocks == 2 || blocks == 4 || blocks == 8, "sample: %d blocks a row; 1, 2, 4 or 8", blocks);
+    if (R == 0) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(R * blocks));
+    cfg.blockDim = dim3(THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = blocks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, ld, V, temperature, top_k, seed, draw, out, blocks);
+    FE_REQUIRE(err == cudaSuccess, "sample (clusters of %d): %s", blocks, cudaGetErrorString(err));
     return fe_check_launch("sample");
 }

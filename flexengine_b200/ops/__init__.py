@@ -616,8 +616,10 @@ def paged_attention(qkv, k_cache, v_cache, block_table, ctx, nq, nkv, d, page_si
                              ctx.max_q_len, nq, nkv, d, page_size, scale, window)
 
 
-def sample(logits, temperature, top_k, seed, draw):
-    """int32 [R]: one token per row of float32 logits [R, V]; see csrc/sampling.cu."""
+def sample(logits, temperature, top_k, seed, draw, blocks: int = 0):
+    """int32 [R]: one token per row of float32 logits [R, V]; see csrc/sampling.cu.  ``blocks``: how many thread
+    blocks (a cluster of 1, 2, 4 or 8) share a row; 0 lets the kernel library choose by the number of rows.  The
+    tokens do not depend on it."""
     _need_cuda(logits, temperature, top_k, seed, draw)
     R, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
@@ -626,8 +628,12 @@ def sample(logits, temperature, top_k, seed, draw):
             or draw.dtype != torch.int64:
         raise TypeError("sample: temperature float32, top_k int32, seed and draw int64")
     out = torch.empty(R, dtype=torch.int32, device=logits.device)
-    _run(_core(), "fe_sample", _ptr(logits), _c_ll(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
-         _ptr(top_k), _ptr(seed), _ptr(draw), _ptr(out), _stream())
+    if blocks:
+        _run(_core(), "fe_sample_blocks", _ptr(logits), _c_ll(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
+             _ptr(top_k), _ptr(seed), _ptr(draw), _ptr(out), _c_int(blocks), _stream())
+    else:
+        _run(_core(), "fe_sample", _ptr(logits), _c_ll(logits.stride(0)), _c_int(R), _c_int(V), _ptr(temperature),
+             _ptr(top_k), _ptr(seed), _ptr(draw), _ptr(out), _stream())
     return out
 
 

@@ -636,6 +636,35 @@ def test_sample_temperature_top_k(V):
     assert torch.equal(shuffled, base[perm])
 
 
+@pytest.mark.parametrize("V", [11, 301, 5000, 152064, 152063])
+def test_sample_does_not_depend_on_how_many_blocks_share_a_row(V):
+    """A row is sampled by a cluster of one to eight blocks, by how many rows the step has: the token must be the
+    same for every size (the vocabulary is cut into the same 256 segments, and their masses are added up in the same
+    order), so a request's tokens do not depend on the size of its batch."""
+    torch.manual_seed(1)
+    R = 12
+    logits = torch.randn(R, V, device=DEV) * 2
+    logits[3, : min(V, 8)] = 7.0                              # ties at the top-k edge, in the first segment
+    logits[4, V - 1] = logits[4, V // 2] = logits[4, 0] = 9.0        # and in segments of different blocks
+    logits[6, 5] = float("nan")
+    temperature = torch.tensor([0.0, 0.7, 1.0, 0.9, 0.5, 2.0] * 2, device=DEV)
+    top_k = torch.tensor([0, 0, 50, 5, 2, V, 1, 3, 0, 40, 7, V - 1], dtype=torch.int32, device=DEV)
+    seed = torch.arange(7, 7 + R, dtype=torch.int64, device=DEV)
+    for draw_no in range(8):
+        draw = torch.full((R,), draw_no, dtype=torch.int64, device=DEV)
+        chosen = ops().sample(logits, temperature, top_k, seed, draw).cpu()
+        for blocks in (1, 2, 4, 8):
+            assert torch.equal(ops().sample(logits, temperature, top_k, seed, draw, blocks=blocks).cpu(), chosen), (blocks, draw_no)
+    # and not on the number of rows of the step: a row alone, and among a hundred
+    many = logits.repeat(9, 1)
+    draw = torch.full((9 * R,), 3, dtype=torch.int64, device=DEV)
+    among = ops().sample(many, temperature.repeat(9), top_k.repeat(9), seed.repeat(9), draw).cpu()
+    for r in range(R):
+        alone = ops().sample(logits[r:r + 1], temperature[r:r + 1], top_k[r:r + 1], seed[r:r + 1], draw[:1]).cpu()
+        assert int(alone[0]) == int(among[r]) == int(among[5 * R + r])
+    ops().check_status(DEV)
+
+
 def test_sample_follows_the_distribution():
     V = 11
     logits = torch.tensor([[0.0, 1.0, 2.0, -1.0, 0.5, 3.0, -2.0, 1.5, 0.2, 2.5, -0.5]], device=DEV)
