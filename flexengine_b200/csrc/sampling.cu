@@ -72,7 +72,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
     __shared__ int s_idx[THREADS];
     __shared__ float blk_val;                           // this block's maximum and its lowest index
     __shared__ int blk_idx;
-    __shared__ unsigned int hist[256], total_hist[256], suffix[256];
+    __shared__ unsigned int hist[2][256], warp_above[8];      // hist: one per parity of the pass
     __shared__ unsigned int warp_hist[WARPS][256];      // one histogram per warp: no two warps meet in a bin
     __shared__ unsigned int s_prefix, s_need;
     __shared__ float seg_mass[SEGMENTS];                // of this block's segments (the first SEGMENTS / C entries)
@@ -195,35 +195,38 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
             if (tid < 256) {
                 unsigned int sum = 0;
                 for (int w = 0; w < WARPS; ++w) sum += warp_hist[w][tid];
-                hist[tid] = sum;
+                hist[pass & 1][tid] = sum;
             }
+            // One cluster barrier a pass: the histograms alternate between two buffers, and a block that writes a buffer
+            // again (two passes on) has passed the barrier of the pass between, which its peers reach only after
+            // they have read the earlier one.
             cluster_sync();
-            // every block adds up the blocks' histograms and finds the bin for itself: the same in all of them
+            // every block adds up the blocks' histograms and finds the bin for itself: the same in all of them.
+            // Thread b ends up with the number of keys in bins b and above: a suffix sum inside each warp of 32 bins by
+            // shuffles, then the totals of the warps above.
+            unsigned int mine = 0, at_and_above = 0;
             if (tid < 256) {
-                unsigned int sum = 0;
-                for (int c = 0; c < C; ++c) sum += ld_peer(&hist[tid], c);
-                total_hist[tid] = sum;
-                suffix[tid] = sum;
-            }
-            __syncthreads();
-            // the bin in which the count of larger keys passes what is still needed: thread b holds the number of keys
-            // in bins above b (suffix sums by doubling), exactly one thread finds need within its own bin
-            for (int off = 1; off < 256; off <<= 1) {
-                const unsigned int add = tid < 256 && tid + off < 256 ? suffix[tid + off] : 0u;
-                __syncthreads();
-                if (tid < 256) suffix[tid] += add;
-                __syncthreads();
+                for (int c = 0; c < C; ++c) mine += ld_peer(&hist[pass & 1][tid], c);
+                at_and_above = mine;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const unsigned int up = __shfl_down_sync(0xffffffffu, at_and_above, off);
+                    if ((tid & 31) + off < 32) at_and_above += up;
+                }
+                if ((tid & 31) == 0) warp_above[tid >> 5] = at_and_above;
             }
             const unsigned int remaining = s_need;
             __syncthreads();
             if (tid < 256) {
-                const unsigned int above = suffix[tid] - total_hist[tid];        // keys in bins above this one
-                if (above < remaining && (suffix[tid] >= remaining || tid == 0)) {
+                for (int w = (tid >> 5) + 1; w < 8; ++w) at_and_above += warp_above[w];
+                const unsigned int above = at_and_above - mine;                  // keys in bins above this one
+                // the bin in which the count of larger keys passes what is still needed: exactly one thread finds it
+                if (above < remaining && (at_and_above >= remaining || tid == 0)) {
                     s_prefix = prefix | ((unsigned int)tid << shift);
                     s_need = remaining - above;
                 }
             }
-            cluster_sync();                             // the blocks' histograms have been read: they may be made anew
+            __syncthreads();
         }
         thr_key = s_prefix;
         need = s_need;             // how many of the keys equal to the threshold are kept
@@ -376,12 +379,39 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
 
 }  // namespace
 
-// How many blocks share a row: as many as keep the device to one round of blocks (one of 1,024 threads fits an SM).
+// How many clusters of ``blocks`` blocks of the kernel the device holds at once (a cluster lives inside one of the GPU's
+// processing clusters); asked of the driver once per size and device.
+static int clusters_resident(int blocks) {
+    static int cached[64][4];
+    int device = 0, slot = blocks == 8 ? 3 : blocks == 4 ? 2 : blocks == 2 ? 1 : 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+    if (cached[device][slot] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(THREADS);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = blocks;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, sample_kernel, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            clusters = 0;
+        }
+        cached[device][slot] = clusters > 0 ? clusters : -1;
+    }
+    return cached[device][slot] > 0 ? cached[device][slot] : 0;
+}
+
+// How many blocks share a row: the most that still lets every row's cluster be resident at once (16 rows of eight
+// blocks are 128 blocks on 148 SMs, but only 15 such clusters fit the processing clusters: a second round).
 static int blocks_per_row(int R) {
-    const int slots = fe_sm_count();
-    int c = MAX_CLUSTER;
-    while (c > 1 && (long long)R * c > slots) c >>= 1;
-    return c;
+    for (int c = MAX_CLUSTER; c > 1; c >>= 1)
+        if (R <= clusters_resident(c)) return c;
+    return 1;
 }
 
 extern "C" int fe_sample(const float* logits, long long ld, int R, int V, const float* temperature,
