@@ -14,8 +14,9 @@
 // set the pace.)  The 16 rows of an MMA tile are the query heads of one key/value group
 // (decode) or (query, head-of-group) pairs (prefill), so the group shares every key it loads.
 //
-// decode:  one warp per (split of the keys, key/value head, request); partial results of the
-//          splits go to scratch memory and are merged by a second kernel (split-KV).
+// decode:  two warps per (split of the keys, key/value head, request).  The splits of one (request, key/value
+//          head) are a thread-block cluster that merges its partial results through distributed shared memory
+//          (up to 16 splits); with more splits they go to scratch memory and are merged by a second kernel.
 // prefill: four warps per (tile of 64 rows, key/value head, request); the warps share the
 //          key/value stages.
 #include <math_constants.h>
