@@ -49,6 +49,7 @@ namespace {
 
 typedef cublasStatus_t (*CreateFn)(cublasHandle_t*);
 typedef cublasStatus_t (*SetStreamFn)(cublasHandle_t, cudaStream_t);
+typedef cublasStatus_t (*SetMathModeFn)(cublasHandle_t, cublasMath_t);
 typedef cublasStatus_t (*GemmExFn)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*, const void*,
                                    cudaDataType, int, const void*, cudaDataType, int, const void*, void*, cudaDataType, int,
                                    cublasComputeType_t, cublasGemmAlgo_t);
@@ -57,6 +58,7 @@ struct Blas {
     bool looked = false;
     CreateFn create = nullptr;
     SetStreamFn set_stream = nullptr;
+    SetMathModeFn set_math_mode = nullptr;
     GemmExFn gemm_ex = nullptr;
     cublasHandle_t handle[64] = {};
 };
@@ -72,6 +74,7 @@ cublasHandle_t blas_handle() {
             g_blas.create = (CreateFn)dlsym(lib, "cublasCreate_v2");
             g_blas.set_stream = (SetStreamFn)dlsym(lib, "cublasSetStream_v2");
             g_blas.gemm_ex = (GemmExFn)dlsym(lib, "cublasGemmEx");
+            g_blas.set_math_mode = (SetMathModeFn)dlsym(lib, "cublasSetMathMode");
         }
     }
     if (!g_blas.create || !g_blas.set_stream || !g_blas.gemm_ex) {
@@ -83,10 +86,17 @@ cublasHandle_t blas_handle() {
         fe_set_error("layer_forward: no current device");
         return nullptr;
     }
-    if (g_blas.handle[device] == nullptr && g_blas.create(&g_blas.handle[device]) != CUBLAS_STATUS_SUCCESS) {
-        g_blas.handle[device] = nullptr;
-        fe_set_error("layer_forward: cublasCreate failed");
-        return nullptr;
+    if (g_blas.handle[device] == nullptr) {
+        if (g_blas.create(&g_blas.handle[device]) != CUBLAS_STATUS_SUCCESS) {
+            g_blas.handle[device] = nullptr;
+            fe_set_error("layer_forward: cublasCreate failed");
+            return nullptr;
+        }
+        // A product split along K adds its partial sums up in float, not in bfloat16 (the library's default allows
+        // the latter: errors of two to four times a bfloat16 rounding at K of a few thousand).
+        if (g_blas.set_math_mode)
+            g_blas.set_math_mode(g_blas.handle[device],
+                                 (cublasMath_t)(CUBLAS_DEFAULT_MATH | CUBLAS_MATH_DISALLOW_REDUCED_PRECISION_REDUCTION));
     }
     return g_blas.handle[device];
 }

@@ -20,6 +20,11 @@ from . import library
 # arguments or kinds of values do not fit.  These names say which C type a value is meant for.
 _c_int, _c_ll, _c_float = int, int, float
 
+# The library's bfloat16 products add the partial sums of a split K up in float: its default allows bfloat16 there, which
+# costs two to four times the error of one bfloat16 rounding at K of a few thousand (measured against the
+# weight-streaming kernel of this package, whose results are the float sums rounded once).
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 _status: dict = {}
 launches = 0          # kernels of this package launched so far (library matrix products not counted)
 

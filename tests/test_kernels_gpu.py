@@ -120,6 +120,20 @@ def test_skinny_gemm(M, N, K, gen):
     assert torch.equal(ops().skinny_gemm(x, w, ops().EPI_F32), ops().skinny_gemm(x, w, ops().EPI_F32))
 
 
+@pytest.mark.parametrize("M,N,K", [(13, 3581, 10240), (64, 2085, 3776), (135, 1000, 18944), (8, 3581, 10240)])
+def test_products_are_float_sums_rounded_once_whichever_kernel_takes_them(M, N, K, gen):
+    """A long K is split by the library's kernels; their partial sums must be added in float (the library's default
+    would allow bfloat16 there: errors of up to four roundings).  Whether a product goes to the weight-streaming
+    kernel (up to 8 rows) or to the library, its error is that of one bfloat16 rounding of the float result."""
+    x, w = rand((M, K), torch.bfloat16, gen), rand((N, K), torch.bfloat16, gen, 0.05)
+    want = x.float() @ w.float().T
+    rounding = (want.to(torch.bfloat16).float() - want).abs().max()
+    got = ops().linear(x, w)
+    assert float((got.float() - want).abs().max()) <= 1.02 * float(rounding) + 1e-3
+    wide = ops().linear(x, w, out_float32=True)
+    torch.testing.assert_close(wide, want, atol=2e-3, rtol=1e-3)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (128, 128, 256), (100, 200, 192), (300, 384, 3584), (2048, 512, 320),
                                    (129, 24, 72)])
 def test_gemm_tcgen05(M, N, K, gen):
