@@ -289,7 +289,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
             keep = in && (key > thr_key || (key == thr_key && (unsigned int)rank_of_tie < need));
             ties_seen += __popc(tied);
         }
-        return keep ? __expf(v * inv_temp - inv_shift) : 0.f;
+        return keep ? expf(v * inv_temp - inv_shift) : 0.f;
     };
 
     // mass of a segment: per group, each lane adds its eight values in order, the lanes' sums are added by a fixed
