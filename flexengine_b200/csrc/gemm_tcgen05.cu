@@ -122,6 +122,21 @@ template <int NCOLS> __device__ __forceinline__ void tmem_dealloc(unsigned taddr
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "n"(NCOLS) : "memory");
 }
 
+// The order of the tiles: row tiles fastest inside a panel of PANEL row tiles, the panels one after the other.  Blocks
+// that run together then share their rows of W (W comes from HBM once per panel), and the rows of x that a panel
+// needs (4,096 x K) stay in L2 while all of W passes by; with every row tile of a long prompt in flight at once
+// (8,192 rows) the output being written pushes x out of L2 between two column tiles.  Gate/up with SwiGLU under a
+// long-running load, 8,192 rows: 7B widths 1.80 -> 1.74 ms, 14B widths 2.07 -> 1.79 ms (panels of 8 / 16 / 24 row
+// tiles: 1.93 / 1.78 / 1.75 and 1.95 / 1.82 / 1.81); up to 4,096 rows nothing changes.
+constexpr int PANEL = 32;
+__device__ __forceinline__ void tile_origin(int t, int m_tiles, int n_tiles, int out_cols, int& m0, int& n0) {
+    const int per_panel = PANEL * n_tiles;
+    const int panel = t / per_panel, within = t - panel * per_panel;
+    const int rows_here = min(PANEL, m_tiles - panel * PANEL);      // the last panel may hold fewer row tiles
+    m0 = (panel * PANEL + within % rows_here) * BM;
+    n0 = (within / rows_here) * out_cols;
+}
+
 constexpr int BN = 256;             // accumulator columns of one tile = UMMA N
 constexpr int ACC_BUFFERS = 2;
 
@@ -162,7 +177,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---- TMA producer ----
         int kbg = 0;                                   // k blocks issued so far, over all tiles
         for (int t = blockIdx.x; t < total_tiles && !give_up; t += gridDim.x) {
-            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * OUT_COLS;
+            int m0, n0;
+            tile_origin(t, m_tiles, n_tiles, OUT_COLS, m0, n0);
             for (int kb = 0; kb < num_kb; ++kb, ++kbg) {
                 const int s = kbg % STAGES, use = kbg / STAGES;
                 if (!mbar_wait(&empty_bar[s], (use & 1) ^ 1)) { give_up = 1; break; }   // parity 1 passes at once at the start
@@ -205,7 +221,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int i = 0;
         for (int t = blockIdx.x; t < total_tiles && !give_up; t += gridDim.x, ++i) {
             const int buf = i & 1;
-            const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * OUT_COLS;
+            int m0, n0;
+            tile_origin(t, m_tiles, n_tiles, OUT_COLS, m0, n0);
             if (!mbar_wait(&acc_full[buf], (i >> 1) & 1)) { give_up = 1; break; }
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;

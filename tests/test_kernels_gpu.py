@@ -135,7 +135,7 @@ def test_products_are_float_sums_rounded_once_whichever_kernel_takes_them(M, N, 
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (128, 128, 256), (100, 200, 192), (300, 384, 3584), (2048, 512, 320),
-                                   (129, 24, 72)])
+                                   (129, 24, 72), (2300, 520, 128), (4097, 256, 64), (4300, 264, 64)])
 def test_gemm_tcgen05(M, N, K, gen):
     """The tcgen05 / TMEM / TMA product against float32 PyTorch: tails in M, N and K, several
     passes round the ring of stages, both epilogues."""
